@@ -1,0 +1,32 @@
+// Internal host-side helpers shared by the launchers: thread-local error
+// text, the CUDA-call guard, per-device scratch for the host-buffer entry points.
+#pragma once
+
+#include <cstdarg>
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../../include/ferro_kittens.h"
+
+/// Record a formatted message as this thread's last error and return `code`.
+int fk_fail(int code, const char* format, ...);
+
+#define FK_CUDA(call)                                                                      \
+    do {                                                                                   \
+        cudaError_t fk_cuda_status = (call);                                               \
+        if (fk_cuda_status != cudaSuccess)                                                 \
+            return fk_fail(FK_ERR_DRIVER, "%s failed: %s", #call,                          \
+                           cudaGetErrorString(fk_cuda_status));                            \
+    } while (0)
+
+namespace fk {
+
+/// A device buffer cached per (device, slot) for the host-buffer entry points;
+/// grown when a call needs more, released at process exit by the runtime.
+int scratch(int slot, size_t bytes, void** out);
+
+/// 4 status words per device for the host-buffer entry points.
+int scratch_status(uint32_t** out);
+
+}  // namespace fk

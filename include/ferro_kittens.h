@@ -1,0 +1,204 @@
+/*
+ * ferro_kittens.h -- C ABI of the B200 (sm_100a) implementation of ferro-kittens'
+ * two dense-contraction hot paths: the two-CTA-cluster bf16 GEMM and
+ * flash-attention forward.
+ *
+ * Every entry point is what a Rust `extern "C"` block in the ferro-kittens crate
+ * would bind to keep its host surface (`global`, `plan`, `launch`, `watchdog`,
+ * the two kernel entry points) while the kernels behind it are CUDA C++.
+ * Each declaration cites the reference item it stands in for, by the file's
+ * path inside the ferro-kittens repository.
+ *
+ * Conventions: plain pointers and sizes only; device pointers are `void*` /
+ * `const void*`; a `cudaStream_t` is passed as `void*`; a tensor map is the
+ * driver's 128-byte, 64-byte-aligned `CUtensorMap`, owned by the caller and
+ * passed by address (the kernels take it by value as a grid constant, so no
+ * device upload is needed). Functions return FK_OK or a negative error code;
+ * `fk_last_error()` returns the thread-local message naming the violated field.
+ * Nothing here falls back to a CPU path.
+ */
+#ifndef FERRO_KITTENS_H
+#define FERRO_KITTENS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    FK_OK = 0,
+    FK_ERR_INVALID = -1,      /* null pointer / bad enum */
+    FK_ERR_SHAPE = -2,        /* shape does not divide the tiling, zero group, ... */
+    FK_ERR_ALIGNMENT = -3,    /* a driver alignment rule of the tensor map */
+    FK_ERR_TOO_LARGE = -4,    /* shared plan past the device's opt-in limit */
+    FK_ERR_DRIVER = -5,       /* the CUDA driver / runtime refused a call */
+    FK_ERR_TIMEOUT = -6,      /* a host wait ran out of its budget */
+    FK_ERR_DEVICE_STALL = -7  /* a kernel's bounded wait gave up; see fk_status_decode */
+};
+
+typedef enum { FK_BF16 = 0, FK_F16 = 1, FK_F32 = 2 } fk_element_t;
+typedef enum { FK_SWIZZLE_NONE = 0, FK_SWIZZLE_128B = 3 } fk_swizzle_t;
+
+/* Thread-local message of the last failing call on this thread ("" if none). */
+const char* fk_last_error(void);
+
+/* ---------------------------------------------------------------- global layouts
+ *
+ * `GlobalLayout<E, RANK>` (src/global.rs:1767-1889): a RANK-dimensional buffer,
+ * dimension 0 contiguous; `strides_bytes[0]` is the element size and is implied
+ * to the driver. `fk_layout_packed` = `GlobalLayout::packed` (:1794-1802),
+ * `fk_layout_strided` = `GlobalLayout::strided` (:1826-1841; fails unless
+ * element_strides[0] == 1).
+ */
+typedef struct {
+    uint64_t base;             /* device address; never dereferenced on the host */
+    uint32_t rank;             /* 1..5 */
+    uint32_t element;          /* fk_element_t */
+    uint64_t extents[5];       /* dimension 0 fastest */
+    uint64_t strides_bytes[5]; /* byte stride of each dimension */
+} fk_layout_t;
+
+int fk_layout_packed(fk_layout_t* out, uint64_t base, uint32_t element, uint32_t rank,
+                     const uint64_t* extents);
+int fk_layout_strided(fk_layout_t* out, uint64_t base, uint32_t element, uint32_t rank,
+                      const uint64_t* extents, const uint64_t* element_strides);
+
+/* `GlobalLayout::descriptor_shape::<T>` (src/global.rs:1867-1888): globalDim and
+ * boxDim for a map delivering a tile whose box is [box_columns, box_rows]. */
+int fk_layout_descriptor_shape(const fk_layout_t* layout, uint32_t box_columns, uint32_t box_rows,
+                               uint64_t* extents_out, uint32_t* box_out);
+
+/* `GlobalLayout::check_driver_requirements` (src/global.rs:1969-2017): base 16-byte
+ * aligned, strides multiples of 16, box dimension 0 a multiple of 16 bytes, no box
+ * wider than its extent, no box over 256. Needs no driver. */
+int fk_layout_check(const fk_layout_t* layout, const uint64_t* extents, const uint32_t* box);
+
+/* `GlobalLayout::tensor_map::<T>` (src/global.rs:1920-1964) over
+ * cuTensorMapEncodeTiled: element strides 1, INTERLEAVE_NONE, the given swizzle,
+ * L2 promotion NONE, OOB fill NONE. `map_out` is 128 bytes, 64-byte aligned. */
+int fk_tensor_map(void* map_out, const fk_layout_t* layout, uint32_t box_columns,
+                  uint32_t box_rows, uint32_t swizzle);
+
+/* `encode_bf16_panels::<R, C>` (src/global.rs:2067-2076): rank-3 SWIZZLE_128B map
+ * over a packed [planes, rows, columns] bf16 buffer, box [64, box_rows, 1];
+ * fails unless rows % box_rows == 0. */
+int fk_encode_bf16_panels(void* map_out, uint64_t base, uint32_t box_rows, uint32_t columns,
+                          uint64_t rows, uint64_t planes);
+
+/* ---------------------------------------------------------------- plan / launch
+ *
+ * `SharedPlan` (src/plan.rs:73-304) as a cursor of two words. Each reservation
+ * aligns to its own rule (tiles 128, barriers 8, slot 4) and returns the start
+ * of the run; `bytes` is what a launch declares.
+ */
+typedef struct {
+    uint64_t bytes;
+} fk_plan_t;
+
+void fk_plan_sizing(fk_plan_t* plan);                                        /* :143-150 */
+uint64_t fk_plan_reserve(fk_plan_t* plan, uint64_t bytes, uint64_t align);   /* :177-195 */
+uint64_t fk_plan_tile(fk_plan_t* plan, uint32_t element, uint64_t rows, uint64_t columns);
+uint64_t fk_plan_tile_ring(fk_plan_t* plan, uint32_t element, uint64_t rows, uint64_t columns,
+                           uint64_t count);                                  /* :213-225 */
+uint64_t fk_plan_semaphores(fk_plan_t* plan, uint64_t count);                /* :263-267 */
+uint64_t fk_plan_tmem_slot(fk_plan_t* plan);                                 /* :276-279 */
+
+/* Dynamic shared memory the two kernels declare (the `#[launch_contract]`
+ * literal of examples/src/gemm.rs:397-402 and SHARED_BYTES of
+ * examples/src/flash_forward.rs:141, for this implementation's own plans). */
+uint32_t fk_gemm_shared_bytes(void);
+uint32_t fk_gemm_threads(void);
+uint32_t fk_flash_shared_bytes(void);
+uint32_t fk_flash_threads(void);
+
+/* `gemm::grid` (examples/src/gemm.rs:472-475): CTAs the launch asks for, a whole
+ * number of two-CTA clusters, capped at one cluster per SM pair. */
+uint32_t fk_gemm_grid(uint32_t m, uint32_t n, uint32_t sm_count);
+
+/* `launch::admit_shared_plan` (src/launch.rs:110-132): opt `kernel` (a host
+ * function pointer of a __global__) into `bytes` of dynamic shared memory.
+ * Idempotent, never lowers; FK_ERR_TOO_LARGE past the device's opt-in limit,
+ * which is written to `limit_out` either way. */
+int fk_admit_shared_plan(const void* kernel, uint32_t bytes, uint32_t* limit_out);
+
+/* ---------------------------------------------------------------- traversal and descriptors
+ * Pure arithmetic, exported so a binding's tests can pin it without a GPU. */
+void fk_grouped(uint32_t item, uint32_t rows, uint32_t columns, uint32_t group, uint32_t* row_out,
+                uint32_t* column_out);                     /* src/pipeline.rs:207-213 */
+uint32_t fk_swizzled_chunk_offset(uint32_t row, uint32_t chunk, uint32_t phase);
+                                                           /* src/shared.rs:1341-1348 */
+uint64_t fk_operand_descriptor(uint64_t shared_address, uint32_t leading_bytes);
+                                                           /* src/shared.rs:1251-1258 */
+uint32_t fk_instruction_descriptor(uint32_t m, uint32_t n, int transpose_a, int transpose_b);
+                                                           /* src/mma.rs:137-146 */
+uint32_t fk_tmem_address(uint32_t base, uint32_t row, uint32_t column); /* src/tmem.rs:487 */
+
+/* ---------------------------------------------------------------- kernels
+ *
+ * GEMM: `kernels::gemm_cg2_staged_x8x4` + `gemm::run`'s guards
+ * (examples/src/gemm.rs:404-413, 487-496). C[m,n] = sum_k A[m,k]*B[n,k]; A is
+ * row-major [m,k] bf16, B is K-major [n,k] bf16, C row-major [m,n] bf16.
+ *   a_map: rank-2 dims [k, m], box [64, 128], SWIZZLE_128B
+ *   b_map: rank-2 dims [k, n], box [64, 128], SWIZZLE_128B
+ *   c_map: rank-2 dims [n, m] (outer stride = ldc bytes), box [64, 32], SWIZZLE_128B
+ * Requires m % 256 == 0, n % 256 == 0, k % 64 == 0, group >= 1. Asynchronous on
+ * `stream`. `device_status` is null or 4 zeroed device words the kernel writes
+ * only if a bounded wait gives up (decode with fk_status_decode).
+ */
+int fk_gemm_bf16_launch(const void* a_map, const void* b_map, const void* c_map, uint32_t m,
+                        uint32_t n, uint32_t k, uint32_t group, void* stream,
+                        uint32_t* device_status);
+
+/* Convenience over the three map builders + the launch, from device pointers
+ * (what `gemm::run` does between staging and read-back, :506-536). */
+int fk_gemm_bf16(const void* a, const void* b, void* c, uint32_t m, uint32_t n, uint32_t k,
+                 uint32_t ldc, uint32_t group, void* stream, uint32_t* device_status);
+
+/* The whole of `gemm::run` from HOST buffers (:503-537): stage A and B, launch,
+ * read C back; blocks until C is on the host. Device buffers are cached per
+ * device and grown on demand. */
+int fk_gemm_bf16_host(const uint16_t* a_host, const uint16_t* b_host, uint16_t* c_host, uint32_t m,
+                      uint32_t n, uint32_t k, uint32_t group);
+
+/* Flash-attention forward: `kernels::flash_forward` + `flash_forward::run`'s
+ * guards (examples/src/flash_forward.rs:151-158, 477-483), widened to a batch,
+ * a non-causal mode, bf16 output and a log-sum-exp vector. Q, K, V and O are
+ * packed [planes = batch*heads, seq, 128] bf16; lse is [planes, seq] fp32
+ * (natural log), may be null. `o_f32`, when non-null, receives the output as
+ * fp32 [planes, seq, 128] (the reference kernel's own output type) instead of
+ * bf16 through `o_map`.
+ *   q_map / k_map / v_map / o_map: fk_encode_bf16_panels(base, 128 box rows, 128, seq, planes)
+ * Requires seq % 128 == 0, planes >= 1. */
+int fk_flash_fwd_launch(const void* q_map, const void* k_map, const void* v_map, const void* o_map,
+                        float* o_f32, float* lse, uint32_t planes, uint32_t seq, float scale,
+                        int causal, void* stream, uint32_t* device_status);
+
+/* Convenience from device pointers. */
+int fk_flash_fwd(const void* q, const void* k, const void* v, void* o_bf16, float* o_f32,
+                 float* lse, uint32_t planes, uint32_t seq, float scale, int causal, void* stream,
+                 uint32_t* device_status);
+
+/* From HOST buffers: stage Q, K, V, launch, read O (bf16) and lse back. */
+int fk_flash_fwd_host(const uint16_t* q_host, const uint16_t* k_host, const uint16_t* v_host,
+                      uint16_t* o_host, float* lse_host, uint32_t planes, uint32_t seq, float scale,
+                      int causal);
+
+/* ---------------------------------------------------------------- waits and status
+ *
+ * `watchdog::wait` / `wait_event` (src/watchdog.rs:300-332): poll with a
+ * deadline instead of blocking in a synchronize. Unlike the reference these
+ * return FK_ERR_TIMEOUT rather than aborting the process. */
+int fk_wait_stream(void* stream, uint32_t budget_ms);
+int fk_wait_event(void* event, uint32_t budget_ms);
+
+/* Read a kernel's 4 status words back (blocking on `stream`) and, when the
+ * first is non-zero, return FK_ERR_DEVICE_STALL with the role, block, stage and
+ * parity in fk_last_error(). */
+int fk_status_check(const uint32_t* device_status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FERRO_KITTENS_H */

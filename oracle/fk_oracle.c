@@ -1,0 +1,234 @@
+/*
+ * fk_oracle.c -- TEST INFRASTRUCTURE, NOT PRODUCT.
+ *
+ * A plain-C restatement of the CPU references the ferro-kittens examples check
+ * their two kernels against, used only as the checker in tests, in the smoke
+ * run and as the timed CPU baseline of the benchmark. Nothing in the library
+ * links, loads or calls this file.
+ *
+ * Parity is pinned: the reference's algorithm for this path lives in its own
+ * repository (no third-party dependency carries it), and the restatement is
+ * held to the known answers its tests state -- the exact integer GEMM gate
+ * (examples/src/gemm.rs:422-451, 544-578), the attention lattice and f64 row
+ * reference with its 2^-8 bound (examples/src/flash_forward.rs:313-440, 475),
+ * the bf16 rounding rule, and the fixtures under tests/golden/.
+ *
+ * Each function cites the reference lines it follows.
+ */
+#include <math.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+int fko_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+/* ---------------------------------------------------------------- bf16 */
+
+/* examples/src/gemm.rs:444-447 -- round-to-nearest-even fp32 -> bf16. */
+uint16_t fko_to_bf16(float value) {
+    uint32_t bits;
+    memcpy(&bits, &value, 4);
+    return (uint16_t)((bits + (0x7fffu + ((bits >> 16) & 1u))) >> 16);
+}
+
+/* examples/src/gemm.rs:449-451 */
+float fko_from_bf16(uint16_t bits) {
+    uint32_t wide = (uint32_t)bits << 16;
+    float value;
+    memcpy(&value, &wide, 4);
+    return value;
+}
+
+/* ---------------------------------------------------------------- GEMM operands */
+
+/* examples/src/gemm.rs:434-436 */
+float fko_gemm_a_value(size_t row, size_t depth) { return (float)((row * 5 + depth * 3) % 7) - 3.0f; }
+
+/* examples/src/gemm.rs:438-440 */
+float fko_gemm_b_value(size_t column, size_t depth) {
+    return (float)((column * 4 + depth * 5) % 21) - 10.0f;
+}
+
+/* examples/src/gemm.rs:455-464 -- a [rows, k] operand as bf16 words, K contiguous
+ * (the reference packs two per u32, low half first: the same bytes). */
+void fko_gemm_stage(int which, size_t rows, size_t k, uint16_t* out) {
+#pragma omp parallel for schedule(static)
+    for (size_t row = 0; row < rows; ++row)
+        for (size_t depth = 0; depth < k; ++depth)
+            out[row * k + depth] =
+                fko_to_bf16(which == 0 ? fko_gemm_a_value(row, depth) : fko_gemm_b_value(row, depth));
+}
+
+/* examples/src/gemm.rs:544-578 -- compare an observed bf16 C element by element
+ * with == against the 7 x 21 distinct dot products the operands' periods leave.
+ * Returns the number of wrong elements; *worst receives the worst relative
+ * error against the exact fp32 value; first_wrong (may be null) the flat index
+ * of the first mismatch. */
+size_t fko_gemm_check_c(const uint16_t* observed, size_t m, size_t n, size_t k, double* worst,
+                        size_t* first_wrong) {
+    float exact[7 * 21];
+    uint16_t reference[7 * 21];
+    for (size_t cell = 0; cell < 7 * 21; ++cell) {
+        float sum = 0.0f;
+        for (size_t depth = 0; depth < k; ++depth)
+            sum += fko_gemm_a_value(cell / 21, depth) * fko_gemm_b_value(cell % 21, depth);
+        exact[cell] = sum;
+        reference[cell] = fko_to_bf16(sum);
+    }
+    size_t wrong = 0, first = (size_t)-1;
+    double worst_seen = 0.0;
+    for (size_t row = 0; row < m; ++row) {
+        for (size_t column = 0; column < n; ++column) {
+            const size_t cell = (row % 7) * 21 + column % 21;
+            const uint16_t value = observed[row * n + column];
+            if (value != reference[cell]) {
+                if (wrong == 0) first = row * n + column;
+                ++wrong;
+            }
+            if (exact[cell] != 0.0f) {
+                const double error = fabs((double)(fko_from_bf16(value) - exact[cell]) / (double)exact[cell]);
+                if (error > worst_seen) worst_seen = error;
+            }
+        }
+    }
+    if (worst) *worst = worst_seen;
+    if (first_wrong) *first_wrong = first;
+    return wrong;
+}
+
+/* The reference value of one cell, for a caller that wants the expected C. */
+uint16_t fko_gemm_expected(size_t row, size_t column, size_t k) {
+    float sum = 0.0f;
+    for (size_t depth = 0; depth < k; ++depth)
+        sum += fko_gemm_a_value(row % 7, depth) * fko_gemm_b_value(column % 21, depth);
+    return fko_to_bf16(sum);
+}
+
+/* ---------------------------------------------------------------- GEMM over arbitrary bf16 inputs
+ *
+ * The same contraction check_c's `exact` performs (:545-551: a running fp32
+ * sum over depth of a*b, then one rounding to bf16), over caller-supplied
+ * bf16 operands: rows [row0, row0+rows) of C = A . B^T, A [m, k], B [n, k].
+ * c_bf16 and/or c_f64 may be null; c_f64 receives the f64-accumulated value
+ * for error bounds. Output buffers hold `rows * n` elements.
+ */
+void fko_gemm_rows(const uint16_t* a, const uint16_t* b, size_t n, size_t k, size_t row0, size_t rows,
+                   uint16_t* c_bf16, double* c_f64) {
+    /* Widen the slab of A once; B rows are widened per column block. */
+    float* a_wide = (float*)malloc(rows * k * sizeof(float));
+    for (size_t i = 0; i < rows * k; ++i) a_wide[i] = fko_from_bf16(a[row0 * k + i]);
+#pragma omp parallel
+    {
+        float* b_wide = (float*)malloc(k * sizeof(float));
+#pragma omp for schedule(dynamic, 16)
+        for (size_t column = 0; column < n; ++column) {
+            for (size_t depth = 0; depth < k; ++depth) b_wide[depth] = fko_from_bf16(b[column * k + depth]);
+            for (size_t row = 0; row < rows; ++row) {
+                const float* a_row = a_wide + row * k;
+                if (c_bf16) {
+                    float sum = 0.0f;
+                    for (size_t depth = 0; depth < k; ++depth) sum += a_row[depth] * b_wide[depth];
+                    c_bf16[row * n + column] = fko_to_bf16(sum);
+                }
+                if (c_f64) {
+                    double sum = 0.0;
+                    for (size_t depth = 0; depth < k; ++depth) sum += (double)a_row[depth] * (double)b_wide[depth];
+                    c_f64[row * n + column] = sum;
+                }
+            }
+        }
+        free(b_wide);
+    }
+    free(a_wide);
+}
+
+/* ---------------------------------------------------------------- attention operands */
+
+/* examples/src/flash_forward.rs:326-334 */
+static size_t permutation(size_t tensor, size_t head, size_t row, size_t column) {
+    const size_t stride = 11 + 2 * ((row + 17 * tensor) % 63);
+    return (53 * head + 37 * row + stride * column + 71 * tensor) % 128;
+}
+size_t fko_flash_permutation(size_t tensor, size_t head, size_t row, size_t column) {
+    return permutation(tensor, head, row, column);
+}
+
+/* examples/src/flash_forward.rs:341-347 */
+float fko_flash_q_value(size_t head, size_t row, size_t dim) {
+    return dim == 0 ? 2.0f : ((float)permutation(0, head, row, dim) - 64.0f) / 64.0f;
+}
+/* examples/src/flash_forward.rs:349-355 */
+float fko_flash_k_value(size_t head, size_t row, size_t dim) {
+    return dim == 0 ? (float)row / 8.0f : ((float)permutation(1, head, row, dim) - 64.0f) / 64.0f;
+}
+/* examples/src/flash_forward.rs:360-362 */
+float fko_flash_v_value(size_t head, size_t row, size_t dim) {
+    return 1.0f + (float)permutation(2, head, row, dim) / 64.0f;
+}
+
+/* examples/src/flash_forward.rs:382-393 -- [heads, sequence, 128] bf16, head-major. */
+void fko_flash_stage(int which, size_t sequence, size_t heads, uint16_t* out) {
+    for (size_t head = 0; head < heads; ++head)
+        for (size_t row = 0; row < sequence; ++row)
+            for (size_t dim = 0; dim < 128; ++dim) {
+                const float value = which == 0   ? fko_flash_q_value(head, row, dim)
+                                    : which == 1 ? fko_flash_k_value(head, row, dim)
+                                                 : fko_flash_v_value(head, row, dim);
+                out[(head * sequence + row) * 128 + dim] = fko_to_bf16(value);
+            }
+}
+
+/* examples/src/flash_forward.rs:419-440 -- the straightforward stable softmax
+ * times V for query rows [row0, row0+rows) of one [sequence, 128] plane, in
+ * f64 over the bf16 inputs: scores, subtract the row max, exponentiate, weight
+ * V, divide by the sum. The reference is causal only (keys 0..=row); `causal`
+ * == 0 attends all `sequence` keys, which is the same function over a longer
+ * key range. lse (may be null) receives max + ln(sum), the natural-log
+ * normaliser the row's softmax divides by.
+ */
+void fko_flash_rows(const uint16_t* q, const uint16_t* k, const uint16_t* v, size_t sequence,
+                    size_t row0, size_t rows, double scale, int causal, double* out, double* lse) {
+#pragma omp parallel
+    {
+        double* weights = (double*)malloc(sequence * sizeof(double));
+#pragma omp for schedule(dynamic, 4)
+        for (size_t r = 0; r < rows; ++r) {
+            const size_t row = row0 + r;
+            const size_t keys = causal ? row + 1 : sequence;
+            double qw[128];
+            for (size_t d = 0; d < 128; ++d) qw[d] = (double)fko_from_bf16(q[row * 128 + d]);
+            double max = -INFINITY;
+            for (size_t key = 0; key < keys; ++key) {
+                double dot = 0.0;
+                for (size_t d = 0; d < 128; ++d) dot += qw[d] * (double)fko_from_bf16(k[key * 128 + d]);
+                weights[key] = scale * dot;
+                if (weights[key] > max) max = weights[key];
+            }
+            double total = 0.0;
+            for (size_t key = 0; key < keys; ++key) {
+                weights[key] = exp(weights[key] - max);
+                total += weights[key];
+            }
+            double acc[128];
+            for (size_t d = 0; d < 128; ++d) acc[d] = 0.0;
+            for (size_t key = 0; key < keys; ++key) {
+                const double w = weights[key];
+                for (size_t d = 0; d < 128; ++d) acc[d] += w * (double)fko_from_bf16(v[key * 128 + d]);
+            }
+            for (size_t d = 0; d < 128; ++d) out[r * 128 + d] = acc[d] / total;
+            if (lse) lse[r] = max + log(total);
+        }
+        free(weights);
+    }
+}

@@ -1,0 +1,136 @@
+"""GPU parity of flash-attention forward against the CPU oracle, through the C ABI.
+
+The first gate is the reference's own (examples/src/flash_forward.rs:313-321,
+475, 534-560): lattice operands, S = 256, 2 heads, scale 0.125, causal, fp32
+output, relative error <= 2^-8 against the f64 row reference. The seeded
+random cases use the task's tolerance, max|err| <= 2e-2 on O (and on LSE).
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from ferro_kittens_b200 import FerroKittensError, flash_forward, gemm
+
+pytestmark = pytest.mark.gpu
+
+
+def _to_device(words: np.ndarray, device) -> torch.Tensor:
+    return torch.from_numpy(words.view(np.int16)).to(device).view(torch.bfloat16)
+
+
+def _to_words(tensor: torch.Tensor) -> np.ndarray:
+    return tensor.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def _run_checked(q, k, v, **kwargs):
+    status = gemm.new_status(q.device)
+    out, lse = flash_forward.run(q, k, v, status=status, **kwargs)
+    gemm.check_status(status)
+    return out, lse
+
+
+def _oracle_planes(q, k, v, scale, causal, rows=None):
+    """f64 reference for every plane of [planes, seq, 128] bf16 words (or the sampled rows)."""
+    planes, sequence, _ = q.shape
+    outs, lses = [], []
+    for plane in range(planes):
+        if rows is None:
+            out, lse = oracle.flash_rows(q[plane], k[plane], v[plane], 0, sequence, scale, causal)
+        else:
+            parts = [oracle.flash_rows(q[plane], k[plane], v[plane], r, 1, scale, causal) for r in rows]
+            out = np.concatenate([p[0] for p in parts])
+            lse = np.concatenate([p[1] for p in parts])
+        outs.append(out)
+        lses.append(lse)
+    return np.stack(outs), np.stack(lses)
+
+
+@pytest.mark.parametrize("sequence,heads", [(256, 2), (128, 1), (384, 3), (1024, 2)])
+def test_reference_lattice_gate(device, sequence, heads):
+    """The reference's check (256 x 2) and neighbours: one tile only, a ragged pair, a longer ring."""
+    q = oracle.flash_stage("q", sequence, heads)
+    k = oracle.flash_stage("k", sequence, heads)
+    v = oracle.flash_stage("v", sequence, heads)
+    out, _ = _run_checked(_to_device(q, device), _to_device(k, device), _to_device(v, device),
+                          scale=flash_forward.SCALE, causal=True, out_dtype=torch.float32)
+    expected, _ = _oracle_planes(q, k, v, flash_forward.SCALE, True)
+    relative = np.abs((out.cpu().numpy().astype(np.float64) - expected) / expected)
+    assert not np.isnan(relative).any()
+    assert relative.max() <= 2 ** -8, f"worst relative error {relative.max():.3e}"
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("shape", [(2, 2, 512), (1, 3, 1280)])
+def test_seeded_random_within_tolerance(device, causal, shape):
+    batch, heads, sequence = shape
+    generator = torch.Generator(device="cpu").manual_seed(3 + int(causal))
+    q, k, v = (torch.randn((batch, heads, sequence, 128), generator=generator).to(torch.bfloat16)
+               for _ in range(3))
+    out, lse = _run_checked(q.to(device), k.to(device), v.to(device), causal=causal)
+    planes = batch * heads
+    words = [_to_words(x).reshape(planes, sequence, 128) for x in (q, k, v)]
+    expected, expected_lse = _oracle_planes(*words, 128 ** -0.5, causal)
+    got = out.float().cpu().numpy().reshape(planes, sequence, 128).astype(np.float64)
+    assert np.abs(got - expected).max() <= 2e-2
+    assert np.abs(lse.cpu().numpy().reshape(planes, sequence) - expected_lse).max() <= 2e-2
+
+
+def test_moving_maximum_forces_rescales(device):
+    """Keys whose scores climb by far more than the rescale threshold from block to block."""
+    sequence = 1024
+    generator = torch.Generator(device="cpu").manual_seed(11)
+    q = torch.randn((1, sequence, 128), generator=generator)
+    k = torch.randn((1, sequence, 128), generator=generator)
+    v = torch.randn((1, sequence, 128), generator=generator)
+    q[..., 0] = 8.0
+    k[..., 0] = torch.arange(sequence, dtype=torch.float32) / 4.0  # +2 per key in raw score
+    q, k, v = (x.to(torch.bfloat16) for x in (q, k, v))
+    for causal in (False, True):
+        out, lse = _run_checked(q.to(device), k.to(device), v.to(device), causal=causal)
+        expected, expected_lse = _oracle_planes(_to_words(q), _to_words(k), _to_words(v), 128 ** -0.5, causal)
+        assert np.abs(out.float().cpu().numpy().astype(np.float64) - expected).max() <= 2e-2
+        assert np.abs(lse.cpu().numpy() - expected_lse).max() <= 2e-2 * np.abs(expected_lse).max()
+
+
+def test_host_buffer_entry_point(device):
+    sequence, heads = 256, 2
+    q = oracle.flash_stage("q", sequence, heads)
+    k = oracle.flash_stage("k", sequence, heads)
+    v = oracle.flash_stage("v", sequence, heads)
+    out = np.zeros_like(q)
+    lse = np.zeros((heads, sequence), dtype=np.float32)
+    flash_forward.run_host(q, k, v, out, lse, heads, sequence, flash_forward.SCALE, True)
+    expected, expected_lse = _oracle_planes(q, k, v, flash_forward.SCALE, True)
+    relative = np.abs((oracle.bf16_to_f32(out).astype(np.float64) - expected) / expected)
+    assert relative.max() <= 2 ** -7  # bf16 output adds one rounding to the 2^-8 gate
+    assert np.abs(lse - expected_lse).max() <= 2e-2
+
+
+def test_shape_guards(device):
+    q = torch.zeros((1, 192, 128), dtype=torch.bfloat16, device=device)
+    with pytest.raises(FerroKittensError, match="does not divide"):
+        flash_forward.run(q, q, q)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        flash_forward.run(q.cpu(), q.cpu(), q.cpu())
+
+
+@pytest.mark.parametrize("config", [(16, 16, 4096, False, 3), (4, 32, 16384, True, 4)])
+def test_full_size_sampled_rows(device, config):
+    """The benchmark's two attention configurations, sampled rows against the oracle, plus the
+    size-independent property that every output row is a convex combination of V rows."""
+    batch, heads, sequence, causal, seed = config
+    generator = torch.Generator(device=device).manual_seed(seed)
+    q, k, v = (torch.randn((batch, heads, sequence, 128), generator=generator, device=device)
+               .to(torch.bfloat16) for _ in range(3))
+    out, lse = _run_checked(q, k, v, causal=causal)
+    assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
+    rows = [0, 127, 128, 1000, sequence // 2 + 5, sequence - 1]
+    for b, h in [(0, 0), (batch - 1, heads - 1)]:
+        words = [_to_words(x[b, h]).reshape(1, sequence, 128) for x in (q, k, v)]
+        expected, expected_lse = _oracle_planes(*words, 128 ** -0.5, causal, rows=rows)
+        got = out[b, h, rows].float().cpu().numpy().astype(np.float64)
+        assert np.abs(got - expected[0]).max() <= 2e-2
+        assert np.abs(lse[b, h, rows].cpu().numpy() - expected_lse[0]).max() <= 2e-2
+    bound = v.float().abs().amax(dim=2, keepdim=True)
+    assert (out.float().abs() <= bound * (1 + 2 ** -7)).all()

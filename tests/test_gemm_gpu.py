@@ -1,0 +1,134 @@
+"""GPU parity of the bf16 GEMM against the CPU oracle, through the C ABI.
+
+The exact gates are the reference's own (examples/src/gemm.rs:422-430, 583-610):
+integer operands, two sizes, four traversal widths, ``==`` on bf16 words. The
+seeded random cases use the tolerance the task states:
+``max|err| <= 1e-2 * sqrt(K) * max|a| * max|b|``.
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from ferro_kittens_b200 import FerroKittensError, gemm
+
+pytestmark = pytest.mark.gpu
+
+
+def _to_device(words: np.ndarray, device) -> torch.Tensor:
+    return torch.from_numpy(words.view(np.int16)).to(device).view(torch.bfloat16)
+
+
+def _to_words(tensor: torch.Tensor) -> np.ndarray:
+    return tensor.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def _run_checked(a, b, group=gemm.GROUP):
+    status = gemm.new_status(a.device)
+    c = gemm.run(a, b, group=group, status=status)
+    gemm.check_status(status)
+    return c
+
+
+@pytest.mark.parametrize("shape", [(512, 256, 256), (4096, 4096, 256)])
+@pytest.mark.parametrize("group", [8, 1, 3, 6])
+def test_reference_integer_gate_is_exact(device, shape, group):
+    m, n, k = shape
+    a = _to_device(oracle.gemm_stage("a", m, k), device)
+    b = _to_device(oracle.gemm_stage("b", n, k), device)
+    c = _run_checked(a, b, group)
+    wrong, worst, first = oracle.gemm_check_c(_to_words(c), m, n, k)
+    assert wrong == 0, f"{wrong} of {m * n} elements wrong, first at flat index {first}"
+    assert worst < 2 ** -8
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 64), (256, 256, 8192), (768, 1280, 1088)])
+def test_integer_operands_other_shapes_exact(device, shape):
+    """One tile and one k-block; a K deep enough to wrap the ring many times; ragged tile counts."""
+    m, n, k = shape
+    a = _to_device(oracle.gemm_stage("a", m, k), device)
+    b = _to_device(oracle.gemm_stage("b", n, k), device)
+    c = _run_checked(a, b, 3)
+    # K past 256 leaves fp32 sums exact (|a*b| <= 30, K <= 8192 -> < 2^24).
+    wrong, _, first = oracle.gemm_check_c(_to_words(c), m, n, k)
+    assert wrong == 0, f"{wrong} wrong, first at {first}"
+
+
+def test_config_1_uniform_1024_cubed(device):
+    """GEMM 1024^3, entries uniform[-1, 1) from seed 0, against the oracle over the same bf16 words."""
+    m = n = k = 1024
+    generator = torch.Generator(device="cpu").manual_seed(0)
+    a = (torch.rand((m, k), generator=generator) * 2 - 1).to(torch.bfloat16)
+    b = (torch.rand((n, k), generator=generator) * 2 - 1).to(torch.bfloat16)
+    c = _run_checked(a.to(device), b.to(device))
+    a_words, b_words = _to_words(a), _to_words(b)
+    expected, exact = oracle.gemm_rows(a_words, b_words, 0, m, want_f64=True)
+    got = oracle.bf16_to_f32(_to_words(c)).astype(np.float64)
+    bound = 1e-2 * math.sqrt(k) * float(a.abs().max()) * float(b.abs().max())
+    assert np.abs(got - exact).max() <= bound
+    # Far tighter in practice: one bf16 rounding of an fp32-accumulated sum.
+    assert np.abs(got - exact).max() <= np.abs(exact).max() * 2 ** -8 + 1e-3
+    assert (np.abs(got - oracle.bf16_to_f32(expected)) <= np.abs(exact) * 2 ** -7 + 1e-3).all()
+
+
+def test_leading_dimension_and_linearity(device):
+    """C written into a wider buffer leaves the margin untouched; (2A).B == 2(A.B) exactly in bf16."""
+    m, n, k = 512, 512, 512
+    generator = torch.Generator(device="cpu").manual_seed(5)
+    a = torch.randn((m, k), generator=generator).to(torch.bfloat16).to(device)
+    b = torch.randn((n, k), generator=generator).to(torch.bfloat16).to(device)
+    wide = torch.full((m, n + 64), 7.0, dtype=torch.bfloat16, device=device)
+    status = gemm.new_status(device)
+    from ferro_kittens_b200._lib import check, library
+    check(library().fk_gemm_bf16(a.data_ptr(), b.data_ptr(), wide.data_ptr(), m, n, k, n + 64, 8,
+                                 torch.cuda.current_stream().cuda_stream, status.data_ptr()))
+    gemm.check_status(status)
+    c = _run_checked(a, b)
+    assert torch.equal(wide[:, :n], c)
+    assert (wide[:, n:] == 7.0).all()
+    doubled = _run_checked(a * 2, b)
+    assert torch.equal(doubled, c * 2)
+
+
+def test_shape_guards_reject_before_launch(device):
+    a = torch.zeros((256, 64), dtype=torch.bfloat16, device=device)
+    b = torch.zeros((256, 64), dtype=torch.bfloat16, device=device)
+    with pytest.raises(FerroKittensError, match="traversal group width of 0"):
+        gemm.run(a, b, group=0)
+    with pytest.raises(FerroKittensError, match="does not divide"):
+        gemm.run(a[:128].contiguous(), b)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        gemm.run(a.cpu(), b.cpu())
+
+
+def test_host_buffer_entry_point(device):
+    m, n, k = 512, 256, 256
+    a = oracle.gemm_stage("a", m, k)
+    b = oracle.gemm_stage("b", n, k)
+    c = np.zeros((m, n), dtype=np.uint16)
+    gemm.run_host(a, b, c, m, n, k)
+    wrong, _, _ = oracle.gemm_check_c(c, m, n, k)
+    assert wrong == 0
+
+
+@pytest.mark.parametrize("shape", [(16384, 16384, 16384)])
+def test_full_size_properties(device, shape):
+    """At the benchmark's size: sampled rows against the oracle, and the whole matrix against
+    a bf16 matmul by torch within one rounding."""
+    m, n, k = shape
+    generator = torch.Generator(device=device).manual_seed(1)
+    a = (torch.randn((m, k), generator=generator, device=device) / math.sqrt(k)).to(torch.bfloat16)
+    b = (torch.randn((n, k), generator=generator, device=device) / math.sqrt(k)).to(torch.bfloat16)
+    c = _run_checked(a, b)
+    rows = [0, 4097, m - 1]
+    a_words = _to_words(a[rows].contiguous())
+    b_words = _to_words(b)
+    _, exact = oracle.gemm_rows(a_words, b_words, 0, len(rows), want_f64=True)
+    got = oracle.bf16_to_f32(_to_words(c[rows].contiguous())).astype(np.float64)
+    bound = 1e-2 * math.sqrt(k) * float(a.abs().max()) * float(b.abs().max())
+    assert np.abs(got - exact).max() <= bound
+    reference = a @ b.T
+    difference = (c.float() - reference.float()).abs().max().item()
+    assert difference <= 2 ** -7 * reference.float().abs().max().item()
