@@ -1,0 +1,121 @@
+"""The CPU oracle against the reference's known answers and the committed fixtures.
+
+Known answers taken from the reference's own sources: the bf16 rounding rule
+(examples/src/gemm.rs:444-447), the operand generators and their periods
+(:434-440, 544-552), the two check sizes and that the CPU reference of them is
+self-consistent under `check_c` (:422-430, 544-578), the attention lattice
+(examples/src/flash_forward.rs:326-362) and the properties its seed is built for
+(every value bf16-exact, V in [1, 3), outputs in [1, 3), a score ramp on the key axis).
+"""
+import hashlib
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import oracle
+
+GOLDEN = json.loads((Path(__file__).parent / "golden" / "golden.json").read_text())
+
+
+def test_bf16_rounding_is_nearest_even():
+    assert oracle.to_bf16(1.0) == 0x3F80
+    assert oracle.to_bf16(1.00390625) == 0x3F80      # exactly half way: ties to even (down)
+    assert oracle.to_bf16(1.01171875) == 0x3F82      # 1 + 3*2^-8: half way, ties to even (up)
+    assert oracle.to_bf16(-2.5) == 0xC020
+    for entry in GOLDEN["bf16"]:
+        assert oracle.to_bf16(entry["value"]) == entry["bits"]
+    values = np.random.default_rng(0).standard_normal(4096).astype(np.float32)
+    vector = oracle.f32_to_bf16(values)
+    assert all(vector[i] == oracle.to_bf16(float(values[i])) for i in range(0, 4096, 37))
+    assert (oracle.bf16_to_f32(vector).view(np.uint32) & 0xFFFF == 0).all()
+
+
+def test_gemm_operands_are_small_integers_with_the_documented_periods():
+    a = oracle.bf16_to_f32(oracle.gemm_stage("a", 64, 64))
+    b = oracle.bf16_to_f32(oracle.gemm_stage("b", 64, 64))
+    assert a.min() == -3 and a.max() == 3 and b.min() == -10 and b.max() == 10
+    assert (a == np.round(a)).all() and (b == np.round(b)).all()
+    assert (a[7:14] == a[:7]).all() and (b[21:42] == b[:21]).all()
+    assert oracle.gemm_a_value(2, 3) == (2 * 5 + 3 * 3) % 7 - 3
+    assert oracle.gemm_b_value(5, 2) == (5 * 4 + 2 * 5) % 21 - 10
+
+
+@pytest.mark.parametrize("k", [64, 256, 1088])
+def test_gemm_cell_table_matches_the_fixture(k):
+    cells = GOLDEN["gemm"][str(k)]
+    for cell in range(7 * 21):
+        assert oracle.gemm_expected(cell // 21, cell % 21, k) == cells["bf16"][cell]
+        assert oracle.from_bf16(cells["bf16"][cell]) == pytest.approx(cells["exact"][cell], rel=2 ** -8)
+
+
+@pytest.mark.parametrize("shape", [(512, 256, 256), (768, 1280, 1088)])
+def test_gemm_reference_is_self_consistent_and_matches_the_fixture(shape):
+    m, n, k = shape
+    a, b = oracle.gemm_stage("a", m, k), oracle.gemm_stage("b", n, k)
+    c, exact = oracle.gemm_rows(a, b, 0, m, want_f64=True)
+    wrong, worst, _ = oracle.gemm_check_c(c, m, n, k)
+    assert wrong == 0 and worst < 2 ** -8
+    fixture = GOLDEN["gemm"][f"{m}x{n}x{k}"]
+    assert hashlib.sha256(a.tobytes()).hexdigest() == fixture["a_sha256"]
+    assert hashlib.sha256(b.tobytes()).hexdigest() == fixture["b_sha256"]
+    assert hashlib.sha256(c.tobytes()).hexdigest() == fixture["c_sha256"]
+    # Integer operands: the fp32 running sum is exact, so it equals the f64 one.
+    assert (oracle.f32_to_bf16(exact.astype(np.float32)) == c).all()
+    # check_c really is `==`: one flipped bit is one wrong element, found where it is.
+    c[5, 9] ^= 1
+    assert oracle.gemm_check_c(c, m, n, k)[::2] == (1, 5 * n + 9)
+
+
+def test_gemm_rows_slab_equals_the_same_rows_of_the_whole():
+    rng = np.random.default_rng(1)
+    a = oracle.f32_to_bf16(rng.standard_normal((96, 320)).astype(np.float32))
+    b = oracle.f32_to_bf16(rng.standard_normal((80, 320)).astype(np.float32))
+    whole, whole64 = oracle.gemm_rows(a, b, 0, 96, want_f64=True)
+    slab, slab64 = oracle.gemm_rows(a, b, 32, 16, want_f64=True)
+    assert (slab == whole[32:48]).all() and (slab64 == whole64[32:48]).all()
+    reference = oracle.bf16_to_f32(a).astype(np.float64) @ oracle.bf16_to_f32(b).astype(np.float64).T
+    assert np.allclose(whole64, reference, rtol=1e-12, atol=1e-12)
+    assert np.abs(oracle.bf16_to_f32(whole) - reference).max() <= np.abs(reference).max() * 2 ** -8 + 1e-4
+
+
+def test_flash_lattice_has_the_properties_its_seed_is_built_for():
+    sequence, heads = GOLDEN["flash"]["sequence"], GOLDEN["flash"]["heads"]
+    tensors = {name: oracle.flash_stage(name, sequence, heads) for name in "qkv"}
+    for name, words in tensors.items():
+        assert hashlib.sha256(words.tobytes()).hexdigest() == GOLDEN["flash"]["inputs_sha256"][name]
+    q, k, v = (oracle.bf16_to_f32(tensors[name]) for name in "qkv")
+    assert (q[..., 0] == 2.0).all()
+    assert (k[..., 0] == np.arange(sequence, dtype=np.float32) / 8.0).all()      # the score ramp
+    assert v.min() >= 1.0 and v.max() < 3.0
+    assert np.abs(q[..., 1:]).max() <= 1.0 and np.abs(k[..., 1:]).max() <= 1.0
+    assert oracle._lib.fko_flash_permutation(2, 1, 5, 7) == (53 + 37 * 5 + (11 + 2 * ((5 + 34) % 63)) * 7 + 142) % 128
+
+
+def test_flash_rows_match_the_fixture_and_stay_convex():
+    sequence, heads, scale = (GOLDEN["flash"][key] for key in ("sequence", "heads", "scale"))
+    q, k, v = (oracle.flash_stage(name, sequence, heads) for name in "qkv")
+    for entry in GOLDEN["flash"]["rows"]:
+        out, lse = oracle.flash_rows(q[entry["head"]], k[entry["head"]], v[entry["head"]], entry["row"], 1,
+                                     scale, entry["causal"])
+        assert np.allclose(out[0], entry["out"], rtol=1e-12, atol=0)
+        assert lse[0] == pytest.approx(entry["lse"], abs=1e-10)
+        assert out.min() >= 1.0 and out.max() < 3.0
+    first, _ = oracle.flash_rows(q[0], k[0], v[0], 0, 1, scale, True)
+    assert np.allclose(first[0], oracle.bf16_to_f32(v[0, 0]))  # row 0 attends key 0 only
+
+
+def test_flash_rows_agree_with_a_dense_numpy_softmax():
+    rng = np.random.default_rng(2)
+    q, k, v = (oracle.f32_to_bf16(rng.standard_normal((192, 128)).astype(np.float32)) for _ in range(3))
+    for causal in (False, True):
+        out, lse = oracle.flash_rows(q, k, v, 0, 192, 128 ** -0.5, causal)
+        scores = (oracle.bf16_to_f32(q).astype(np.float64) @ oracle.bf16_to_f32(k).astype(np.float64).T) * 128 ** -0.5
+        if causal:
+            scores = np.where(np.tril(np.ones_like(scores, dtype=bool)), scores, -np.inf)
+        top = scores.max(axis=1, keepdims=True)
+        weights = np.exp(scores - top)
+        dense = weights @ oracle.bf16_to_f32(v).astype(np.float64) / weights.sum(axis=1, keepdims=True)
+        assert np.allclose(out, dense, rtol=1e-10, atol=1e-12)
+        assert np.allclose(lse, (top + np.log(weights.sum(axis=1, keepdims=True)))[:, 0], rtol=1e-12)

@@ -1,0 +1,78 @@
+"""The multi-GPU split on the CPU: shard arithmetic, and a world-size-2 gloo run in which each
+rank computes its own block with the oracle and the blocks tile the whole, with no collective on
+the data path (the gather below is the test's own check)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import oracle
+from ferro_kittens_b200 import shard
+
+
+def test_gemm_columns_tile_the_matrix_in_whole_tiles():
+    for n, world in [(16384, 1), (16384, 2), (16384, 4), (16384, 8), (28672, 8), (768, 2), (1280, 4)]:
+        blocks = [shard.gemm_columns(n, world, rank) for rank in range(world)]
+        assert blocks[0][0] == 0 and blocks[-1][1] == n
+        assert all(a[1] == b[0] for a, b in zip(blocks, blocks[1:]))
+        assert all(start % 256 == 0 and stop % 256 == 0 for start, stop in blocks)
+        sizes = [stop - start for start, stop in blocks]
+        assert max(sizes) - min(sizes) <= 256
+    with pytest.raises(ValueError):
+        shard.gemm_columns(1000, 2, 0)
+    with pytest.raises(ValueError):
+        shard.gemm_columns(1024, 2, 2)
+
+
+def test_planes_tile_the_batch():
+    for total, world in [(256, 8), (128, 8), (6, 4), (1, 2)]:
+        blocks = [shard.planes(total, world, rank) for rank in range(world)]
+        assert blocks[0][0] == 0 and blocks[-1][1] == total
+        assert all(a[1] == b[0] for a, b in zip(blocks, blocks[1:]))
+
+
+def _free_port() -> int:
+    with socket.socket() as probe:
+        probe.bind(("127.0.0.1", 0))
+        return probe.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        m, n, k = 256, 768, 128
+        a, b = oracle.gemm_stage("a", m, k), oracle.gemm_stage("b", n, k)
+        start, stop = shard.gemm_columns(n, world, rank)
+        block, _ = oracle.gemm_rows(a, b[start:stop], 0, m)
+        # timing aggregation as the benchmark does it: the slowest rank sets the step time
+        seconds = torch.tensor([0.25 + rank], dtype=torch.float64)
+        dist.all_reduce(seconds, op=dist.ReduceOp.MAX)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (start, stop, block.tobytes()))
+        if rank == 0:
+            whole = np.zeros((m, n), dtype=np.uint16)
+            for s, e, raw in gathered:
+                whole[:, s:e] = np.frombuffer(raw, dtype=np.uint16).reshape(m, e - s)
+            results.put((oracle.gemm_check_c(whole, m, n, k)[0], float(seconds.item())))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_compute_disjoint_blocks_that_tile_c():
+    context = mp.get_context("spawn")
+    results = context.Queue()
+    world, port = 2, _free_port()
+    workers = [context.Process(target=_worker, args=(rank, world, port, results)) for rank in range(world)]
+    for worker in workers:
+        worker.start()
+    wrong, slowest = results.get(timeout=120)
+    for worker in workers:
+        worker.join(timeout=60)
+        assert worker.exitcode == 0
+    assert wrong == 0
+    assert slowest == 1.25
