@@ -354,8 +354,54 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         dist.destroy_process_group()
 
 
+def run_only(args, local_rank: int) -> None:
+    """One kernel alone on a chosen size: the command an ncu capture wraps."""
+    import torch
+
+    from ferro_kittens_b200 import gemm
+    from ferro_kittens_b200._lib import check, library
+
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    stream = torch.cuda.current_stream().cuda_stream
+    status = gemm.new_status(device)
+    if args.only == "gemm":
+        m, n, k = args.m, args.n, args.k
+        generator = torch.Generator(device=device).manual_seed(GEMM_SEED)
+        a = (torch.randn((m, k), generator=generator, device=device) / math.sqrt(k)).to(torch.bfloat16)
+        b = (torch.randn((n, k), generator=generator, device=device) / math.sqrt(k)).to(torch.bfloat16)
+        c = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+        a_map, b_map, c_map = gemm.maps(a, b, c)
+        fn = lambda: gemm.launch(a_map, b_map, c_map, m, n, k, args.group, status)  # noqa: E731
+        flops = 2.0 * m * n * k
+        name = f"gemm_bf16_{m}x{n}x{k}"
+    else:
+        planes, seq = args.planes, args.seq
+        generator = torch.Generator(device=device).manual_seed(FLASH["seed"])
+        q, kk, v = (torch.randn((planes, seq, 128), generator=generator, device=device).to(torch.bfloat16)
+                    for _ in range(3))
+        out = torch.empty_like(q)
+        lse = torch.empty((planes, seq), dtype=torch.float32, device=device)
+        fn = lambda: check(library().fk_flash_fwd(  # noqa: E731
+            q.data_ptr(), kk.data_ptr(), v.data_ptr(), out.data_ptr(), None, lse.data_ptr(), planes, seq,
+            128 ** -0.5, int(args.causal), stream, status.data_ptr()))
+        flops = 4.0 * planes * seq * seq * 128 * (0.5 if args.causal else 1.0)
+        name = f"flash_fwd_planes{planes}_seq{seq}_{'causal' if args.causal else 'full'}"
+    seconds = time_steps(fn, args.steps, args.warmup, lambda: None)
+    gemm.check_status(status)
+    print(json.dumps({"only": name, "steps": args.steps, "ms_per_step": seconds / args.steps * 1e3,
+                      "tflops": flops * args.steps / seconds / 1e12}), flush=True)
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
+    parser.add_argument("--only", choices=["gemm", "flash"], help="run one kernel alone (for profiling)")
+    parser.add_argument("--m", type=int, default=8192)
+    parser.add_argument("--n", type=int, default=8192)
+    parser.add_argument("--k", type=int, default=8192)
+    parser.add_argument("--planes", type=int, default=32)
+    parser.add_argument("--seq", type=int, default=4096)
+    parser.add_argument("--causal", action="store_true")
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=5)
@@ -367,7 +413,9 @@ def main() -> None:
     rank, local_rank, world = env_int("RANK", 0), env_int("LOCAL_RANK", 0), env_int("WORLD_SIZE", 1)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    if args.impl == "reference":
+    if args.only:
+        run_only(args, local_rank)
+    elif args.impl == "reference":
         run_reference(args, rank, world)
     else:
         run_ours(args, rank, local_rank, world)
