@@ -246,9 +246,12 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     if not worst <= 2 ** -7 * scale:
         raise RuntimeError(f"GEMM disagrees with cuBLASLt: max |diff| {worst} against max |c| {scale}")
 
-    # ---- the timed region: K launches, device-timed, max over ranks
+    # ---- the timed region: K launches, device-timed, max over ranks. cuBLASLt is timed the same way
+    # immediately before and after, so that neither side owns the cooler chip.
     with ClockSampler(local_rank) as sampler:
+        cublaslt_before = max_over_ranks(time_steps(cublaslt_step, args.steps, args.warmup, barrier))
         seconds = max_over_ranks(time_steps(step, args.steps, args.warmup, barrier))
+        cublaslt_after = max_over_ranks(time_steps(cublaslt_step, args.steps, args.warmup, barrier))
     gemm.check_status(status)
     clocks = sampler.summary()
     flops_total = 2.0 * M * N * K
@@ -257,8 +260,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     achieved = 2.0 * M * n_local * K / per_launch_s / 1e12  # this rank's kernel
     long_region = seconds > 2.0
     peak = peaks["sustained"] if long_region else peaks["burst"]
-
-    cublaslt_seconds = max_over_ranks(time_steps(cublaslt_step, args.steps, args.warmup, barrier))
+    cublaslt_seconds = 0.5 * (cublaslt_before + cublaslt_after)
     cublaslt_value = flops_total * args.steps / cublaslt_seconds / 1e12
 
     # ---- flash-attention forward, planes split across ranks
@@ -336,6 +338,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                          "peak_source": f"{peaks['source']} ({'sustained' if long_region else 'burst'} cuBLAS bf16)",
                          "frac_of_nominal_2250": achieved / 2250.0},
             "cublaslt": {"value": cublaslt_value, "unit": "TFLOP/s", "ratio_ours_over_cublaslt": value / cublaslt_value,
+                         "before": flops_total * args.steps / cublaslt_before / 1e12,
+                         "after": flops_total * args.steps / cublaslt_after / 1e12,
                          "max_abs_diff_vs_ours": worst},
             "flash_fwd": {"config": {k: v for k, v in FLASH.items()}, "value": flash_value, "unit": "TFLOP/s",
                           "ms_per_step": flash_seconds / args.steps * 1e3,

@@ -81,14 +81,19 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
                  : "memory");
 }
+// How long one try_wait may keep the thread suspended in hardware (ns). The
+// thread wakes as soon as the phase completes, so a long hint costs no latency;
+// it only keeps waiting roles from spending issue slots on polling.
+constexpr uint32_t kSuspendHintNs = 200000;
+
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
         : "memory");
     return ok != 0;
 }

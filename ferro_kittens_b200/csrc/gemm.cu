@@ -1,21 +1,26 @@
 // bf16 GEMM  C[m, n] = sum_k A[m, k] * B[n, k]  (fp32 accumulate, bf16 out) for
-// sm_100a: a persistent grid of two-CTA clusters, each pair sharing one
-// tcgen05 M256 N256 K16 MMA (cta_group::2) that accumulates in tensor memory.
+// sm_100a: a persistent grid of two-CTA clusters, each pair sharing tcgen05
+// M256 N256 K16 MMAs (cta_group::2) that accumulate in tensor memory.
 //
 // Replaces the reference kernel `gemm_cg2_staged_x8x4` and its launcher
-// (examples/src/gemm.rs:395-419, 477-538). Same operand layouts, same
-// [256, 256] cluster tile, same `grouped` traversal; the structure is new:
+// (examples/src/gemm.rs:395-419, 477-538). Same operand layouts and the same
+// `grouped` traversal; the structure is new:
 //
-//   warp 0      producer: this CTA's [128, 64] halves of A and B per k-block, by TMA,
-//               into a kStages-deep SWIZZLE_128B ring; every load of the pair completes
-//               on the leader CTA's `full` barrier (no multicast: the halves differ).
-//   warp 1      (leader CTA only) MMA issue: 4 chained MMAs per k-block, tcgen05.commit
-//               releases the stage in both CTAs, then hands the accumulator over.
-//   warps 2-5   epilogue: tcgen05.ld -> bf16 -> SWIZZLE_128B staging -> TMA store,
-//               one 32-row band per warp, double-buffered.
+//   item        one [512, 256] block of C per cluster: two vertically adjacent [256, 256] pair
+//               tiles ("halves") that share every B tile, each half accumulating in its own
+//               256 tensor-memory columns. Per k-block a CTA stages two [128, 64] tiles of A
+//               and one [128, 64] tile of B: 48 KiB for 1024 tensor cycles, against 32 KiB for
+//               512 with a single [256, 256] tile -- what keeps the operand feed under the
+//               L2->SM rate without multicast. The last partial wave of a launch is re-cut
+//               into single-half items when that shortens it.
+//   warp 0      producer: this CTA's A and B tiles per k-block, by TMA, into a kStages-deep
+//               SWIZZLE_128B ring; every load of the pair completes on the leader's `full`.
+//   warp 1      (leader CTA only) MMA issue: 4 chained MMAs per half per k-block;
+//               tcgen05.commit releases the stage in both CTAs, then publishes the accumulators.
+//   warps 2-9   epilogue: warps 2-5 drain half 0, warps 6-9 half 1, one 32-row band each:
+//               tcgen05.ld -> bf16 pairs held in registers -> accumulator handed back ->
+//               SWIZZLE_128B staging -> TMA store, overlapping the next item's main loop.
 //
-// Tensor memory holds two [128, 256] fp32 accumulators per CTA (all 512
-// columns), so the epilogue of item i overlaps the main loop of item i+1.
 // Barriers are initialised once per launch and their phases carried across
 // items; roles meet only through them. Every wait is bounded.
 
@@ -26,33 +31,35 @@
 namespace fk {
 namespace gemm {
 
-constexpr uint32_t kBlockM = 128;   // rows of A (and of C) per CTA; the pair covers 256
-constexpr uint32_t kBlockN = 256;   // columns of C per pair; each CTA stages kBlockN/2 rows of B
+constexpr uint32_t kBlockM = 128;   // rows of A (and of C) per CTA per half; the pair covers 256
+constexpr uint32_t kHalves = 2;     // [256, 256] pair tiles per item, stacked along M
+constexpr uint32_t kBlockN = 256;   // columns of C per item; each CTA stages kBlockN/2 rows of B
 constexpr uint32_t kHalfN = kBlockN / 2;
 constexpr uint32_t kBlockK = 64;    // one 128-byte swizzle atom of bf16
-constexpr uint32_t kStages = 6;
-constexpr uint32_t kAccumulators = 2;
-constexpr uint32_t kTmemColumns = kAccumulators * kBlockN;  // 512
-constexpr uint32_t kEpilogueWarps = 4;
+#ifndef FK_GEMM_STAGES
+#define FK_GEMM_STAGES 4
+#endif
+constexpr uint32_t kStages = FK_GEMM_STAGES;
+constexpr uint32_t kTmemColumns = kHalves * kBlockN;  // 512
+constexpr uint32_t kEpilogueWarps = 4 * kHalves;
 constexpr uint32_t kStageColumns = 64;  // columns per epilogue pass: one swizzle atom of bf16
-constexpr uint32_t kStageBuffers = 2;
+constexpr uint32_t kPasses = kBlockN / kStageColumns;
 constexpr uint32_t kThreads = (2 + kEpilogueWarps) * 32;
 constexpr uint32_t kATileBytes = kBlockM * kBlockK * 2;
 constexpr uint32_t kBTileBytes = kHalfN * kBlockK * 2;
 constexpr uint32_t kBandBytes = 32 * kStageColumns * 2;  // one warp's [32, 64] bf16 staging tile
-constexpr uint32_t kPairStageBytes = 2 * (kATileBytes + kBTileBytes);
 
 // The shared plan, one walk for the kernel's offsets and the launch's total.
 struct Plan {
     SharedPlan a_ring, b_ring, bands, full, empty, acc_full, acc_empty, tmem_slot, stop, end;
     constexpr Plan()
-        : a_ring(SharedPlan{}.tile_ring(kBlockM, kBlockK, 2, kStages)),
+        : a_ring(SharedPlan{}.tile_ring(kBlockM, kBlockK, 2, kStages * kHalves)),
           b_ring(a_ring.tile_ring(kHalfN, kBlockK, 2, kStages)),
-          bands(b_ring.tile_ring(32, kStageColumns, 2, kEpilogueWarps * kStageBuffers)),
+          bands(b_ring.tile_ring(32, kStageColumns, 2, kEpilogueWarps)),
           full(bands.semaphores(kStages)),
           empty(full.semaphores(kStages)),
-          acc_full(empty.semaphores(kAccumulators)),
-          acc_empty(acc_full.semaphores(kAccumulators)),
+          acc_full(empty.semaphore()),
+          acc_empty(acc_full.semaphore()),
           tmem_slot(acc_empty.tmem_slot()),
           stop(tmem_slot.word()),
           end(stop) {}
@@ -74,13 +81,49 @@ enum StallCode : uint32_t {
     kStallEpilogue = 0x104,
 };
 
+// What the launch hands every role so that each walks the same item list.
+struct Schedule {
+    uint32_t m;          // rows of C
+    uint32_t tiles_m;    // [512, 256] tile rows: ceil(m / 512)
+    uint32_t tiles_n;    // tile columns: n / 256
+    uint32_t group;      // traversal width of `grouped`
+    uint32_t k_blocks;   // k / 64
+    uint32_t whole;      // leading items that are whole two-half tiles
+    uint32_t items;      // whole + 2 * (tiles - whole): the rest are single halves
+};
+
+struct Item {
+    uint32_t row;     // first row of C the item covers
+    uint32_t column;  // first column
+    uint32_t halves;  // 0 (nothing inside the matrix), 1 or 2
+};
+
+__host__ __device__ __forceinline__ Item item_at(const Schedule& plan, uint32_t index) {
+    uint32_t tile = index, first_half = 0, halves = kHalves;
+    if (index >= plan.whole) {
+        const uint32_t rest = index - plan.whole;
+        tile = plan.whole + rest / kHalves;
+        first_half = rest % kHalves;
+        halves = 1;
+    }
+    const TileCoord at = grouped(tile, plan.tiles_m, plan.tiles_n, plan.group);
+    Item item;
+    item.row = kHalves * 2 * kBlockM * at.row + 2 * kBlockM * first_half;
+    item.column = kBlockN * at.column;
+    item.halves = item.row >= plan.m ? 0u
+                  : (halves == 2 && item.row + 2 * kBlockM >= plan.m) ? 1u
+                                                                       : halves;
+    return item;
+}
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap a_map,
                           const __grid_constant__ CUtensorMap b_map,
-                          const __grid_constant__ CUtensorMap c_map, uint32_t tiles_m,
-                          uint32_t tiles_n, uint32_t group, uint32_t k_blocks, uint32_t* status) {
+                          const __grid_constant__ CUtensorMap c_map, const Schedule plan,
+                          uint32_t* status) {
     extern __shared__ uint8_t dynamic_shared[];
-    const uint32_t base = (smem_u32(dynamic_shared) + kBaseAlign - 1) & ~(kBaseAlign - 1);
+    const uint32_t raw = smem_u32(dynamic_shared);
+    const uint32_t base = (raw + kBaseAlign - 1) & ~(kBaseAlign - 1);
 
     const uint32_t a_ring = base + kPlan.a_ring.at;
     const uint32_t b_ring = base + kPlan.b_ring.at;
@@ -91,26 +134,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     const uint32_t acc_empty = base + kPlan.acc_empty.at;
     const uint32_t slot = base + kPlan.tmem_slot.at;
     const uint32_t stop_addr = base + kPlan.stop.at;
-    volatile uint32_t* stop_flag = reinterpret_cast<volatile uint32_t*>(
-        dynamic_shared + (stop_addr - smem_u32(dynamic_shared)));
-    volatile uint32_t* slot_ptr =
-        reinterpret_cast<volatile uint32_t*>(dynamic_shared + (slot - smem_u32(dynamic_shared)));
+    volatile uint32_t* stop_flag =
+        reinterpret_cast<volatile uint32_t*>(dynamic_shared + (stop_addr - raw));
+    volatile uint32_t* slot_ptr = reinterpret_cast<volatile uint32_t*>(dynamic_shared + (slot - raw));
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const uint32_t peer = rank ^ 1u;
-    const uint32_t items = tiles_m * tiles_n;
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
             mbar_init(full + 8 * s, 1);
             mbar_init(empty + 8 * s, 1);
         }
-        for (uint32_t a = 0; a < kAccumulators; ++a) {
-            mbar_init(acc_full + 8 * a, 1);
-            mbar_init(acc_empty + 8 * a, 2 * kEpilogueWarps);
-        }
+        mbar_init(acc_full, 1);
+        mbar_init(acc_empty, 2 * kEpilogueWarps);
         *stop_flag = 0;
         fence_mbarrier_init();
         prefetch_tensormap(&a_map);
@@ -132,23 +171,30 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         if (lane == 0) {
             uint32_t fill = 0;
             bool live = true;
-            for (uint32_t item = cluster_id_x(); live && item < items; item += cluster_count_x()) {
-                const TileCoord tile = grouped(item, tiles_m, tiles_n, group);
-                const int a_row = static_cast<int>(2 * kBlockM * tile.row + kBlockM * rank);
-                const int b_row = static_cast<int>(kBlockN * tile.column + kHalfN * rank);
-                for (uint32_t k = 0; k < k_blocks; ++k, ++fill) {
+            for (uint32_t index = cluster_id_x(); live && index < plan.items;
+                 index += cluster_count_x()) {
+                const Item item = item_at(plan, index);
+                if (item.halves == 0) continue;
+                const int a_row = static_cast<int>(item.row + kBlockM * rank);
+                const int b_row = static_cast<int>(item.column + kHalfN * rank);
+                // Both CTAs' boxes land on the leader's barrier.
+                const uint32_t pair_bytes = 2 * (item.halves * kATileBytes + kBTileBytes);
+                for (uint32_t k = 0; k < plan.k_blocks; ++k, ++fill) {
                     const uint32_t s = fill % kStages;
                     const uint32_t parity = (fill / kStages) & 1u;
                     if (!mbar_wait(empty + 8 * s, parity ^ 1u, site, kStallProducer, fill)) {
                         live = false;
                         break;
                     }
-                    // The leader's barrier collects all four boxes of the pair's stage.
                     const uint32_t arrive_at = mapa(full + 8 * s, 0);
-                    if (rank == 0) mbar_arrive_expect_tx(full + 8 * s, kPairStageBytes);
+                    if (rank == 0) mbar_arrive_expect_tx(full + 8 * s, pair_bytes);
                     const int column = static_cast<int>(kBlockK * k);
-                    tma_load_2d_pair(a_ring + s * kATileBytes, &a_map, column, a_row, arrive_at);
+                    tma_load_2d_pair(a_ring + (s * kHalves) * kATileBytes, &a_map, column, a_row,
+                                     arrive_at);
                     tma_load_2d_pair(b_ring + s * kBTileBytes, &b_map, column, b_row, arrive_at);
+                    if (item.halves == 2)
+                        tma_load_2d_pair(a_ring + (s * kHalves + 1) * kATileBytes, &a_map, column,
+                                         a_row + static_cast<int>(2 * kBlockM), arrive_at);
                 }
             }
         }
@@ -158,18 +204,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             constexpr uint32_t idesc = instruction_descriptor(2 * kBlockM, kBlockN, false, false);
             uint32_t drain = 0, count = 0;
             bool live = true;
-            for (uint32_t item = cluster_id_x(); live && item < items;
-                 item += cluster_count_x(), ++count) {
-                const uint32_t acc = count % kAccumulators;
-                const uint32_t acc_parity = (count / kAccumulators) & 1u;
-                if (!mbar_wait(acc_empty + 8 * acc, acc_parity ^ 1u, site, kStallMmaAccumulator,
-                               count)) {
+            for (uint32_t index = cluster_id_x(); live && index < plan.items;
+                 index += cluster_count_x()) {
+                const Item item = item_at(plan, index);
+                if (item.halves == 0) continue;
+                // The previous item's accumulators must have been read out.
+                if (!mbar_wait(acc_empty, (count & 1u) ^ 1u, site, kStallMmaAccumulator, count)) {
                     live = false;
                     break;
                 }
                 tc_fence_after_sync();
-                const uint32_t d_tmem = tmem + acc * kBlockN;
-                for (uint32_t k = 0; k < k_blocks; ++k, ++drain) {
+                for (uint32_t k = 0; k < plan.k_blocks; ++k, ++drain) {
                     const uint32_t s = drain % kStages;
                     const uint32_t parity = (drain / kStages) & 1u;
                     if (!mbar_wait(full + 8 * s, parity, site, kStallMmaFull, drain)) {
@@ -177,85 +222,100 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                         break;
                     }
                     tc_fence_after_sync();
-                    const uint64_t a_desc =
-                        operand_descriptor(a_ring + s * kATileBytes, kKMajorLeadingBytes);
+                    const uint64_t a0_desc = operand_descriptor(
+                        a_ring + (s * kHalves) * kATileBytes, kKMajorLeadingBytes);
+                    const uint64_t a1_desc = operand_descriptor(
+                        a_ring + (s * kHalves + 1) * kATileBytes, kKMajorLeadingBytes);
                     const uint64_t b_desc =
                         operand_descriptor(b_ring + s * kBTileBytes, kKMajorLeadingBytes);
+                    const uint32_t accumulate = k != 0;
+                    if (item.halves == 2) {
 #pragma unroll
-                    for (uint32_t chunk = 0; chunk < kBlockK / 16; ++chunk) {
-                        // Advancing the 14-bit address field by 32 B per K=16 chunk.
-                        const uint64_t step = (chunk * kKMajorChunkBytes) >> 4;
-                        mma_ss<2>(d_tmem, a_desc + step, b_desc + step, idesc, (k | chunk) != 0);
+                        for (uint32_t chunk = 0; chunk < kBlockK / 16; ++chunk) {
+                            // Advancing the 14-bit address field by 32 B per K=16 chunk.
+                            const uint64_t step = (chunk * kKMajorChunkBytes) >> 4;
+                            mma_ss<2>(tmem, a0_desc + step, b_desc + step, idesc, accumulate | chunk);
+                            mma_ss<2>(tmem + kBlockN, a1_desc + step, b_desc + step, idesc,
+                                      accumulate | chunk);
+                        }
+                    } else {
+#pragma unroll
+                        for (uint32_t chunk = 0; chunk < kBlockK / 16; ++chunk) {
+                            const uint64_t step = (chunk * kKMajorChunkBytes) >> 4;
+                            mma_ss<2>(tmem, a0_desc + step, b_desc + step, idesc, accumulate | chunk);
+                        }
                     }
                     // The MMA's own retirement frees the stage, in both CTAs.
                     mma_commit<2>(empty + 8 * s);
                     mma_commit<2>(mapa(empty + 8 * s, 1));
                 }
                 if (!live) break;
-                mma_commit<2>(acc_full + 8 * acc);
-                mma_commit<2>(mapa(acc_full + 8 * acc, 1));
+                mma_commit<2>(acc_full);
+                mma_commit<2>(mapa(acc_full, 1));
+                ++count;
             }
         }
     } else {
         // ------------------------------------------------ epilogue (both CTAs)
-        const uint32_t quadrant = warp & 3u;  // the tensor-memory lanes this warp may read
-        const uint32_t my_bands = bands + (warp - 2) * kStageBuffers * kBandBytes;
-        const uint32_t row_in_band = lane;
-        uint32_t count = 0, pass = 0;
+        const uint32_t half = (warp - 2) >> 2;  // which accumulator this warp drains
+        const uint32_t quadrant = warp & 3u;    // the tensor-memory lanes this warp may read
+        const uint32_t band = bands + (warp - 2) * kBandBytes;
+        const uint32_t t_row = tmem_address(tmem, 32 * quadrant, half * kBlockN);
+        uint32_t count = 0;
         bool live = true;
-        for (uint32_t item = cluster_id_x(); live && item < items;
-             item += cluster_count_x(), ++count) {
-            const TileCoord tile = grouped(item, tiles_m, tiles_n, group);
-            const uint32_t acc = count % kAccumulators;
-            const uint32_t acc_parity = (count / kAccumulators) & 1u;
-            if (!mbar_wait(acc_full + 8 * acc, acc_parity, site, kStallEpilogue, count)) {
+        for (uint32_t index = cluster_id_x(); live && index < plan.items;
+             index += cluster_count_x()) {
+            const Item item = item_at(plan, index);
+            if (item.halves == 0) continue;
+            if (!mbar_wait(acc_full, count & 1u, site, kStallEpilogue, count)) {
                 live = false;
                 break;
             }
+            ++count;
             tc_fence_after_sync();
+            const bool mine = half < item.halves;
+            // Read this warp's [32, 256] band out as bf16 pairs, then release the accumulator:
+            // the stores below overlap the next item's main loop.
+            uint32_t held[kPasses][32];
+            if (mine) {
+#pragma unroll
+                for (uint32_t pass = 0; pass < kPasses; ++pass) {
+                    uint32_t lo[32], hi[32];
+                    tmem_ld_32x32(t_row + pass * kStageColumns, lo);
+                    tmem_ld_32x32(t_row + pass * kStageColumns + 32, hi);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (uint32_t i = 0; i < 16; ++i) {
+                        held[pass][i] =
+                            pack_bf16x2(__uint_as_float(lo[2 * i]), __uint_as_float(lo[2 * i + 1]));
+                        held[pass][16 + i] =
+                            pack_bf16x2(__uint_as_float(hi[2 * i]), __uint_as_float(hi[2 * i + 1]));
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa(acc_empty, 0));
+            if (!mine) continue;
+
             const int c_row =
-                static_cast<int>(2 * kBlockM * tile.row + kBlockM * rank + 32 * quadrant);
-            const int c_column = static_cast<int>(kBlockN * tile.column);
-            const uint32_t t_row = tmem_address(tmem, 32 * quadrant, acc * kBlockN);
-#pragma unroll 1
-            for (uint32_t at = 0; at < kBlockN; at += kStageColumns, ++pass) {
-                const uint32_t band = my_bands + (pass % kStageBuffers) * kBandBytes;
-                // The store that last read this buffer must be done reading it.
-                if (lane == 0) tma_store_wait_read<kStageBuffers - 1>();
+                static_cast<int>(item.row + 2 * kBlockM * half + kBlockM * rank + 32 * quadrant);
+#pragma unroll
+            for (uint32_t pass = 0; pass < kPasses; ++pass) {
+                // The store that last read this warp's staging tile must be done reading it.
+                if (lane == 0) tma_store_wait_read<0>();
                 __syncwarp();
-                uint32_t lo[32], hi[32];
-                tmem_ld_32x32(t_row + at, lo);
-                tmem_ld_32x32(t_row + at + 32, hi);
-                tmem_wait_ld();
-                if (at + kStageColumns == kBlockN) {
-                    // Last read of this accumulator: hand it back to the MMA warp.
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(mapa(acc_empty + 8 * acc, 0));
-                }
 #pragma unroll
-                for (uint32_t chunk = 0; chunk < 4; ++chunk) {
-                    const uint32_t* v = lo + 8 * chunk;
-                    st_shared_v4(band + swizzled_chunk_offset(row_in_band, chunk, 0),
-                                 pack_bf16x2(__uint_as_float(v[0]), __uint_as_float(v[1])),
-                                 pack_bf16x2(__uint_as_float(v[2]), __uint_as_float(v[3])),
-                                 pack_bf16x2(__uint_as_float(v[4]), __uint_as_float(v[5])),
-                                 pack_bf16x2(__uint_as_float(v[6]), __uint_as_float(v[7])));
-                }
-#pragma unroll
-                for (uint32_t chunk = 0; chunk < 4; ++chunk) {
-                    const uint32_t* v = hi + 8 * chunk;
-                    st_shared_v4(band + swizzled_chunk_offset(row_in_band, 4 + chunk, 0),
-                                 pack_bf16x2(__uint_as_float(v[0]), __uint_as_float(v[1])),
-                                 pack_bf16x2(__uint_as_float(v[2]), __uint_as_float(v[3])),
-                                 pack_bf16x2(__uint_as_float(v[4]), __uint_as_float(v[5])),
-                                 pack_bf16x2(__uint_as_float(v[6]), __uint_as_float(v[7])));
-                }
+                for (uint32_t chunk = 0; chunk < 8; ++chunk)
+                    st_shared_v4(band + swizzled_chunk_offset(lane, chunk, 0), held[pass][4 * chunk],
+                                 held[pass][4 * chunk + 1], held[pass][4 * chunk + 2],
+                                 held[pass][4 * chunk + 3]);
                 // Every writer publishes to the async proxy, then one lane stores.
                 fence_proxy_async_shared();
                 __syncwarp();
                 if (lane == 0) {
-                    tma_store_2d(&c_map, band, c_column + static_cast<int>(at), c_row);
+                    tma_store_2d(&c_map, band,
+                                 static_cast<int>(item.column + pass * kStageColumns), c_row);
                     tma_store_commit();
                 }
             }
@@ -275,6 +335,24 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     if (warp == 1) tmem_dealloc<2>(tmem, kTmemColumns);
 }
 
+// The item list of a launch over `clusters` resident clusters: whole [512, 256]
+// tiles, with the last partial wave re-cut into single halves when it holds at
+// most half a wave of tiles (two short half-waves then beat one long one).
+static Schedule schedule(uint32_t m, uint32_t n, uint32_t k, uint32_t group, uint32_t clusters) {
+    Schedule plan;
+    plan.m = m;
+    plan.tiles_m = (m + kHalves * 2 * kBlockM - 1) / (kHalves * 2 * kBlockM);
+    plan.tiles_n = n / kBlockN;
+    plan.group = group;
+    plan.k_blocks = k / kBlockK;
+    const uint32_t tiles = plan.tiles_m * plan.tiles_n;
+    const uint32_t tail = tiles % clusters;
+    const bool recut = tail != 0 && 2 * tail <= clusters;
+    plan.whole = recut ? tiles - tail : tiles;
+    plan.items = plan.whole + kHalves * (tiles - plan.whole);
+    return plan;
+}
+
 }  // namespace gemm
 }  // namespace fk
 
@@ -286,9 +364,10 @@ extern "C" uint32_t fk_gemm_shared_bytes(void) { return gemm::kSharedBytes; }
 extern "C" uint32_t fk_gemm_threads(void) { return gemm::kThreads; }
 
 extern "C" uint32_t fk_gemm_grid(uint32_t m, uint32_t n, uint32_t sm_count) {
-    const uint32_t tiles = (m / (2 * gemm::kBlockM)) * (n / gemm::kBlockN);
     const uint32_t clusters = sm_count / 2;
-    return 2 * (tiles < clusters ? tiles : clusters);
+    if (clusters == 0) return 0;
+    const gemm::Schedule plan = gemm::schedule(m, n, gemm::kBlockK, 1, clusters);
+    return 2 * (plan.items < clusters ? plan.items : clusters);
 }
 
 extern "C" int fk_gemm_bf16_launch(const void* a_map, const void* b_map, const void* c_map,
@@ -310,12 +389,13 @@ extern "C" int fk_gemm_bf16_launch(const void* a_map, const void* b_map, const v
         reinterpret_cast<const void*>(gemm::gemm_bf16_pair_kernel), gemm::kSharedBytes, &limit);
     if (admitted != FK_OK) return admitted;
 
-    const uint32_t grid = fk_gemm_grid(m, n, static_cast<uint32_t>(sm_count));
+    const uint32_t clusters = static_cast<uint32_t>(sm_count) / 2;
+    const gemm::Schedule plan = gemm::schedule(m, n, k, group, clusters);
+    const uint32_t grid = 2 * (plan.items < clusters ? plan.items : clusters);
     gemm::gemm_bf16_pair_kernel<<<grid, gemm::kThreads, gemm::kSharedBytes,
                                   static_cast<cudaStream_t>(stream)>>>(
         *static_cast<const CUtensorMap*>(a_map), *static_cast<const CUtensorMap*>(b_map),
-        *static_cast<const CUtensorMap*>(c_map), m / (2 * gemm::kBlockM), n / gemm::kBlockN, group,
-        k / gemm::kBlockK, device_status);
+        *static_cast<const CUtensorMap*>(c_map), plan, device_status);
     FK_CUDA(cudaGetLastError());
     return FK_OK;
 }

@@ -187,13 +187,13 @@ def test_this_librarys_own_plans_fit_one_cta_per_sm():
     lib = library()
     for total in (lib.fk_gemm_shared_bytes(), lib.fk_flash_shared_bytes()):
         assert 116_736 < total <= 232_448  # admits exactly one CTA per SM
-    assert lib.fk_gemm_threads() == 192 and lib.fk_flash_threads() == 320
-    # gemm: 6 stages of two [128, 64] tiles, 8 staging bands, 16 barriers, slot, stop word, base pad.
+    assert lib.fk_gemm_threads() == 320 and lib.fk_flash_threads() == 320
+    # gemm: 4 stages of two A tiles and one B tile, 8 staging bands, 10 barriers, slot, stop word, base pad.
     plan = SharedPlan.sizing()
-    plan.tile_ring(128, 64, 6)
-    plan.tile_ring(128, 64, 6)
+    plan.tile_ring(128, 64, 8)
+    plan.tile_ring(128, 64, 4)
     plan.tile_ring(32, 64, 8)
-    for count in (6, 6, 2, 2):
+    for count in (4, 4, 1, 1):
         plan.semaphores(count)
     plan.tmem_slot()
     plan.reserve(4, 4)
@@ -202,10 +202,11 @@ def test_this_librarys_own_plans_fit_one_cta_per_sm():
 
 def test_grid_is_whole_clusters_capped_at_one_per_sm_pair():
     lib = library()
-    assert lib.fk_gemm_grid(512, 256, 148) == 4
+    assert lib.fk_gemm_grid(512, 256, 148) == 4      # one [512, 256] tile, re-cut into two halves
     assert lib.fk_gemm_grid(4096, 4096, 148) == 148
     assert lib.fk_gemm_grid(16384, 16384, 148) == 148
-    assert lib.fk_gemm_grid(256, 256, 148) == 2
+    assert lib.fk_gemm_grid(1024, 512, 148) == 16    # 4 tiles = a short tail: 8 single-half items
+    assert lib.fk_gemm_grid(16384, 2048, 148) == 148
 
 
 # ---------------------------------------------------------------- layouts
