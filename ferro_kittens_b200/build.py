@@ -42,14 +42,20 @@ def _stale(target: Path, inputs: list[Path]) -> bool:
     return any(path.stat().st_mtime > built for path in inputs)
 
 
-def build_library(force: bool = False, verbose: bool = False) -> Path:
-    """Compile ``csrc/*.cu`` into ``libferro_kittens_b200.so`` if out of date."""
+def build_library(force: bool = False, verbose: bool = False, defines: tuple[str, ...] = (),
+                  output: Path | None = None) -> Path:
+    """Compile ``csrc/*.cu`` into ``libferro_kittens_b200.so`` if out of date.
+
+    ``defines`` (``NAME=value`` strings) and ``output`` build a tuning variant beside the default.
+    """
+    target = Path(output) if output else LIBRARY
     sources = [CSRC / name for name in SOURCES if (CSRC / name).exists()]
     inputs = sources + list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh")) + [
         PACKAGE.parent / "include" / "ferro_kittens.h"]
-    if not force and not _stale(LIBRARY, inputs):
-        return LIBRARY
-    command = [_nvcc(), *NVCC_FLAGS, "-shared", "-o", str(LIBRARY), *map(str, sources)]
+    if not force and not _stale(target, inputs):
+        return target
+    command = [_nvcc(), *NVCC_FLAGS, *[f"-D{item}" for item in defines], "-shared", "-o", str(target),
+               *map(str, sources)]
     if verbose:
         command.insert(1, "-Xptxas=-v")
     result = subprocess.run(command, capture_output=True, text=True)
@@ -57,7 +63,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
         raise RuntimeError("nvcc failed:\n" + result.stdout + result.stderr)
     if verbose:
         sys.stderr.write(result.stderr)
-    return LIBRARY
+    return target
 
 
 def build_cublaslt(force: bool = False) -> Path:

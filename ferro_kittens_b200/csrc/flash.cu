@@ -47,13 +47,21 @@ constexpr uint32_t kScoreColumn = 0;     // S_t at kScoreColumn + 128 t
 constexpr uint32_t kOutputColumn = 256;  // O_t at kOutputColumn + 128 t
 // The running max is refreshed only when the block max exceeds it by this much (log2 domain).
 constexpr float kRescaleThreshold = 8.0f;
+// Of the 16 pairs of scores in a 32-column chunk, the pairs whose bit is set here take their
+// 2^x from a polynomial on the FMA pipe instead of the ex2 unit: at D = 128 a score tile costs
+// as many ex2-unit cycles as tensor cycles, so part of the exponentials has to move.
+#ifndef FK_FLASH_POLY_MASK
+#define FK_FLASH_POLY_MASK 0x5555u
+#endif
+constexpr uint32_t kPolyMask = FK_FLASH_POLY_MASK;
 
 struct Plan {
-    SharedPlan q, kv, q_full, kv_full, kv_empty, s_full, p_ready, o_done, tmem_slot, stop, end;
+    SharedPlan q, kv, swap, q_full, kv_full, kv_empty, s_full, p_ready, o_done, tmem_slot, stop, end;
     constexpr Plan()
         : q(SharedPlan{}.tile_ring(kTileRows, kHead, 2, kTiles)),
           kv(q.tile_ring(kBlockKeys, kHead, 2, kSlots)),
-          q_full(kv.semaphore()),
+          swap(kv.reserve(2 * 2 * kTileRows * 4, 16)),  // half-row maxima / sums, two buffers
+          q_full(swap.semaphore()),
           kv_full(q_full.semaphores(kSlots)),
           kv_empty(kv_full.semaphores(kSlots)),
           s_full(kv_empty.semaphores(kTiles)),
@@ -64,8 +72,10 @@ struct Plan {
           end(stop) {}
 };
 constexpr Plan kPlan{};
+// Swizzled tiles need a 1024-byte-aligned base: the dynamic shared array is declared so, and
+// the kernel refuses to run (status kMisaligned) should the base ever come back otherwise.
 constexpr uint32_t kBaseAlign = 1024;
-constexpr uint32_t kSharedBytes = static_cast<uint32_t>(kPlan.end.bytes()) + kBaseAlign;
+constexpr uint32_t kSharedBytes = static_cast<uint32_t>(kPlan.end.bytes());
 static_assert(kSharedBytes <= 232448, "plan exceeds the opt-in shared memory of an sm_100 CTA");
 
 enum StallCode : uint32_t {
@@ -75,6 +85,7 @@ enum StallCode : uint32_t {
     kStallMmaP = 0x204,
     kStallSoftmaxS = 0x205,
     kStallSoftmaxO = 0x206,
+    kMisaligned = 0x2ff,
 };
 
 struct Extent {
@@ -94,6 +105,31 @@ __device__ __forceinline__ Extent extent(uint32_t q_row0, uint32_t seq, bool cau
     return e;
 }
 
+// 2^x for a pair, on the FMA pipe: clamp, split x = n + f with f in [-0.5, 0.5] by the
+// 1.5 * 2^23 shift trick, a degree-3 minimax polynomial for 2^f (maximum relative error
+// 7.5e-5, far inside P's rounding to bf16), then n added into the exponent field. The same
+// split the reference's `exp2_approx` makes (src/reg.rs:81-93), on packed fp32 pairs.
+__device__ __forceinline__ float2 exp2_pair_fma(float2 x) {
+    constexpr float kShift = 12582912.0f;  // 1.5 * 2^23
+    x.x = fmaxf(x.x, -125.0f);
+    x.y = fmaxf(x.y, -125.0f);
+    const float2 shifted = __fadd2_rn(x, make_float2(kShift, kShift));
+    const float2 whole = __fadd2_rn(shifted, make_float2(-kShift, -kShift));
+    const float2 f = __ffma2_rn(whole, make_float2(-1.0f, -1.0f), x);
+    float2 p = __ffma2_rn(f, make_float2(0.05517166f, 0.05517166f), make_float2(0.24261113f, 0.24261113f));
+    p = __ffma2_rn(p, f, make_float2(0.69326097f, 0.69326097f));
+    p = __ffma2_rn(p, f, make_float2(0.99992806f, 0.99992806f));
+    p.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(shifted.x) << 23));
+    p.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(shifted.y) << 23));
+    return p;
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
     flash_forward_kernel(const __grid_constant__ CUtensorMap q_map,
                          const __grid_constant__ CUtensorMap k_map,
@@ -101,9 +137,13 @@ __global__ void __launch_bounds__(kThreads, 1)
                          const __grid_constant__ CUtensorMap o_map, float* __restrict__ o_f32,
                          float* __restrict__ lse, uint32_t seq, float scale, uint32_t causal,
                          uint32_t* status) {
-    extern __shared__ uint8_t dynamic_shared[];
+    extern __shared__ __align__(1024) uint8_t dynamic_shared[];
     const uint32_t raw = smem_u32(dynamic_shared);
-    const uint32_t base = (raw + kBaseAlign - 1) & ~(kBaseAlign - 1);
+    const uint32_t base = raw;
+    if (raw & (kBaseAlign - 1)) {
+        if (threadIdx.x == 0 && status) atomicCAS(status, 0u, static_cast<uint32_t>(kMisaligned));
+        return;
+    }
 
     const uint32_t q_tiles = base + kPlan.q.at;
     const uint32_t kv_ring = base + kPlan.kv.at;
@@ -134,7 +174,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         for (uint32_t t = 0; t < kTiles; ++t) {
             mbar_init(s_full + 8 * t, 1);
-            mbar_init(p_ready + 8 * t, 4);
+            mbar_init(p_ready + 8 * t, kSoftmaxWarps);
             mbar_init(o_done + 8 * t, 1);
         }
         *stop_flag = 0;
@@ -154,6 +194,15 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t tmem = *slot_ptr;
 
     const StallSite site{status, stop_flag, 0};
+#ifdef FK_FLASH_TRACE
+    // Development build: clock stamps of the first blocks of CTA (0, 0), after the status words.
+    auto trace = [&](uint32_t role, uint32_t block, uint32_t point) {
+        if (blockIdx.x == 0 && blockIdx.y == 0 && block < 24 && lane == 0)
+            reinterpret_cast<long long*>(status + 4)[(role * 24 + block) * 6 + point] = clock64();
+    };
+#else
+    auto trace = [](uint32_t, uint32_t, uint32_t) {};
+#endif
 
     if (warp == kLoaderWarp) {
         // ------------------------------------------------ loader
@@ -240,6 +289,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                             break;
                         }
                         tc_fence_after_sync();
+                        trace(2, j, 2 * t);
                         output(t, v_slot, j != 0);
                     }
                     if (j + 1 < keys.blocks[t]) {
@@ -252,8 +302,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                             tc_fence_after_sync();
                             next_loaded = true;
                         }
+                        trace(2, j, 4 + t);
                         scores(t, k_slot);
                     }
+                    trace(2, j, 2 * t + 1);
                 }
                 if (!live) break;
                 mma_commit<1>(kv_empty + 8 * v_slot);
@@ -262,118 +314,169 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
     } else {
         // ------------------------------------------------ softmax, correction, epilogue
-        const uint32_t t = warp >> 2;            // query tile of this warpgroup
+        // All eight warps work on one query tile at a time, alternating tiles: warps 0-3 own
+        // key columns 0-63 of a score block and warps 4-7 columns 64-127, so the two warps
+        // that share a scheduler (and its ex2 unit) overlap one's exponentials with the
+        // other's FMA-pipe work. Two sibling warps own the same 32 rows and swap half-row
+        // maxima through shared memory under a 64-thread named barrier.
+        const uint32_t half = warp >> 2;         // which 64 key columns / 64 head columns
         const uint32_t quadrant = warp & 3u;     // tensor-memory lanes this warp may touch
         const uint32_t row = 32 * quadrant + lane;  // row of the tile this thread owns
-        const uint32_t blocks = keys.blocks[t];
         const uint32_t lane_base = (32 * quadrant) << 16;
-        const uint32_t s_tmem = tmem + lane_base + kScoreColumn + kBlockKeys * t;
-        const uint32_t o_tmem = tmem + lane_base + kOutputColumn + kHead * t;
         const float scale_log2 = scale * 1.4426950408889634f;
+        float* const swap = reinterpret_cast<float*>(dynamic_shared + (base + kPlan.swap.at - raw));
+        const auto sibling_sync = [&]() {
+            asm volatile("bar.sync %0, 64;" ::"r"(1u + quadrant) : "memory");
+        };
 
-        float row_max = -INFINITY;  // raw score units
-        float row_sum = 0.0f;
-        bool live = blocks != 0;
+        float row_max[kTiles] = {-INFINITY, -INFINITY};  // raw score units, same in both siblings
+        float row_sum[kTiles] = {0.0f, 0.0f};            // this thread's half of the row only
+        uint32_t step = 0;
+        bool live = true;
 
-        for (uint32_t j = 0; live && j < blocks; ++j) {
-            if (!mbar_wait(s_full + 8 * t, j & 1u, site, kStallSoftmaxS, j)) {
-                live = false;
-                break;
-            }
-            tc_fence_after_sync();
-            uint32_t raw_s[4][32];
+        for (uint32_t j = 0; live && j < keys.most; ++j) {
 #pragma unroll
-            for (uint32_t c = 0; c < 4; ++c) tmem_ld_32x32(s_tmem + 32 * c, raw_s[c]);
-            tmem_wait_ld();
+            for (uint32_t t = 0; t < kTiles; ++t) {
+                if (!live || j >= keys.blocks[t]) continue;
+                const uint32_t s_tmem = tmem + lane_base + kScoreColumn + kBlockKeys * t;
+                const uint32_t o_tmem = tmem + lane_base + kOutputColumn + kHead * t + 64 * half;
+                if (!mbar_wait(s_full + 8 * t, j & 1u, site, kStallSoftmaxS, j)) {
+                    live = false;
+                    continue;
+                }
+                tc_fence_after_sync();
+                if (warp == 0) trace(t, j, 0);
+                uint32_t raw_s[2][32];
+                tmem_ld_32x32(s_tmem + 64 * half, raw_s[0]);
+                tmem_ld_32x32(s_tmem + 64 * half + 32, raw_s[1]);
+                tmem_wait_ld();
+                if (warp == 0) trace(t, j, 1);
 
-            if (causal && j + 1 == blocks) {
-                // Diagonal block: key (128 j + c) is visible to query (tile start + row) iff c <= row.
+                if (causal && j + 1 == keys.blocks[t]) {
+                    // Diagonal block: key (128 j + c) is visible to query (tile start + row) iff c <= row.
 #pragma unroll
-                for (uint32_t c = 0; c < 4; ++c)
-#pragma unroll
-                    for (uint32_t i = 0; i < 32; ++i)
-                        if (32 * c + i > row) raw_s[c][i] = 0xff800000u;  // -inf
-            }
-
-            float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
-#pragma unroll
-            for (uint32_t i = 0; i < 32; ++i) {
-                m0 = fmaxf(m0, __uint_as_float(raw_s[0][i]));
-                m1 = fmaxf(m1, __uint_as_float(raw_s[1][i]));
-                m2 = fmaxf(m2, __uint_as_float(raw_s[2][i]));
-                m3 = fmaxf(m3, __uint_as_float(raw_s[3][i]));
-            }
-            const float block_max = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-            const float new_max = fmaxf(row_max, block_max);
-            const bool moved = (new_max - row_max) * scale_log2 > kRescaleThreshold;
-            if (__any_sync(0xffffffffu, moved)) {
-                // Refresh this warp's maxima; rows whose max did not move scale by 1.
-                const float factor = ex2_approx((row_max - new_max) * scale_log2);
-                if (j > 0) {
-                    if (!mbar_wait(o_done + 8 * t, (j - 1) & 1u, site, kStallSoftmaxO, j)) {
-                        live = false;
-                        break;
-                    }
-                    tc_fence_after_sync();
-#pragma unroll 1
-                    for (uint32_t c = 0; c < 4; ++c) {
-                        uint32_t o[32];
-                        tmem_ld_32x32(o_tmem + 32 * c, o);
-                        tmem_wait_ld();
+                    for (uint32_t c = 0; c < 2; ++c)
 #pragma unroll
                         for (uint32_t i = 0; i < 32; ++i)
-                            o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
-                        tmem_st_32x32(o_tmem + 32 * c, o);
-                    }
-                    tmem_wait_st();
+                            if (64 * half + 32 * c + i > row) raw_s[c][i] = 0xff800000u;  // -inf
                 }
-                row_sum *= factor;
-                row_max = new_max;
-            }
 
-            const float shift = row_max * scale_log2;
-            float s0 = 0.0f, s1 = 0.0f;
+                float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-            for (uint32_t c = 0; c < 4; ++c) {
-                // 32 keys -> 16 packed bf16 pairs, written over the S columns already read.
-                uint32_t packed[16];
-#pragma unroll
-                for (uint32_t i = 0; i < 16; ++i) {
-                    const float p0 =
-                        ex2_approx(fmaf(__uint_as_float(raw_s[c][2 * i]), scale_log2, -shift));
-                    const float p1 =
-                        ex2_approx(fmaf(__uint_as_float(raw_s[c][2 * i + 1]), scale_log2, -shift));
-                    s0 += p0;
-                    s1 += p1;
-                    packed[i] = pack_bf16x2(p0, p1);
+                for (uint32_t i = 0; i < 8; ++i) {
+                    m0 = max3(m0, __uint_as_float(raw_s[0][4 * i]), __uint_as_float(raw_s[0][4 * i + 1]));
+                    m1 = max3(m1, __uint_as_float(raw_s[0][4 * i + 2]), __uint_as_float(raw_s[0][4 * i + 3]));
+                    m2 = max3(m2, __uint_as_float(raw_s[1][4 * i]), __uint_as_float(raw_s[1][4 * i + 1]));
+                    m3 = max3(m3, __uint_as_float(raw_s[1][4 * i + 2]), __uint_as_float(raw_s[1][4 * i + 3]));
                 }
-                tmem_st_32x16(s_tmem + 16 * c, packed);
+                // Swap half-row maxima with the sibling warp. Two buffers by step parity: a warp
+                // cannot be two steps ahead of its sibling, which every step's barrier holds.
+                float* const mine = swap + ((step & 1u) * 2 + half) * kTileRows + row;
+                float* const theirs = swap + ((step & 1u) * 2 + (half ^ 1u)) * kTileRows + row;
+                ++step;
+                *mine = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+                sibling_sync();
+                const float block_max = fmaxf(*mine, *theirs);
+                const float new_max = fmaxf(row_max[t], block_max);
+                const bool moved = (new_max - row_max[t]) * scale_log2 > kRescaleThreshold;
+                if (__any_sync(0xffffffffu, moved)) {
+                    // Refresh this warp's maxima; rows whose max did not move scale by 1. Both
+                    // siblings hold the same rows and the same maxima, so both take this branch.
+                    const float factor = ex2_approx((row_max[t] - new_max) * scale_log2);
+                    if (j > 0) {
+                        if (!mbar_wait(o_done + 8 * t, (j - 1) & 1u, site, kStallSoftmaxO, j)) {
+                            live = false;
+                            continue;
+                        }
+                        tc_fence_after_sync();
+#pragma unroll 1
+                        for (uint32_t c = 0; c < 2; ++c) {
+                            uint32_t o[32];
+                            tmem_ld_32x32(o_tmem + 32 * c, o);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (uint32_t i = 0; i < 32; ++i)
+                                o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+                            tmem_st_32x32(o_tmem + 32 * c, o);
+                        }
+                        tmem_wait_st();
+                    }
+                    row_sum[t] *= factor;
+                    row_max[t] = new_max;
+                }
+                if (warp == 0) trace(t, j, 2);
+
+                const float shift = row_max[t] * scale_log2;
+                const float2 scale2 = make_float2(scale_log2, scale_log2);
+                const float2 shift2 = make_float2(-shift, -shift);
+                float2 sum_a = make_float2(0.0f, 0.0f), sum_b = make_float2(0.0f, 0.0f);
+#pragma unroll
+                for (uint32_t c = 0; c < 2; ++c) {
+                    // 32 keys -> 16 packed bf16 pairs, written over S columns both siblings have read.
+                    uint32_t packed[16];
+#pragma unroll
+                    for (uint32_t i = 0; i < 16; ++i) {
+                        const float2 x = __ffma2_rn(make_float2(__uint_as_float(raw_s[c][2 * i]),
+                                                                __uint_as_float(raw_s[c][2 * i + 1])),
+                                                    scale2, shift2);
+                        float2 p;
+                        if ((kPolyMask >> i) & 1u) {
+                            p = exp2_pair_fma(x);
+                        } else {
+                            p.x = ex2_approx(x.x);
+                            p.y = ex2_approx(x.y);
+                        }
+                        if (i & 1u)
+                            sum_b = __fadd2_rn(sum_b, p);
+                        else
+                            sum_a = __fadd2_rn(sum_a, p);
+                        packed[i] = pack_bf16x2(p.x, p.y);
+                    }
+                    tmem_st_32x16(s_tmem + 32 * half + 16 * c, packed);
+                }
+                row_sum[t] += (sum_a.x + sum_b.x) + (sum_a.y + sum_b.y);
+                if (warp == 0) trace(t, j, 3);
+                tmem_wait_st();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_ready + 8 * t);
+                if (warp == 0) trace(t, j, 4);
             }
-            row_sum += s0 + s1;
-            tmem_wait_st();
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(p_ready + 8 * t);
         }
 
-        if (live) live = mbar_wait(o_done + 8 * t, (blocks - 1) & 1u, site, kStallSoftmaxO, blocks);
-        if (live) {
+#pragma unroll
+        for (uint32_t t = 0; t < kTiles; ++t) {
+            const uint32_t blocks = keys.blocks[t];
+            if (!live || blocks == 0) continue;
+            const uint32_t o_tmem = tmem + lane_base + kOutputColumn + kHead * t + 64 * half;
+            if (!mbar_wait(o_done + 8 * t, (blocks - 1) & 1u, site, kStallSoftmaxO, blocks)) {
+                live = false;
+                continue;
+            }
             tc_fence_after_sync();
-            const float inverse = 1.0f / row_sum;
+            // The row sum is the two siblings' halves together.
+            float* const mine = swap + ((step & 1u) * 2 + half) * kTileRows + row;
+            float* const theirs = swap + ((step & 1u) * 2 + (half ^ 1u)) * kTileRows + row;
+            ++step;
+            *mine = row_sum[t];
+            sibling_sync();
+            const float total = *mine + *theirs;
+            const float inverse = 1.0f / total;
             const uint32_t q_index = q_row0 + kTileRows * t + row;
-            if (lse)
+            if (lse && half == 0)
                 lse[static_cast<size_t>(plane) * seq + q_index] =
-                    (row_max * scale_log2 + lg2_approx(row_sum)) * 0.6931471805599453f;
-            // Q_t's shared tile is dead once the last MMA retired: it stages the output.
-            const uint32_t stage = q_tiles + t * kBlockBytes;
+                    (row_max[t] * scale_log2 + lg2_approx(total)) * 0.6931471805599453f;
+            // Q_t's shared tile is dead once the last MMA retired: it stages the output. This
+            // warp owns rows [32 q, 32 q + 32) of the [128, 64] subtile of head columns 64 half...
+            const uint32_t subtile = q_tiles + t * kBlockBytes + half * kSubtileBytes;
 #pragma unroll 1
-            for (uint32_t c = 0; c < 4; ++c) {
+            for (uint32_t c = 0; c < 2; ++c) {
                 uint32_t o[32];
                 tmem_ld_32x32(o_tmem + 32 * c, o);
                 tmem_wait_ld();
                 if (o_f32) {
                     float4* out = reinterpret_cast<float4*>(
-                        o_f32 + (static_cast<size_t>(plane) * seq + q_index) * kHead + 32 * c);
+                        o_f32 + (static_cast<size_t>(plane) * seq + q_index) * kHead + 64 * half + 32 * c);
 #pragma unroll
                     for (uint32_t i = 0; i < 8; ++i)
                         out[i] = make_float4(__uint_as_float(o[4 * i]) * inverse,
@@ -381,12 +484,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                                              __uint_as_float(o[4 * i + 2]) * inverse,
                                              __uint_as_float(o[4 * i + 3]) * inverse);
                 } else {
-                    const uint32_t subtile = stage + (c / 2) * kSubtileBytes;
 #pragma unroll
                     for (uint32_t i = 0; i < 4; ++i) {
-                        const uint32_t chunk = 4 * (c % 2) + i;
                         const uint32_t* v = o + 8 * i;
-                        st_shared_v4(subtile + swizzled_chunk_offset(row, chunk, 0),
+                        st_shared_v4(subtile + swizzled_chunk_offset(row, 4 * c + i, 0),
                                      pack_bf16x2(__uint_as_float(v[0]) * inverse,
                                                  __uint_as_float(v[1]) * inverse),
                                      pack_bf16x2(__uint_as_float(v[2]) * inverse,
@@ -402,15 +503,14 @@ __global__ void __launch_bounds__(kThreads, 1)
                 fence_proxy_async_shared();
                 __syncwarp();
                 if (lane == 0) {
-                    const int out_row = static_cast<int>(q_row0 + kTileRows * t + 32 * quadrant);
-                    for (uint32_t half = 0; half < 2; ++half)
-                        tma_store_3d(&o_map, stage + half * kSubtileBytes + 32 * quadrant * 128,
-                                     static_cast<int>(64 * half), out_row, static_cast<int>(plane));
+                    tma_store_3d(&o_map, subtile + 32 * quadrant * 128, static_cast<int>(64 * half),
+                                 static_cast<int>(q_row0 + kTileRows * t + 32 * quadrant),
+                                 static_cast<int>(plane));
                     tma_store_commit();
-                    tma_store_wait_all();
                 }
             }
         }
+        if (lane == 0) tma_store_wait_all();
     }
 
     // ---------------------------------------------------- teardown

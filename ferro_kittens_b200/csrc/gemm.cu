@@ -66,9 +66,10 @@ struct Plan {
 };
 constexpr Plan kPlan{};
 // Tiles must sit on 1024-byte boundaries for the operand descriptors' zero base
-// offset; the kernel rounds its dynamic base up, which the launch pays for here.
+// offset: the dynamic shared array is declared with that alignment and the kernel
+// refuses to run (status kMisaligned) should the base ever come back otherwise.
 constexpr uint32_t kBaseAlign = 1024;
-constexpr uint32_t kSharedBytes = static_cast<uint32_t>(kPlan.end.bytes()) + kBaseAlign;
+constexpr uint32_t kSharedBytes = static_cast<uint32_t>(kPlan.end.bytes());
 static_assert(kSharedBytes <= 232448, "plan exceeds the opt-in shared memory of an sm_100 CTA");
 static_assert(kPlan.a_ring.at % 1024 == 0 && kPlan.b_ring.at % 1024 == 0 &&
                   kPlan.bands.at % 1024 == 0,
@@ -79,6 +80,7 @@ enum StallCode : uint32_t {
     kStallMmaFull = 0x102,
     kStallMmaAccumulator = 0x103,
     kStallEpilogue = 0x104,
+    kMisaligned = 0x1ff,
 };
 
 // What the launch hands every role so that each walks the same item list.
@@ -121,9 +123,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                           const __grid_constant__ CUtensorMap b_map,
                           const __grid_constant__ CUtensorMap c_map, const Schedule plan,
                           uint32_t* status) {
-    extern __shared__ uint8_t dynamic_shared[];
+    extern __shared__ __align__(1024) uint8_t dynamic_shared[];
     const uint32_t raw = smem_u32(dynamic_shared);
-    const uint32_t base = (raw + kBaseAlign - 1) & ~(kBaseAlign - 1);
+    const uint32_t base = raw;
+    if (raw & (kBaseAlign - 1)) {
+        if (threadIdx.x == 0 && status) atomicCAS(status, 0u, static_cast<uint32_t>(kMisaligned));
+        return;
+    }
 
     const uint32_t a_ring = base + kPlan.a_ring.at;
     const uint32_t b_ring = base + kPlan.b_ring.at;
@@ -230,6 +236,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                         operand_descriptor(b_ring + s * kBTileBytes, kKMajorLeadingBytes);
                     const uint32_t accumulate = k != 0;
                     if (item.halves == 2) {
+#ifdef FK_GEMM_GROUPED_ISSUE
+#pragma unroll
+                        for (uint32_t chunk = 0; chunk < kBlockK / 16; ++chunk) {
+                            const uint64_t step = (chunk * kKMajorChunkBytes) >> 4;
+                            mma_ss<2>(tmem, a0_desc + step, b_desc + step, idesc, accumulate | chunk);
+                        }
+#pragma unroll
+                        for (uint32_t chunk = 0; chunk < kBlockK / 16; ++chunk) {
+                            const uint64_t step = (chunk * kKMajorChunkBytes) >> 4;
+                            mma_ss<2>(tmem + kBlockN, a1_desc + step, b_desc + step, idesc,
+                                      accumulate | chunk);
+                        }
+#else
 #pragma unroll
                         for (uint32_t chunk = 0; chunk < kBlockK / 16; ++chunk) {
                             // Advancing the 14-bit address field by 32 B per K=16 chunk.
@@ -238,6 +257,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                             mma_ss<2>(tmem + kBlockN, a1_desc + step, b_desc + step, idesc,
                                       accumulate | chunk);
                         }
+#endif
                     } else {
 #pragma unroll
                         for (uint32_t chunk = 0; chunk < kBlockK / 16; ++chunk) {

@@ -307,7 +307,8 @@ static const char* stall_role(uint32_t code) {
         case 0x204: return "flash MMA waiting for P";
         case 0x205: return "flash softmax waiting for S";
         case 0x206: return "flash softmax waiting for O";
-        case 0x207: return "flash MMA waiting for a drained S";
+        case 0x1ff: return "gemm found its shared memory base off a 1024-byte boundary";
+        case 0x2ff: return "flash found its shared memory base off a 1024-byte boundary";
         default: return "unknown role";
     }
 }
