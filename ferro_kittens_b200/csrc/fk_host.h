@@ -26,7 +26,7 @@ namespace fk {
 /// grown when a call needs more, released at process exit by the runtime.
 int scratch(int slot, size_t bytes, void** out);
 
-/// 4 status words per device for the host-buffer entry points.
+/// 8 status words per device for the host-buffer entry points.
 int scratch_status(uint32_t** out);
 
 }  // namespace fk

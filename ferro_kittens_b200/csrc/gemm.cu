@@ -463,7 +463,7 @@ extern "C" int fk_gemm_bf16_host(const uint16_t* a_host, const uint16_t* b_host,
     if (status == FK_OK) status = scratch_status(&status_words);
     if (status != FK_OK) return status;
     cudaStream_t stream = nullptr;
-    FK_CUDA(cudaMemsetAsync(status_words, 0, 16, stream));
+    FK_CUDA(cudaMemsetAsync(status_words, 0, 32, stream));
     FK_CUDA(cudaMemcpyAsync(a, a_host, a_bytes, cudaMemcpyHostToDevice, stream));
     FK_CUDA(cudaMemcpyAsync(b, b_host, b_bytes, cudaMemcpyHostToDevice, stream));
     status = fk_gemm_bf16(a, b, c, m, n, k, n, group, stream, status_words);

@@ -307,6 +307,10 @@ static const char* stall_role(uint32_t code) {
         case 0x204: return "flash MMA waiting for P";
         case 0x205: return "flash softmax waiting for S";
         case 0x206: return "flash softmax waiting for O";
+        case 0x207: return "flash MMA waiting for the previous item's output to be read out";
+        case 0x208: return "flash loader waiting for a free Q buffer";
+        case 0x209: return "flash role waiting on the item queue";
+        case 0x20a: return "flash softmax warp waiting for its sibling warp";
         case 0x1ff: return "gemm found its shared memory base off a 1024-byte boundary";
         case 0x2ff: return "flash found its shared memory base off a 1024-byte boundary";
         default: return "unknown role";
@@ -356,7 +360,7 @@ int scratch_status(uint32_t** out) {
     FK_CUDA(cudaGetDevice(&device));
     if (device >= kMaxDevices) return fk_fail(FK_ERR_INVALID, "device index out of range");
     std::lock_guard<std::mutex> lock(scratch_guard);
-    if (!status_words[device]) FK_CUDA(cudaMalloc(&status_words[device], 4 * sizeof(uint32_t)));
+    if (!status_words[device]) FK_CUDA(cudaMalloc(&status_words[device], 8 * sizeof(uint32_t)));
     *out = status_words[device];
     return FK_OK;
 }

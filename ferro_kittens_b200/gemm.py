@@ -34,8 +34,8 @@ def _require_cuda_bf16(name: str, tensor: torch.Tensor) -> None:
 
 
 def new_status(device) -> torch.Tensor:
-    """Four zeroed device words a launch writes only if one of its waits gives up."""
-    return torch.zeros(4, dtype=torch.int32, device=device)
+    """Zeroed device words for a launch; it writes the first four only if one of its waits gives up."""
+    return torch.zeros(8, dtype=torch.int32, device=device)
 
 
 def maps(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor):

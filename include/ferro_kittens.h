@@ -35,7 +35,7 @@ enum {
     FK_ERR_TOO_LARGE = -4,    /* shared plan past the device's opt-in limit */
     FK_ERR_DRIVER = -5,       /* the CUDA driver / runtime refused a call */
     FK_ERR_TIMEOUT = -6,      /* a host wait ran out of its budget */
-    FK_ERR_DEVICE_STALL = -7  /* a kernel's bounded wait gave up; see fk_status_decode */
+    FK_ERR_DEVICE_STALL = -7  /* a kernel's bounded wait gave up; see fk_status_check */
 };
 
 typedef enum { FK_BF16 = 0, FK_F16 = 1, FK_F32 = 2 } fk_element_t;
@@ -145,7 +145,7 @@ uint32_t fk_tmem_address(uint32_t base, uint32_t row, uint32_t column); /* src/t
  *   c_map: rank-2 dims [n, m] (outer stride = ldc bytes), box [64, 32], SWIZZLE_128B
  * Requires m % 256 == 0, n % 256 == 0, k % 64 == 0, group >= 1. Asynchronous on
  * `stream`. `device_status` is null or 4 zeroed device words the kernel writes
- * only if a bounded wait gives up (decode with fk_status_decode).
+ * only if a bounded wait gives up (read them with fk_status_check).
  */
 int fk_gemm_bf16_launch(const void* a_map, const void* b_map, const void* c_map, uint32_t m,
                         uint32_t n, uint32_t k, uint32_t group, void* stream,
@@ -169,8 +169,9 @@ int fk_gemm_bf16_host(const uint16_t* a_host, const uint16_t* b_host, uint16_t* 
  * (natural log), may be null. `o_f32`, when non-null, receives the output as
  * fp32 [planes, seq, 128] (the reference kernel's own output type) instead of
  * bf16 through `o_map`.
- *   q_map / k_map / v_map / o_map: fk_encode_bf16_panels(base, 128 box rows, 128, seq, planes)
- * Requires seq % 128 == 0, planes >= 1. */
+ *   q_map / k_map / v_map: fk_encode_bf16_panels(base, 128 box rows, 128, seq, planes)
+ *   o_map:                 fk_encode_bf16_panels(base,  32 box rows, 128, seq, planes)
+ * Requires seq % 128 == 0, planes >= 1. `device_status` as for the GEMM. */
 int fk_flash_fwd_launch(const void* q_map, const void* k_map, const void* v_map, const void* o_map,
                         float* o_f32, float* lse, uint32_t planes, uint32_t seq, float scale,
                         int causal, void* stream, uint32_t* device_status);
