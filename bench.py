@@ -315,10 +315,10 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     if world == 1 and not args.no_cpu_baseline:
         import oracle
 
-        a_words = host_a[:256].view(torch.int16).numpy().view(np.uint16)
+        a_words = host_a[:2048].view(torch.int16).numpy().view(np.uint16)
         b_words = host_b.view(torch.int16).numpy().view(np.uint16)
         probe_rate, _ = cpu_gemm_rate(a_words, b_words, 8)
-        rows = int(max(8, min(256, probe_rate * 1e12 * 15.0 / (2.0 * N * K))))
+        rows = int(max(8, min(2048, probe_rate * 1e12 * 15.0 / (2.0 * N * K))))
         rate, elapsed = cpu_gemm_rate(a_words, b_words, rows)
         cpu_baseline = {"value": rate, "unit": "TFLOP/s", "cores": oracle.threads(), "kind": "port",
                         "sample": f"{rows} rows of C x full N={N} x full K={K} in {elapsed:.1f} s "

@@ -49,14 +49,17 @@ constexpr uint32_t kOutputColumn = 256;  // O_t at kOutputColumn + 128 t
 constexpr float kRescaleThreshold = 8.0f;
 // Of the 16 pairs of scores in a 32-column chunk, the pairs whose bit is set here take their
 // 2^x from a polynomial on the FMA pipe instead of the ex2 unit: at D = 128 a score tile costs
-// as many ex2-unit cycles as tensor cycles, so part of the exponentials has to move.
+// as many ex2-unit cycles as tensor cycles. Measured on B200 every non-zero mask was slower
+// than none (the softmax warps are bound by issue and latency, not by the ex2 unit alone),
+// so the default moves nothing; the path stays for tuning.
 #ifndef FK_FLASH_POLY_MASK
-#define FK_FLASH_POLY_MASK 0x5555u
+#define FK_FLASH_POLY_MASK 0x0000u
 #endif
 constexpr uint32_t kPolyMask = FK_FLASH_POLY_MASK;
 
 struct Plan {
-    SharedPlan q, kv, swap, q_full, kv_full, kv_empty, s_full, p_ready, o_done, tmem_slot, stop, end;
+    SharedPlan q, kv, swap, q_full, kv_full, kv_empty, s_full, p_ready, o_done, pair, tmem_slot, stop,
+        end;
     constexpr Plan()
         : q(SharedPlan{}.tile_ring(kTileRows, kHead, 2, kTiles)),
           kv(q.tile_ring(kBlockKeys, kHead, 2, kSlots)),
@@ -67,7 +70,8 @@ struct Plan {
           s_full(kv_empty.semaphores(kTiles)),
           p_ready(s_full.semaphores(kTiles)),
           o_done(p_ready.semaphores(kTiles)),
-          tmem_slot(o_done.tmem_slot()),
+          pair(o_done.semaphores(4)),
+          tmem_slot(pair.tmem_slot()),
           stop(tmem_slot.word()),
           end(stop) {}
 };
@@ -85,6 +89,7 @@ enum StallCode : uint32_t {
     kStallMmaP = 0x204,
     kStallSoftmaxS = 0x205,
     kStallSoftmaxO = 0x206,
+    kStallSibling = 0x20a,
     kMisaligned = 0x2ff,
 };
 
@@ -177,6 +182,8 @@ __global__ void __launch_bounds__(kThreads, 1)
             mbar_init(p_ready + 8 * t, kSoftmaxWarps);
             mbar_init(o_done + 8 * t, 1);
         }
+        for (uint32_t quadrant = 0; quadrant < 4; ++quadrant)
+            mbar_init(base + kPlan.pair.at + 8 * quadrant, 2);
         *stop_flag = 0;
         fence_mbarrier_init();
         prefetch_tensormap(&q_map);
@@ -325,14 +332,19 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t lane_base = (32 * quadrant) << 16;
         const float scale_log2 = scale * 1.4426950408889634f;
         float* const swap = reinterpret_cast<float*>(dynamic_shared + (base + kPlan.swap.at - raw));
-        const auto sibling_sync = [&]() {
-            asm volatile("bar.sync %0, 64;" ::"r"(1u + quadrant) : "memory");
-        };
+        const uint32_t pair_bar = base + kPlan.pair.at + 8 * quadrant;
 
         float row_max[kTiles] = {-INFINITY, -INFINITY};  // raw score units, same in both siblings
         float row_sum[kTiles] = {0.0f, 0.0f};            // this thread's half of the row only
         uint32_t step = 0;
         bool live = true;
+        // Rendezvous of the two warps that own the same rows, called after `step` was advanced:
+        // a two-arrival mbarrier, so that this wait is bounded like every other one.
+        const auto sibling_sync = [&]() {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(pair_bar);
+            if (!mbar_wait(pair_bar, (step - 1) & 1u, site, kStallSibling, step)) live = false;
+        };
 
         for (uint32_t j = 0; live && j < keys.most; ++j) {
 #pragma unroll
