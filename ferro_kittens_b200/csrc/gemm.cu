@@ -24,6 +24,8 @@
 // Barriers are initialised once per launch and their phases carried across
 // items; roles meet only through them. Every wait is bounded.
 
+#include <mutex>
+
 #include "fk_host.h"
 #include "fk_layout.h"
 #include "fk_ptx.cuh"
@@ -463,6 +465,70 @@ extern "C" int fk_gemm_bf16_host(const uint16_t* a_host, const uint16_t* b_host,
     if (status == FK_OK) status = scratch_status(&status_words);
     if (status != FK_OK) return status;
     cudaStream_t stream = nullptr;
+    FK_CUDA(cudaMemsetAsync(status_words, 0, 32, stream));
+    FK_CUDA(cudaMemcpyAsync(a, a_host, a_bytes, cudaMemcpyHostToDevice, stream));
+    FK_CUDA(cudaMemcpyAsync(b, b_host, b_bytes, cudaMemcpyHostToDevice, stream));
+    status = fk_gemm_bf16(a, b, c, m, n, k, n, group, stream, status_words);
+    if (status != FK_OK) return status;
+    FK_CUDA(cudaMemcpyAsync(c_host, c, c_bytes, cudaMemcpyDeviceToHost, stream));
+    return fk_status_check(status_words, stream);
+}
+
+// ------------------------------------------------------------------ no-allocation variant
+//
+// fk_gemm_bf16_host stages its operands in device buffers it gets from cudaMalloc. Some callers
+// must never reach the CUDA allocator from this call: a serving loop whose latency budget cannot
+// absorb the device-wide synchronisation cudaMalloc and cudaFree imply, or a process whose device
+// memory is already handed out in full to another pool, where a late cudaMalloc may simply fail.
+// For them the same staging (A, B, C and the status words) lives in one array that is part of
+// the library image, of a fixed, modest size.
+
+namespace {
+
+constexpr size_t kStaticOperandBytes = 8u << 20;  // each of A, B and C: at most 8 MiB
+constexpr size_t kStaticStatusBytes = 256;
+// Held by every GPU that loads the library, until the process exits.
+static __device__ __align__(256) uint8_t fk_static_scratch[3 * kStaticOperandBytes + kStaticStatusBytes];
+
+// The array's name is only a host-side handle; the device address is looked up once per device.
+int static_scratch(uint8_t** out) {
+    static std::mutex guard;
+    static uint8_t* base[64] = {};
+    int device = 0;
+    FK_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= 64) return fk_fail(FK_ERR_INVALID, "device index %d out of range", device);
+    std::lock_guard<std::mutex> lock(guard);
+    if (!base[device]) {
+        void* address = nullptr;
+        FK_CUDA(cudaGetSymbolAddress(&address, fk_static_scratch));
+        base[device] = static_cast<uint8_t*>(address);
+    }
+    *out = base[device];
+    return FK_OK;
+}
+
+}  // namespace
+
+extern "C" int fk_gemm_bf16_host_noalloc(const uint16_t* a_host, const uint16_t* b_host,
+                                         uint16_t* c_host, uint32_t m, uint32_t n, uint32_t k,
+                                         uint32_t group) {
+    if (!a_host || !b_host || !c_host) return fk_fail(FK_ERR_INVALID, "an operand pointer is null");
+    const size_t a_bytes = size_t(m) * k * 2, b_bytes = size_t(n) * k * 2, c_bytes = size_t(m) * n * 2;
+    if (a_bytes > kStaticOperandBytes || b_bytes > kStaticOperandBytes || c_bytes > kStaticOperandBytes)
+        return fk_fail(FK_ERR_TOO_LARGE,
+                       "%ux%ux%u needs %zu / %zu / %zu bytes for A / B / C; the built-in staging holds "
+                       "%zu bytes each (use fk_gemm_bf16_host for larger shapes)",
+                       m, n, k, a_bytes, b_bytes, c_bytes, kStaticOperandBytes);
+    uint8_t* scratch_base = nullptr;
+    int status = static_scratch(&scratch_base);
+    if (status != FK_OK) return status;
+    void* a = scratch_base;
+    void* b = scratch_base + kStaticOperandBytes;
+    void* c = scratch_base + 2 * kStaticOperandBytes;
+    uint32_t* status_words = reinterpret_cast<uint32_t*>(scratch_base + 3 * kStaticOperandBytes);
+    cudaStream_t stream = nullptr;
+    // The array keeps the previous call's contents: the status words must start at zero. A, B
+    // and C are overwritten in full by this call before anything reads them.
     FK_CUDA(cudaMemsetAsync(status_words, 0, 32, stream));
     FK_CUDA(cudaMemcpyAsync(a, a_host, a_bytes, cudaMemcpyHostToDevice, stream));
     FK_CUDA(cudaMemcpyAsync(b, b_host, b_bytes, cudaMemcpyHostToDevice, stream));

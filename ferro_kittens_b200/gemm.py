@@ -86,3 +86,11 @@ def run_host(a, b, c, m: int, n: int, k: int, group: int = GROUP) -> None:
     def address(x):
         return x.data_ptr() if hasattr(x, "data_ptr") else x.ctypes.data
     check(library().fk_gemm_bf16_host(address(a), address(b), address(c), m, n, k, group))
+
+
+def run_host_noalloc(a, b, c, m: int, n: int, k: int, group: int = GROUP) -> None:
+    """``run_host`` for callers that must not reach the CUDA allocator: the staging lives in an
+    array built into the library, so each of A, B and C is limited to 8 MiB."""
+    def address(x):
+        return x.data_ptr() if hasattr(x, "data_ptr") else x.ctypes.data
+    check(library().fk_gemm_bf16_host_noalloc(address(a), address(b), address(c), m, n, k, group))

@@ -162,6 +162,22 @@ int fk_gemm_bf16(const void* a, const void* b, void* c, uint32_t m, uint32_t n, 
 int fk_gemm_bf16_host(const uint16_t* a_host, const uint16_t* b_host, uint16_t* c_host, uint32_t m,
                       uint32_t n, uint32_t k, uint32_t group);
 
+/* No counterpart in the reference. fk_gemm_bf16_host for callers that must not reach the CUDA
+ * allocator from this call (a latency-bound serving loop that cannot take the device-wide
+ * synchronisation of cudaMalloc/cudaFree; a process whose device memory is already handed out
+ * in full to another pool): A, B, C and the status words are staged in an array that is part of
+ * the library image, so the call allocates nothing. Limits and rules:
+ *   - each of A (m*k), B (n*k) and C (m*n) at most 8 MiB of bf16; larger shapes are refused
+ *     with FK_ERR_TOO_LARGE and a message naming the sizes;
+ *   - every GPU that loads the library holds the 24 MiB + 256 B array until the process exits;
+ *   - the first call on a device looks the array's device address up (cudaGetSymbolAddress);
+ *     make that first call outside any stream capture;
+ *   - all calls on a device share the array, which keeps the previous call's contents (the
+ *     call clears what must start at zero): two calls that overlap on the GPU race. The call
+ *     itself runs on the default stream and returns once C is on the host. */
+int fk_gemm_bf16_host_noalloc(const uint16_t* a_host, const uint16_t* b_host, uint16_t* c_host,
+                              uint32_t m, uint32_t n, uint32_t k, uint32_t group);
+
 /* Flash-attention forward: `kernels::flash_forward` + `flash_forward::run`'s
  * guards (examples/src/flash_forward.rs:151-158, 477-483), widened to a batch,
  * a non-causal mode, bf16 output and a log-sum-exp vector. Q, K, V and O are
