@@ -132,6 +132,7 @@ def run_reference(args, rank: int, world: int) -> None:
         return
     import oracle
 
+    oracle.use_all_cores()
     a_words, b_words = host_operands(256)
     probe_rate, _ = cpu_gemm_rate(a_words, b_words, 8)
     budget = 120.0 / max(1, args.steps + args.warmup)
@@ -315,6 +316,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     if world == 1 and not args.no_cpu_baseline:
         import oracle
 
+        oracle.use_all_cores()
         a_words = host_a[:2048].view(torch.int16).numpy().view(np.uint16)
         b_words = host_b.view(torch.int16).numpy().view(np.uint16)
         probe_rate, _ = cpu_gemm_rate(a_words, b_words, 8)

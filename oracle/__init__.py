@@ -20,6 +20,8 @@ _u16p = np.ctypeslib.ndpointer(dtype=np.uint16, flags="C_CONTIGUOUS")
 _f64p = np.ctypeslib.ndpointer(dtype=np.float64, flags="C_CONTIGUOUS")
 
 _lib.fko_threads.restype = c_int
+_lib.fko_set_threads.argtypes = [c_int]
+_lib.fko_set_threads.restype = None
 _lib.fko_to_bf16.argtypes = [c_float]
 _lib.fko_to_bf16.restype = c_uint16
 _lib.fko_from_bf16.argtypes = [c_uint16]
@@ -50,6 +52,16 @@ _lib.fko_flash_rows.restype = None
 def threads() -> int:
     """Host threads the OpenMP loops use."""
     return _lib.fko_threads()
+
+
+def use_all_cores() -> int:
+    """Let the OpenMP loops use every core this process may run on (a launcher may have set
+    OMP_NUM_THREADS=1); returns the count."""
+    import os
+
+    count = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    _lib.fko_set_threads(count)
+    return threads()
 
 
 def to_bf16(value: float) -> int:

@@ -33,6 +33,15 @@ int fko_threads(void) {
 #endif
 }
 
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; the timed baseline sets its own count. */
+void fko_set_threads(int count) {
+#ifdef _OPENMP
+    if (count > 0) omp_set_num_threads(count);
+#else
+    (void)count;
+#endif
+}
+
 /* ---------------------------------------------------------------- bf16 */
 
 /* examples/src/gemm.rs:444-447 -- round-to-nearest-even fp32 -> bf16. */
