@@ -93,6 +93,7 @@ SIGNATURES = {
     "fk_wait_stream": (c_int, [c_void_p, c_uint32]),
     "fk_wait_event": (c_int, [c_void_p, c_uint32]),
     "fk_status_check": (c_int, [c_void_p, c_void_p]),
+    "fk_selftest_stall": (c_int, [c_void_p, c_void_p, c_uint32]),
 }
 
 _library = None

@@ -100,16 +100,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Where a bounded wait gave up: written once per launch into the caller's
 // status words {code, block, detail, parity}. 0 means the launch ran clean.
-struct StallSite {
-    uint32_t* status;        // global, may be null
-    volatile uint32_t* stop; // shared: raised once any role gives up
-    uint32_t peer_stop;      // shared::cluster address of the peer's flag, 0 if none
-};
-
 // Cycle budget of one wait. About a second at the clocks a B200 runs at; the
 // longest legitimate wait in either kernel is one tile's main loop (tens of
 // microseconds).
 constexpr long long kWaitBudgetCycles = 1ll << 31;
+
+struct StallSite {
+    uint32_t* status;        // global, may be null
+    volatile uint32_t* stop; // shared: raised once any role gives up
+    uint32_t peer_stop;      // shared::cluster address of the peer's flag, 0 if none
+    long long budget = kWaitBudgetCycles;
+};
 
 /// Parity wait with a deadline. Returns false when the budget ran out or
 /// another role already raised `stop`; the caller must then fall through to
@@ -125,7 +126,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const S
         for (int i = 0; i < 16; ++i)
             if (mbar_try_wait(bar, parity)) return true;
         if (*site.stop) return false;
-        if (clock64() - start > kWaitBudgetCycles) {
+        if (clock64() - start > site.budget) {
             *site.stop = 1;
             if (site.peer_stop) st_shared_cluster_u32(site.peer_stop, 1);
             if (site.status && atomicCAS(site.status, 0u, code) == 0u) {

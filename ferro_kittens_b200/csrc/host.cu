@@ -12,6 +12,7 @@
 
 #include "fk_host.h"
 #include "fk_layout.h"
+#include "fk_ptx.cuh"
 
 // ------------------------------------------------------------------ errors
 
@@ -169,6 +170,10 @@ extern "C" int fk_tensor_map(void* map_out, const fk_layout_t* layout, uint32_t 
     EncodeTiled encode = nullptr;
     status = encode_entry(&encode);
     if (status != FK_OK) return status;
+    // The driver call wants a context current on the calling thread; a thread that has made no
+    // runtime call yet has none (the encode then fails with CUDA_ERROR_INVALID_CONTEXT). A null
+    // free binds the device's primary context and does nothing else.
+    FK_CUDA(cudaFree(nullptr));
 
     cuuint64_t dims[5], strides[4];
     cuuint32_t boxes[5], element_strides[5];
@@ -313,6 +318,7 @@ static const char* stall_role(uint32_t code) {
         case 0x20a: return "flash softmax warp waiting for its sibling warp";
         case 0x1ff: return "gemm found its shared memory base off a 1024-byte boundary";
         case 0x2ff: return "flash found its shared memory base off a 1024-byte boundary";
+        case 0x301: return "self-test wait on a barrier nothing arrives on";
         default: return "unknown role";
     }
 }
@@ -326,6 +332,34 @@ extern "C" int fk_status_check(const uint32_t* device_status, void* stream) {
     if (words[0] == 0) return FK_OK;
     return fk_fail(FK_ERR_DEVICE_STALL, "device stall: %s (code %#x) in block %u, step %u, parity %u",
                    stall_role(words[0]), words[0], words[1], words[2], words[3]);
+}
+
+// A wait that nothing will ever complete, with a short budget: exercises the bounded-wait,
+// status-word and clean-exit path that both kernels rely on, without starving any barrier that
+// real data depends on. The kernel returns normally and the context stays usable.
+__global__ void stall_probe_kernel(uint32_t* status, long long budget_cycles) {
+    __shared__ __align__(8) unsigned long long barrier;
+    __shared__ uint32_t stop;
+    const uint32_t bar = fk::smem_u32(&barrier);
+    if (threadIdx.x == 0) {
+        fk::mbar_init(bar, 1);
+        stop = 0;
+        fk::fence_mbarrier_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const fk::StallSite site{status, &stop, 0, budget_cycles};
+        fk::mbar_wait(bar, 0, site, 0x301, 7);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) fk::mbar_inval(bar);
+}
+
+extern "C" int fk_selftest_stall(void* stream, uint32_t* device_status, uint32_t budget_cycles) {
+    if (!device_status) return fk_fail(FK_ERR_INVALID, "the status pointer is null");
+    stall_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(device_status, budget_cycles);
+    FK_CUDA(cudaGetLastError());
+    return FK_OK;
 }
 
 // ------------------------------------------------------------------ per-device scratch

@@ -215,6 +215,12 @@ int fk_wait_event(void* event, uint32_t budget_ms);
  * parity in fk_last_error(). */
 int fk_status_check(const uint32_t* device_status, void* stream);
 
+/* `Semaphore::wait_before(parity, ticks)` giving up (src/sync.rs:214-245), as a self-test: launches
+ * one warp that waits `budget_cycles` on a barrier nothing arrives on, records the expiry in the 4
+ * zeroed `device_status` words and exits normally. fk_status_check then reports
+ * FK_ERR_DEVICE_STALL; the context stays usable. */
+int fk_selftest_stall(void* stream, uint32_t* device_status, uint32_t budget_cycles);
+
 #ifdef __cplusplus
 }
 #endif

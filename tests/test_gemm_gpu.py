@@ -132,3 +132,23 @@ def test_full_size_properties(device, shape):
     reference = a @ b.T
     difference = (c.float() - reference.float()).abs().max().item()
     assert difference <= 2 ** -7 * reference.float().abs().max().item()
+
+
+def test_a_wait_that_runs_out_is_reported_and_leaves_the_context_usable(device):
+    """Nothing is starved on purpose in the real kernels: a probe warp waits on a barrier nobody
+    arrives on, with a short budget, through the same bounded wait both kernels use."""
+    from ferro_kittens_b200._lib import FK_ERR_DEVICE_STALL, check, library
+
+    status = gemm.new_status(device)
+    check(library().fk_selftest_stall(torch.cuda.current_stream().cuda_stream, status.data_ptr(), 200_000))
+    with pytest.raises(FerroKittensError, match="self-test wait") as error:
+        gemm.check_status(status)
+    assert error.value.code == FK_ERR_DEVICE_STALL
+    words = status.tolist()
+    assert words[0] == 0x301 and words[2] == 7 and words[3] == 0
+    # The launch returned normally: the same context runs the exact gate right after.
+    m, n, k = 512, 256, 256
+    a = _to_device(oracle.gemm_stage("a", m, k), device)
+    b = _to_device(oracle.gemm_stage("b", n, k), device)
+    c = _run_checked(a, b)
+    assert oracle.gemm_check_c(_to_words(c), m, n, k)[0] == 0
