@@ -49,11 +49,11 @@ constexpr uint32_t kOutputColumn = 256;  // O_t at kOutputColumn + 128 t
 constexpr float kRescaleThreshold = 8.0f;
 // Of the 16 pairs of scores in a 32-column chunk, the pairs whose bit is set here take their
 // 2^x from a polynomial on the FMA pipe instead of the ex2 unit: at D = 128 a score tile costs
-// as many ex2-unit cycles as tensor cycles. Measured on B200 every non-zero mask was slower
-// than none (the softmax warps are bound by issue and latency, not by the ex2 unit alone),
-// so the default moves nothing; the path stays for tuning.
+// as many ex2-unit cycles as tensor cycles. Measured on B200 in back-to-back launches (the
+// power-capped regime), two pairs of sixteen are the best share: +6 % non-causal, +3 % causal
+// over none; one pair is about as good, three or more lose again to the extra issue slots.
 #ifndef FK_FLASH_POLY_MASK
-#define FK_FLASH_POLY_MASK 0x0000u
+#define FK_FLASH_POLY_MASK 0x0101u
 #endif
 constexpr uint32_t kPolyMask = FK_FLASH_POLY_MASK;
 
@@ -421,7 +421,12 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const float shift = row_max[t] * scale_log2;
                 const float2 scale2 = make_float2(scale_log2, scale_log2);
                 const float2 shift2 = make_float2(-shift, -shift);
+                // Four independent sum chains: with two, the compiler recycles the registers the
+                // exponentials land in so tightly that every ex2 waits out the one before it and
+                // the loop runs at half the unit's rate (measured in isolation: 1219 cycles per 64
+                // columns for two warps on a scheduler against 1080 with four chains, bound 1024).
                 float2 sum_a = make_float2(0.0f, 0.0f), sum_b = make_float2(0.0f, 0.0f);
+                float2 sum_c = make_float2(0.0f, 0.0f), sum_d = make_float2(0.0f, 0.0f);
 #pragma unroll
                 for (uint32_t c = 0; c < 2; ++c) {
                     // 32 keys -> 16 packed bf16 pairs, written over S columns both siblings have read.
@@ -438,15 +443,19 @@ __global__ void __launch_bounds__(kThreads, 1)
                             p.x = ex2_approx(x.x);
                             p.y = ex2_approx(x.y);
                         }
-                        if (i & 1u)
-                            sum_b = __fadd2_rn(sum_b, p);
-                        else
+                        if ((i & 3u) == 0)
                             sum_a = __fadd2_rn(sum_a, p);
+                        else if ((i & 3u) == 1)
+                            sum_b = __fadd2_rn(sum_b, p);
+                        else if ((i & 3u) == 2)
+                            sum_c = __fadd2_rn(sum_c, p);
+                        else
+                            sum_d = __fadd2_rn(sum_d, p);
                         packed[i] = pack_bf16x2(p.x, p.y);
                     }
                     tmem_st_32x16(s_tmem + 32 * half + 16 * c, packed);
                 }
-                row_sum[t] += (sum_a.x + sum_b.x) + (sum_a.y + sum_b.y);
+                row_sum[t] += ((sum_a.x + sum_b.x) + (sum_c.x + sum_d.x)) + ((sum_a.y + sum_b.y) + (sum_c.y + sum_d.y));
                 if (warp == 0) trace(t, j, 3);
                 tmem_wait_st();
                 tc_fence_before_sync();
