@@ -65,10 +65,12 @@ constexpr uint32_t kMnMajorChunkBytes = 2048;
 /// accumulator: D format at [5:4], A/B formats at [9:7]/[12:10], transpose
 /// A/B at 15/16, N>>3 at [22:17], M>>4 at [28:24]
 /// (reference: `descriptor` src/mma.rs:137-146, layout restated in its test :576-584).
+/// `operand_format`: 1 = bf16 (the default), 0 = fp16, for both A and B.
 FK_HD constexpr uint32_t instruction_descriptor(uint32_t m, uint32_t n, bool transpose_a,
-                                                bool transpose_b) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((transpose_a ? 1u : 0u) << 15) |
-           ((transpose_b ? 1u : 0u) << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
+                                                bool transpose_b, uint32_t operand_format = 1u) {
+    return (1u << 4) | (operand_format << 7) | (operand_format << 10) |
+           ((transpose_a ? 1u : 0u) << 15) | ((transpose_b ? 1u : 0u) << 16) | ((n >> 3) << 17) |
+           ((m >> 4) << 24);
 }
 
 /// Tensor-memory address of (lane row, 32-bit column) from an allocation base

@@ -173,6 +173,15 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
                  "r"(src), "r"(c0), "r"(c1)
                  : "memory");
 }
+/// As `tma_store_2d`, but each element is ADDED into its destination, in the tensor map's own
+/// element type, by the copy engine (reference: `tma_store_add_2d`, src/shared.rs:974-1009).
+/// Same bulk-group completion as a plain store.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+    asm volatile(
+        "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+        "r"(src), "r"(c0), "r"(c1)
+        : "memory");
+}
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1,
                                              int c2) {
     asm volatile(

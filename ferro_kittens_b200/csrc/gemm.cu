@@ -94,6 +94,8 @@ struct Schedule {
     uint32_t k_blocks;   // k / 64
     uint32_t whole;      // leading items that are whole two-half tiles
     uint32_t items;      // whole + 2 * (tiles - whole): the rest are single halves
+    uint32_t idesc;      // tcgen05 instruction descriptor (operand format differs by entry point)
+    uint32_t accumulate; // non-zero: C += A . B^T through the copy engine's reduce-add
 };
 
 struct Item {
@@ -209,7 +211,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     } else if (warp == 1) {
         // ------------------------------------------------ MMA issue (leader only)
         if (rank == 0 && lane == 0) {
-            constexpr uint32_t idesc = instruction_descriptor(2 * kBlockM, kBlockN, false, false);
+            const uint32_t idesc = plan.idesc;
             uint32_t drain = 0, count = 0;
             bool live = true;
             for (uint32_t index = cluster_id_x(); live && index < plan.items;
@@ -336,8 +338,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 fence_proxy_async_shared();
                 __syncwarp();
                 if (lane == 0) {
-                    tma_store_2d(&c_map, band,
-                                 static_cast<int>(item.column + pass * kStageColumns), c_row);
+                    if (plan.accumulate)
+                        tma_reduce_add_2d(&c_map, band,
+                                          static_cast<int>(item.column + pass * kStageColumns), c_row);
+                    else
+                        tma_store_2d(&c_map, band,
+                                     static_cast<int>(item.column + pass * kStageColumns), c_row);
                     tma_store_commit();
                 }
             }
@@ -360,8 +366,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 // The item list of a launch over `clusters` resident clusters: whole [512, 256]
 // tiles, with the last partial wave re-cut into single halves when it holds at
 // most half a wave of tiles (two short half-waves then beat one long one).
-static Schedule schedule(uint32_t m, uint32_t n, uint32_t k, uint32_t group, uint32_t clusters) {
+static Schedule schedule(uint32_t m, uint32_t n, uint32_t k, uint32_t group, uint32_t clusters,
+                         uint32_t flags = 0) {
     Schedule plan;
+    plan.idesc = instruction_descriptor(2 * kBlockM, kBlockN, false, false,
+                                        (flags & FK_GEMM_F16_OPERANDS) ? 0u : 1u);
+    plan.accumulate = (flags & FK_GEMM_ACCUMULATE) ? 1u : 0u;
     plan.m = m;
     plan.tiles_m = (m + kHalves * 2 * kBlockM - 1) / (kHalves * 2 * kBlockM);
     plan.tiles_n = n / kBlockN;
@@ -392,9 +402,11 @@ extern "C" uint32_t fk_gemm_grid(uint32_t m, uint32_t n, uint32_t sm_count) {
     return 2 * (plan.items < clusters ? plan.items : clusters);
 }
 
-extern "C" int fk_gemm_bf16_launch(const void* a_map, const void* b_map, const void* c_map,
-                                   uint32_t m, uint32_t n, uint32_t k, uint32_t group, void* stream,
-                                   uint32_t* device_status) {
+extern "C" int fk_gemm_launch(const void* a_map, const void* b_map, const void* c_map, uint32_t m,
+                              uint32_t n, uint32_t k, uint32_t group, uint32_t flags, void* stream,
+                              uint32_t* device_status) {
+    if (flags & ~(FK_GEMM_F16_OPERANDS | FK_GEMM_ACCUMULATE))
+        return fk_fail(FK_ERR_INVALID, "unknown GEMM flags 0x%x", flags);
     if (!a_map || !b_map || !c_map) return fk_fail(FK_ERR_INVALID, "a tensor map pointer is null");
     if (m == 0 || n == 0 || k == 0 || m % (2 * gemm::kBlockM) || n % gemm::kBlockN ||
         k % gemm::kBlockK)
@@ -412,7 +424,7 @@ extern "C" int fk_gemm_bf16_launch(const void* a_map, const void* b_map, const v
     if (admitted != FK_OK) return admitted;
 
     const uint32_t clusters = static_cast<uint32_t>(sm_count) / 2;
-    const gemm::Schedule plan = gemm::schedule(m, n, k, group, clusters);
+    const gemm::Schedule plan = gemm::schedule(m, n, k, group, clusters, flags);
     const uint32_t grid = 2 * (plan.items < clusters ? plan.items : clusters);
     gemm::gemm_bf16_pair_kernel<<<grid, gemm::kThreads, gemm::kSharedBytes,
                                   static_cast<cudaStream_t>(stream)>>>(
@@ -422,25 +434,31 @@ extern "C" int fk_gemm_bf16_launch(const void* a_map, const void* b_map, const v
     return FK_OK;
 }
 
+extern "C" int fk_gemm_bf16_launch(const void* a_map, const void* b_map, const void* c_map,
+                                   uint32_t m, uint32_t n, uint32_t k, uint32_t group, void* stream,
+                                   uint32_t* device_status) {
+    return fk_gemm_launch(a_map, b_map, c_map, m, n, k, group, 0, stream, device_status);
+}
+
 // The three maps `gemm::run` builds (examples/src/gemm.rs:506-513), plus the
 // store map for C: dims [n, m] with the caller's leading dimension.
 static int gemm_maps(const void* a, const void* b, void* c, uint32_t m, uint32_t n, uint32_t k,
-                     uint32_t ldc, CUtensorMap* maps) {
+                     uint32_t ldc, CUtensorMap* maps, uint32_t operand_element = FK_BF16) {
     fk_layout_t layout;
     const uint64_t a_extents[2] = {k, m}, b_extents[2] = {k, n}, c_extents[2] = {n, m};
     const uint64_t c_strides[2] = {1, ldc};
-    int status = fk_layout_packed(&layout, reinterpret_cast<uint64_t>(a), FK_BF16, 2, a_extents);
+    int status = fk_layout_packed(&layout, reinterpret_cast<uint64_t>(a), operand_element, 2, a_extents);
     if (status == FK_OK) status = fk_tensor_map(&maps[0], &layout, gemm::kBlockK, gemm::kBlockM, FK_SWIZZLE_128B);
-    if (status == FK_OK) status = fk_layout_packed(&layout, reinterpret_cast<uint64_t>(b), FK_BF16, 2, b_extents);
+    if (status == FK_OK) status = fk_layout_packed(&layout, reinterpret_cast<uint64_t>(b), operand_element, 2, b_extents);
     if (status == FK_OK) status = fk_tensor_map(&maps[1], &layout, gemm::kBlockK, gemm::kHalfN, FK_SWIZZLE_128B);
     if (status == FK_OK) status = fk_layout_strided(&layout, reinterpret_cast<uint64_t>(c), FK_BF16, 2, c_extents, c_strides);
     if (status == FK_OK) status = fk_tensor_map(&maps[2], &layout, gemm::kStageColumns, 32, FK_SWIZZLE_128B);
     return status;
 }
 
-extern "C" int fk_gemm_bf16(const void* a, const void* b, void* c, uint32_t m, uint32_t n,
-                            uint32_t k, uint32_t ldc, uint32_t group, void* stream,
-                            uint32_t* device_status) {
+extern "C" int fk_gemm(const void* a, const void* b, void* c, uint32_t m, uint32_t n, uint32_t k,
+                       uint32_t ldc, uint32_t group, uint32_t flags, void* stream,
+                       uint32_t* device_status) {
     if (!a || !b || !c) return fk_fail(FK_ERR_INVALID, "an operand pointer is null");
     if (m == 0 || n == 0 || k == 0 || m % (2 * gemm::kBlockM) || n % gemm::kBlockN ||
         k % gemm::kBlockK)
@@ -448,9 +466,15 @@ extern "C" int fk_gemm_bf16(const void* a, const void* b, void* c, uint32_t m, u
                        2 * gemm::kBlockM, gemm::kBlockN, gemm::kBlockK);
     if (ldc < n) return fk_fail(FK_ERR_SHAPE, "ldc %u is narrower than the %u columns of C", ldc, n);
     alignas(64) CUtensorMap maps[3];
-    const int status = gemm_maps(a, b, c, m, n, k, ldc, maps);
+    const int status = gemm_maps(a, b, c, m, n, k, ldc, maps, (flags & FK_GEMM_F16_OPERANDS) ? FK_F16 : FK_BF16);
     if (status != FK_OK) return status;
-    return fk_gemm_bf16_launch(&maps[0], &maps[1], &maps[2], m, n, k, group, stream, device_status);
+    return fk_gemm_launch(&maps[0], &maps[1], &maps[2], m, n, k, group, flags, stream, device_status);
+}
+
+extern "C" int fk_gemm_bf16(const void* a, const void* b, void* c, uint32_t m, uint32_t n,
+                            uint32_t k, uint32_t ldc, uint32_t group, void* stream,
+                            uint32_t* device_status) {
+    return fk_gemm(a, b, c, m, n, k, ldc, group, 0, stream, device_status);
 }
 
 extern "C" int fk_gemm_bf16_host(const uint16_t* a_host, const uint16_t* b_host, uint16_t* c_host,

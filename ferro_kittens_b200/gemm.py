@@ -16,6 +16,10 @@ BLOCK_N = 256
 BLOCK_K = 64
 #: The traversal width the reference ships (examples/src/gemm.rs:138).
 GROUP = 8
+#: fp16 A and B (C stays bf16): the operand types of examples/src/gemm_sol.rs.
+F16_OPERANDS = 1
+#: C += A . B^T through the copy engine's reduce-add (src/shared.rs:974-1009).
+ACCUMULATE = 2
 
 
 def tile_grid(m: int, n: int) -> tuple[int, int]:
@@ -57,21 +61,34 @@ def launch(a_map, b_map, c_map, m: int, n: int, k: int, group: int = GROUP, stat
 
 
 def run(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor | None = None, group: int = GROUP,
-        status: torch.Tensor | None = None) -> torch.Tensor:
-    """``C[m, n] = sum_k A[m, k] * B[n, k]``; A is [m, k], B is [n, k], both bf16 on one GPU."""
-    _require_cuda_bf16("a", a)
-    _require_cuda_bf16("b", b)
+        status: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+    """``C[m, n] (+)= sum_k A[m, k] * B[n, k]``; A is [m, k], B is [n, k], both bf16 or both fp16 on
+    one GPU, C bf16. With ``accumulate`` the rounded product is added into ``c`` (in bf16, by the
+    copy engine), which must then be given and hold values."""
+    for name, tensor in (("a", a), ("b", b)):
+        if not tensor.is_cuda:
+            raise RuntimeError(f"{name} must live on a CUDA device: there is no CPU path")
+        if tensor.dtype not in (torch.bfloat16, torch.float16) or not tensor.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous bfloat16 or float16 tensor")
+    if a.dtype != b.dtype:
+        raise ValueError("a and b must share one element type")
     m, k = a.shape
     n = b.shape[0]
     if b.shape[1] != k:
         raise ValueError("a and b disagree on K")
     if c is None:
+        if accumulate:
+            raise ValueError("accumulating needs the C to add into")
         c = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
-    _require_cuda_bf16("c", c)
+    if not c.is_cuda:
+        raise RuntimeError("c must live on a CUDA device: there is no CPU path")
+    if c.dtype != torch.bfloat16 or c.dim() != 2 or c.stride(1) != 1 or c.shape != (m, n):
+        raise ValueError("c must be an [m, n] bfloat16 tensor with unit column stride (rows may be padded)")
+    flags = (F16_OPERANDS if a.dtype == torch.float16 else 0) | (ACCUMULATE if accumulate else 0)
     with torch.cuda.device(a.device):
         handle = torch.cuda.current_stream().cuda_stream
-        check(library().fk_gemm_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, c.stride(0),
-                                     group, handle, status.data_ptr() if status is not None else None))
+        check(library().fk_gemm(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, c.stride(0), group,
+                                flags, handle, status.data_ptr() if status is not None else None))
     return c
 
 

@@ -156,6 +156,23 @@ int fk_gemm_bf16_launch(const void* a_map, const void* b_map, const void* c_map,
 int fk_gemm_bf16(const void* a, const void* b, void* c, uint32_t m, uint32_t n, uint32_t k,
                  uint32_t ldc, uint32_t group, void* stream, uint32_t* device_status);
 
+/* The same kernel behind two switches, for the callers next to the path:
+ *   FK_GEMM_F16_OPERANDS  A and B are fp16 (maps built with FK_F16), C stays bf16: the operand
+ *                         types of `gemm_sol` (examples/src/gemm_sol.rs:6-8, 202-207), whose
+ *                         [512, 256] cluster tile is this kernel's own.
+ *   FK_GEMM_ACCUMULATE    C += A.B^T: the epilogue's stores become the copy engine's
+ *                         reduce-add (`tma_store_add_2d`, src/shared.rs:974-1009;
+ *                         `commit_add_2d`, src/epilogue.rs:789-812): the rounded bf16 tile is
+ *                         added into C in bf16, C is never read by a thread, and C must hold
+ *                         values beforehand.
+ * fk_gemm_bf16_launch / fk_gemm_bf16 are these with flags = 0. */
+#define FK_GEMM_F16_OPERANDS 1u
+#define FK_GEMM_ACCUMULATE 2u
+int fk_gemm_launch(const void* a_map, const void* b_map, const void* c_map, uint32_t m, uint32_t n,
+                   uint32_t k, uint32_t group, uint32_t flags, void* stream, uint32_t* device_status);
+int fk_gemm(const void* a, const void* b, void* c, uint32_t m, uint32_t n, uint32_t k, uint32_t ldc,
+            uint32_t group, uint32_t flags, void* stream, uint32_t* device_status);
+
 /* The whole of `gemm::run` from HOST buffers (:503-537): stage A and B, launch,
  * read C back; blocks until C is on the host. Device buffers are cached per
  * device and grown on demand. */

@@ -185,12 +185,22 @@ inline uint32_t grid(uint32_t m, uint32_t n, uint32_t sm_count = 148) { return f
 
 /// `gemm::run` between staging and read-back (examples/src/gemm.rs:506-536): build the maps,
 /// launch on `stream`. `status` is null or 4 zeroed device words (see fk_status_check).
+/// `flags`: FK_GEMM_F16_OPERANDS for fp16 A and B (examples/src/gemm_sol.rs), FK_GEMM_ACCUMULATE
+/// for C += A.B^T through the copy engine's reduce-add (src/shared.rs:974-1009).
 inline void run(void* stream, uint64_t a, uint64_t b, uint64_t c, uint32_t m, uint32_t n, uint32_t k,
-                uint32_t group = GROUP, uint32_t* status = nullptr) {
-    const auto a_map = global::GlobalLayout<shared::Bf16, 2>::packed(a, {k, m}).tensor_map<ATile>();
-    const auto b_map = global::GlobalLayout<shared::Bf16, 2>::packed(b, {k, n}).tensor_map<BTile>();
+                uint32_t group = GROUP, uint32_t* status = nullptr, uint32_t flags = 0) {
+    global::TensorMap a_map, b_map;
+    if (flags & FK_GEMM_F16_OPERANDS) {
+        using A16 = shared::SharedTile<shared::F16, BLOCK_M, BLOCK_K>;
+        using B16 = shared::SharedTile<shared::F16, HALF_N, BLOCK_K>;
+        a_map = global::GlobalLayout<shared::F16, 2>::packed(a, {k, m}).tensor_map<A16>();
+        b_map = global::GlobalLayout<shared::F16, 2>::packed(b, {k, n}).tensor_map<B16>();
+    } else {
+        a_map = global::GlobalLayout<shared::Bf16, 2>::packed(a, {k, m}).tensor_map<ATile>();
+        b_map = global::GlobalLayout<shared::Bf16, 2>::packed(b, {k, n}).tensor_map<BTile>();
+    }
     const auto c_map = global::GlobalLayout<shared::Bf16, 2>::packed(c, {n, m}).tensor_map<CStage>();
-    check(fk_gemm_bf16_launch(a_map.as_ptr(), b_map.as_ptr(), c_map.as_ptr(), m, n, k, group, stream, status));
+    check(fk_gemm_launch(a_map.as_ptr(), b_map.as_ptr(), c_map.as_ptr(), m, n, k, group, flags, stream, status));
 }
 
 }  // namespace gemm

@@ -32,6 +32,12 @@ _lib.fko_gemm_b_value.argtypes = [c_size_t, c_size_t]
 _lib.fko_gemm_b_value.restype = c_float
 _lib.fko_gemm_stage.argtypes = [c_int, c_size_t, c_size_t, _u16p]
 _lib.fko_gemm_stage.restype = None
+_lib.fko_to_f16.argtypes = [c_float]
+_lib.fko_to_f16.restype = c_uint16
+_lib.fko_bf16_add.argtypes = [c_uint16, c_uint16]
+_lib.fko_bf16_add.restype = c_uint16
+_lib.fko_gemm_stage_f16.argtypes = [c_int, c_size_t, c_size_t, _u16p]
+_lib.fko_gemm_stage_f16.restype = None
 _lib.fko_gemm_check_c.argtypes = [_u16p, c_size_t, c_size_t, c_size_t, POINTER(c_double), POINTER(c_size_t)]
 _lib.fko_gemm_check_c.restype = c_size_t
 _lib.fko_gemm_expected.argtypes = [c_size_t, c_size_t, c_size_t]
@@ -96,6 +102,39 @@ def gemm_stage(which: str, rows: int, k: int) -> np.ndarray:
     out = np.empty((rows, k), dtype=np.uint16)
     _lib.fko_gemm_stage(0 if which == "a" else 1, rows, k, out)
     return out
+
+
+def gemm_stage_f16(which: str, rows: int, k: int) -> np.ndarray:
+    """The same operand as [rows, k] fp16 words (examples/src/gemm_sol.rs:1241-1249)."""
+    out = np.empty((rows, k), dtype=np.uint16)
+    _lib.fko_gemm_stage_f16(0 if which == "a" else 1, rows, k, out)
+    return out
+
+
+def to_f16(value: float) -> int:
+    return _lib.fko_to_f16(value)
+
+
+def bf16_add(held: int, added: int) -> int:
+    """What a bf16 reduce-add leaves: the exact sum rounded once to bf16."""
+    return _lib.fko_bf16_add(held, added)
+
+
+def bf16_add_words(held: np.ndarray, added: np.ndarray) -> np.ndarray:
+    """``bf16_add`` over arrays: exact sum in float64, one round-to-nearest-even to bf16."""
+    total = bf16_to_f32(held).astype(np.float64) + bf16_to_f32(added).astype(np.float64)
+    bits = total.view(np.uint64)
+    sign = (bits >> np.uint64(63)).astype(np.uint32)
+    exponent = ((bits >> np.uint64(52)) & np.uint64(0x7FF)).astype(np.int64) - 1023
+    mantissa = bits & np.uint64((1 << 52) - 1)
+    kept = (mantissa >> np.uint64(45)).astype(np.uint32)
+    rest = mantissa & np.uint64((1 << 45) - 1)
+    up = (rest > np.uint64(1 << 44)) | ((rest == np.uint64(1 << 44)) & ((kept & 1) == 1))
+    combined = ((exponent + 127).astype(np.uint32) << 7) + kept + up.astype(np.uint32)  # a carry bumps the exponent
+    out = (sign << 15) | combined
+    out = np.where(total == 0.0, sign << 15, out)
+    assert np.all((exponent >= -126) & (exponent <= 126) | (total == 0.0)), "outside the range this helper covers"
+    return out.astype(np.uint16)
 
 
 def gemm_check_c(observed: np.ndarray, m: int, n: int, k: int) -> tuple[int, float, int]:

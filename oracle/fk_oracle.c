@@ -59,6 +59,57 @@ float fko_from_bf16(uint16_t bits) {
     return value;
 }
 
+/* Round-to-nearest-even fp32 -> fp16 (IEEE binary16), what `half::f16::from_f32` does for the
+ * operands of examples/src/gemm_sol.rs:1241-1249. Handles normals, subnormals, overflow to
+ * infinity and NaN. */
+uint16_t fko_to_f16(float value) {
+    uint32_t bits;
+    memcpy(&bits, &value, 4);
+    const uint32_t sign = (bits >> 16) & 0x8000u;
+    const uint32_t magnitude = bits & 0x7fffffffu;
+    if (magnitude >= 0x7f800000u) return (uint16_t)(sign | 0x7c00u | (magnitude > 0x7f800000u ? 0x200u : 0u));
+    if (magnitude >= 0x477ff000u) return (uint16_t)(sign | 0x7c00u); /* rounds to >= 65520: infinity */
+    if (magnitude < 0x38800000u) {                                   /* below 2^-14: subnormal */
+        if (magnitude < 0x33000000u) return (uint16_t)sign;          /* below 2^-25: zero */
+        const uint32_t shift = 126u - (magnitude >> 23);             /* 14..24 */
+        const uint32_t mantissa = (magnitude & 0x7fffffu) | 0x800000u;
+        const uint32_t kept = mantissa >> shift;
+        const uint32_t rest = mantissa & ((1u << shift) - 1u), halfway = 1u << (shift - 1u);
+        return (uint16_t)(sign | (kept + ((rest > halfway || (rest == halfway && (kept & 1u))) ? 1u : 0u)));
+    }
+    const uint32_t rebased = magnitude - 0x38000000u; /* exponent bias 127 -> 15 */
+    const uint32_t kept = rebased >> 13, rest = rebased & 0x1fffu;
+    return (uint16_t)(sign | (kept + ((rest > 0x1000u || (rest == 0x1000u && (kept & 1u))) ? 1u : 0u)));
+}
+
+/* What the copy engine's reduce-add leaves in a bf16 destination: the sum of the two bf16
+ * values rounded once to bf16 (`tma_store_add_2d`, src/shared.rs:974-1009: "the add happens at
+ * the destination in the element's own type ... with round-to-nearest"). The sum is formed in
+ * double, where it is exact for operands within 2^40 of each other. */
+uint16_t fko_bf16_add(uint16_t held, uint16_t added) {
+    const double sum = (double)fko_from_bf16(held) + (double)fko_from_bf16(added);
+    /* double -> bf16 in one rounding: go through the bit pattern of the double. */
+    uint64_t bits;
+    memcpy(&bits, &sum, 8);
+    const uint64_t sign = bits >> 63;
+    const int64_t exponent = (int64_t)((bits >> 52) & 0x7ff) - 1023;
+    if (sum == 0.0) return (uint16_t)(sign << 15);
+    if (exponent > 127) return (uint16_t)((sign << 15) | 0x7f80u);
+    if (exponent < -126) return fko_to_bf16((float)sum); /* subnormal range: not reached by the tests */
+    const uint64_t mantissa = bits & 0xfffffffffffffull; /* 52 bits; keep 7 */
+    uint64_t kept = mantissa >> 45;
+    const uint64_t rest = mantissa & ((1ull << 45) - 1), halfway = 1ull << 44;
+    uint64_t biased = (uint64_t)(exponent + 127);
+    if (rest > halfway || (rest == halfway && (kept & 1))) {
+        if (++kept == 128) {
+            kept = 0;
+            ++biased;
+        }
+    }
+    if (biased >= 255) return (uint16_t)((sign << 15) | 0x7f80u);
+    return (uint16_t)((sign << 15) | (biased << 7) | kept);
+}
+
 /* ---------------------------------------------------------------- GEMM operands */
 
 /* examples/src/gemm.rs:434-436 */
@@ -77,6 +128,15 @@ void fko_gemm_stage(int which, size_t rows, size_t k, uint16_t* out) {
         for (size_t depth = 0; depth < k; ++depth)
             out[row * k + depth] =
                 fko_to_bf16(which == 0 ? fko_gemm_a_value(row, depth) : fko_gemm_b_value(row, depth));
+}
+
+/* examples/src/gemm_sol.rs:1241-1249 -- the same operands staged as fp16 words. */
+void fko_gemm_stage_f16(int which, size_t rows, size_t k, uint16_t* out) {
+#pragma omp parallel for schedule(static)
+    for (size_t row = 0; row < rows; ++row)
+        for (size_t depth = 0; depth < k; ++depth)
+            out[row * k + depth] =
+                fko_to_f16(which == 0 ? fko_gemm_a_value(row, depth) : fko_gemm_b_value(row, depth));
 }
 
 /* examples/src/gemm.rs:544-578 -- compare an observed bf16 C element by element

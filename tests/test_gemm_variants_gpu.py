@@ -1,0 +1,104 @@
+"""The GEMM's two switches for the callers next to the path: fp16 operands (the operand types of
+examples/src/gemm_sol.rs, checked the way its `check` does, :1382-1392) and `C += A.B^T` through the
+copy engine's reduce-add (src/shared.rs:974-1009). All through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from ferro_kittens_b200 import FerroKittensError, gemm
+from ferro_kittens_b200._lib import check, library
+
+pytestmark = pytest.mark.gpu
+
+
+def _device_words(words: np.ndarray, device, dtype) -> torch.Tensor:
+    return torch.from_numpy(words.view(np.int16)).to(device).view(dtype)
+
+
+def _words(tensor: torch.Tensor) -> np.ndarray:
+    return tensor.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def _run(a, b, c=None, accumulate=False):
+    status = gemm.new_status(a.device)
+    c = gemm.run(a, b, c, status=status, accumulate=accumulate)
+    torch.cuda.synchronize(a.device)
+    gemm.check_status(status)
+    return c
+
+
+# gemm_sol::check: every variant at 1024 x 1024 x 512, then the shallow-K gate (:1371-1380).
+@pytest.mark.parametrize("shape", [(1024, 1024, 512), (2048, 2048, 256), (2560, 2048, 256), (5120, 2048, 256)])
+def test_fp16_operands_are_exact_on_the_reference_gate(device, shape):
+    m, n, k = shape
+    a = _device_words(oracle.gemm_stage_f16("a", m, k), device, torch.float16)
+    b = _device_words(oracle.gemm_stage_f16("b", n, k), device, torch.float16)
+    c = _run(a, b)
+    wrong, worst, first = oracle.gemm_check_c(_words(c), m, n, k)
+    assert wrong == 0, f"{wrong} of {m * n} wrong, first at {first}"
+
+
+def test_fp16_operands_random_within_tolerance(device):
+    m, n, k = 1024, 768, 1088
+    generator = torch.Generator(device="cpu").manual_seed(11)
+    a = (torch.rand((m, k), generator=generator) * 2 - 1).to(torch.float16).to(device)
+    b = (torch.rand((n, k), generator=generator) * 2 - 1).to(torch.float16).to(device)
+    c = _run(a, b)
+    reference = a.double() @ b.double().T
+    # BASELINE's GEMM bound: 1e-2 * sqrt(K) * max|a| * max|b|.
+    assert (c.double() - reference).abs().max().item() <= 1e-2 * k ** 0.5
+
+
+def test_mixed_operand_types_are_refused(device):
+    a = torch.zeros((256, 64), dtype=torch.float16, device=device)
+    b = torch.zeros((256, 64), dtype=torch.bfloat16, device=device)
+    with pytest.raises(ValueError, match="share one element type"):
+        gemm.run(a, b)
+
+
+@pytest.mark.parametrize("operands", ["bf16", "f16"])
+def test_accumulate_adds_the_rounded_product_in_bf16(device, operands):
+    m, n, k = 1024, 512, 256
+    if operands == "bf16":
+        a = _device_words(oracle.gemm_stage("a", m, k), device, torch.bfloat16)
+        b = _device_words(oracle.gemm_stage("b", n, k), device, torch.bfloat16)
+    else:
+        a = _device_words(oracle.gemm_stage_f16("a", m, k), device, torch.float16)
+        b = _device_words(oracle.gemm_stage_f16("b", n, k), device, torch.float16)
+    product = np.array([[oracle.gemm_expected(r, c, k) for c in range(21)] for r in range(7)], dtype=np.uint16)
+    product = product[np.arange(m)[:, None] % 7, np.arange(n)[None, :] % 21]
+    rows, columns = np.meshgrid(np.arange(m), np.arange(n), indexing="ij")
+    held = oracle.f32_to_bf16(((rows * 3 + columns * 5) % 37 - 18).astype(np.float32) * 0.75)
+    c = _device_words(held.copy(), device, torch.bfloat16)
+    _run(a, b, c, accumulate=True)
+    once = oracle.bf16_add_words(held, product)
+    assert np.array_equal(_words(c), once)
+    _run(a, b, c, accumulate=True)
+    assert np.array_equal(_words(c), oracle.bf16_add_words(once, product))
+    # Spot-check the vectorised expectation against the scalar C restatement.
+    for r, col in ((0, 0), (5, 20), (1023, 511), (512, 77)):
+        assert once[r, col] == oracle.bf16_add(int(held[r, col]), int(product[r, col]))
+
+
+def test_accumulate_respects_the_leading_dimension(device):
+    m, n, k, ldc = 512, 256, 128, 384
+    a = _device_words(oracle.gemm_stage("a", m, k), device, torch.bfloat16)
+    b = _device_words(oracle.gemm_stage("b", n, k), device, torch.bfloat16)
+    whole = torch.full((m, ldc), 2.0, dtype=torch.bfloat16, device=device)
+    _run(a, b, whole[:, :n], accumulate=True)
+    assert torch.all(whole[:, n:] == 2.0)
+    product = np.array([[oracle.gemm_expected(r, c, k) for c in range(21)] for r in range(7)], dtype=np.uint16)
+    product = product[np.arange(m)[:, None] % 7, np.arange(n)[None, :] % 21]
+    two = np.full((m, n), oracle.to_bf16(2.0), dtype=np.uint16)
+    assert np.array_equal(_words(whole[:, :n]), oracle.bf16_add_words(two, product))
+
+
+def test_unknown_flags_and_missing_c_are_refused(device):
+    a = torch.zeros((256, 64), dtype=torch.bfloat16, device=device)
+    with pytest.raises(ValueError, match="needs the C"):
+        gemm.run(a, a, accumulate=True)
+    c = torch.zeros((256, 256), dtype=torch.bfloat16, device=device)
+    with pytest.raises(FerroKittensError, match="unknown GEMM flags"):
+        check(library().fk_gemm(a.data_ptr(), a.data_ptr(), c.data_ptr(), 256, 256, 64, 256, 8, 4,
+                                torch.cuda.current_stream().cuda_stream, None))

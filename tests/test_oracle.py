@@ -119,3 +119,33 @@ def test_flash_rows_agree_with_a_dense_numpy_softmax():
         dense = weights @ oracle.bf16_to_f32(v).astype(np.float64) / weights.sum(axis=1, keepdims=True)
         assert np.allclose(out, dense, rtol=1e-10, atol=1e-12)
         assert np.allclose(lse, (top + np.log(weights.sum(axis=1, keepdims=True)))[:, 0], rtol=1e-12)
+
+
+def test_fp16_rounding_known_answers():
+    """`half::f16::from_f32` (examples/src/gemm_sol.rs:1245): round to nearest even, with the
+    format's overflow and subnormal edges; and the whole operand range against numpy."""
+    cases = {1.0: 0x3C00, -2.0: 0xC000, 65504.0: 0x7BFF, 65519.0: 0x7BFF, 65520.0: 0x7C00, 1e10: 0x7C00,
+             2.0 ** -24: 0x0001, 2.0 ** -25: 0x0000, 1.5 * 2.0 ** -24: 0x0002, 2.0 ** -14: 0x0400,
+             1.0 + 2.0 ** -11: 0x3C00, 1.0 + 3 * 2.0 ** -11: 0x3C02, 0.0: 0x0000}
+    for value, bits in cases.items():
+        assert oracle.to_f16(value) == bits, value
+    values = np.arange(-10, 11, dtype=np.float32)
+    assert [oracle.to_f16(float(v)) for v in values] == list(values.astype(np.float16).view(np.uint16))
+    staged = oracle.gemm_stage_f16("b", 32, 64)
+    expected = np.array([[oracle.gemm_b_value(r, d) for d in range(64)] for r in range(32)], dtype=np.float16)
+    assert np.array_equal(staged, expected.view(np.uint16))
+
+
+def test_bf16_add_rounds_the_exact_sum_once():
+    """What a bf16 reduce-add leaves (src/shared.rs:974-1009): spacing at 256 is 2, ties go to even."""
+    word = oracle.to_bf16
+    assert oracle.bf16_add(word(1.0), word(1.0)) == word(2.0)
+    assert oracle.bf16_add(word(256.0), word(1.0)) == word(256.0)   # 257 ties to the even 256
+    assert oracle.bf16_add(word(256.0), word(3.0)) == word(260.0)   # 259 ties to the even 260
+    assert oracle.bf16_add(word(258.0), word(1.0)) == word(260.0)
+    assert oracle.bf16_add(word(-4.0), word(4.0)) == 0
+    assert oracle.bf16_add(word(255.0), word(1.0)) == word(256.0)   # a carry into the exponent
+    held = np.array([word(v) for v in (1.0, 256.0, 256.0, -4.0, 255.0, 0.75)], dtype=np.uint16)
+    added = np.array([word(v) for v in (1.0, 1.0, 3.0, 4.0, 1.0, 1000.0)], dtype=np.uint16)
+    scalar = [oracle.bf16_add(int(h), int(a)) for h, a in zip(held, added)]
+    assert list(oracle.bf16_add_words(held, added)) == scalar
