@@ -33,6 +33,9 @@ GEMM_SEED = 1
 FLASH = dict(batch=16, heads=16, seq=4096, head_dim=128, seed=3, causal=False)
 WORKLOAD = "gemm_bf16_16384x16384x16384_normal_over_sqrtK_seed1"
 METRIC = "bf16_gemm_tflops_16384"
+#: 4 Mi rows x 128 bf16 = 1 GiB in and 1 GiB out per launch, far larger than the L2.
+ROW_KERNEL_ROWS = 4 * 1024 * 1024
+ROW_KERNEL_SEED = 5
 
 
 def env_int(name: str, default: int) -> int:
@@ -291,6 +294,40 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     flash_value = flash_flops * args.steps / flash_seconds / 1e12
     del qkv, out, lse
 
+    # ---- the row kernels either side of the two contractions: rows split across ranks, HBM roofline
+    from ferro_kittens_b200 import rows as row_kernels
+
+    rows_total = ROW_KERNEL_ROWS
+    r0, r1 = rows_total * rank // world, rows_total * (rank + 1) // world
+    r0, r1 = r0 // 128 * 128, r1 // 128 * 128
+    generator = torch.Generator(device=device).manual_seed(ROW_KERNEL_SEED)
+    activations = (torch.randn((r1 - r0, 128), generator=generator, device=device) * 2).to(torch.bfloat16)
+    normalised = torch.empty_like(activations)
+    ones = torch.ones(128, dtype=torch.bfloat16, device=device)
+    zeros = torch.zeros(128, dtype=torch.bfloat16, device=device)
+    row_status = gemm.new_status(device)
+    row_results = {}
+    for name, call in (("softmax_rows", lambda: row_kernels.softmax_rows(activations, out=normalised, status=row_status)),
+                       ("layernorm_rows", lambda: row_kernels.layernorm_rows(activations, ones, zeros, 1e-5,
+                                                                              out=normalised, status=row_status)),
+                       ("groupnorm_tile", lambda: row_kernels.groupnorm_tile(activations, 1e-5, out=normalised,
+                                                                             status=row_status))):
+        call()
+        gemm.check_status(row_status)
+        if name == "softmax_rows":
+            drift = (normalised[:4096].float().sum(dim=1) - 1).abs().max().item()
+        elif name == "layernorm_rows":
+            drift = normalised[:4096].float().mean(dim=1).abs().max().item()
+        else:
+            drift = abs(normalised[:128].float().mean().item())
+        if not drift <= 2e-2:
+            raise RuntimeError(f"{name} fails its row property: {drift}")
+        row_seconds = max_over_ranks(time_steps(call, args.steps, args.warmup, barrier))
+        gbs = 4.0 * rows_total * 128 * args.steps / row_seconds / 1e9
+        row_results[name] = {"value": gbs, "unit": "GB/s", "ms_per_step": row_seconds / args.steps * 1e3,
+                             "frac_of_measured_hbm": gbs / world / peaks["hbm"]}
+    del activations, normalised
+
     # ---- end to end: host buffers through the C-ABI call, copies inside the timed region
     e2e_steps = 3
     host_a = torch.empty((M, K), dtype=torch.bfloat16).pin_memory()
@@ -352,6 +389,9 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                           "frac_of_measured_peak": flash_value / world / peaks["burst"],
                           "frac_of_nominal_2250": flash_value / world / 2250.0,
                           "max_abs_diff_vs_sdpa": flash_error},
+            "row_kernels": {"config": {"rows": rows_total, "columns": 128, "seed": ROW_KERNEL_SEED,
+                                       "bytes_per_element": 4, "sharding": f"rows over {world} rank(s)"},
+                            "peak": peaks["hbm"], "peak_unit": "GB/s", "peak_source": peaks["source"], **row_results},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "call": "fk_gemm_bf16_host"},
             "gpu_launches": args.steps,
@@ -385,6 +425,23 @@ def run_only(args, local_rank: int) -> None:
         fn = lambda: gemm.launch(a_map, b_map, c_map, m, n, k, args.group, status)  # noqa: E731
         flops = 2.0 * m * n * k
         name = f"gemm_bf16_{m}x{n}x{k}"
+    elif args.only in ("softmax", "layernorm", "groupnorm"):
+        from ferro_kittens_b200 import rows as row_kernels
+
+        generator = torch.Generator(device=device).manual_seed(ROW_KERNEL_SEED)
+        x = (torch.randn((args.rows, 128), generator=generator, device=device) * 2).to(torch.bfloat16)
+        y = torch.empty_like(x)
+        ones = torch.ones(128, dtype=torch.bfloat16, device=device)
+        zeros = torch.zeros(128, dtype=torch.bfloat16, device=device)
+        fn = {"softmax": lambda: row_kernels.softmax_rows(x, out=y, status=status),
+              "layernorm": lambda: row_kernels.layernorm_rows(x, ones, zeros, 1e-5, out=y, status=status),
+              "groupnorm": lambda: row_kernels.groupnorm_tile(x, 1e-5, out=y, status=status)}[args.only]
+        seconds = time_steps(fn, args.steps, args.warmup, lambda: None)
+        gemm.check_status(status)
+        print(json.dumps({"only": f"{args.only}_rows{args.rows}", "steps": args.steps,
+                          "ms_per_step": seconds / args.steps * 1e3,
+                          "gbs": 4.0 * args.rows * 128 * args.steps / seconds / 1e9}), flush=True)
+        return
     else:
         planes, seq = args.planes, args.seq
         generator = torch.Generator(device=device).manual_seed(FLASH["seed"])
@@ -405,7 +462,9 @@ def run_only(args, local_rank: int) -> None:
 
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--only", choices=["gemm", "flash"], help="run one kernel alone (for profiling)")
+    parser.add_argument("--only", choices=["gemm", "flash", "softmax", "layernorm", "groupnorm"],
+                        help="run one kernel alone (for profiling)")
+    parser.add_argument("--rows", type=int, default=1 << 20, help="rows of 128 columns for the row kernels")
     parser.add_argument("--m", type=int, default=8192)
     parser.add_argument("--n", type=int, default=8192)
     parser.add_argument("--k", type=int, default=8192)

@@ -94,6 +94,11 @@ SIGNATURES = {
                              c_uint32, c_float, c_int, c_void_p, c_void_p]),
     "fk_flash_fwd_host": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_uint32,
                                   c_uint32, c_float, c_int]),
+    "fk_rows_shared_bytes": (c_uint32, []),
+    "fk_rows_threads": (c_uint32, []),
+    "fk_softmax_rows": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, c_void_p, c_void_p]),
+    "fk_layernorm_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_uint32, c_float, c_void_p, c_void_p]),
+    "fk_groupnorm_tile": (c_int, [c_void_p, c_void_p, c_uint32, c_float, c_void_p, c_void_p]),
     "fk_wait_stream": (c_int, [c_void_p, c_uint32]),
     "fk_wait_event": (c_int, [c_void_p, c_uint32]),
     "fk_status_check": (c_int, [c_void_p, c_void_p]),

@@ -319,6 +319,9 @@ static const char* stall_role(uint32_t code) {
         case 0x1ff: return "gemm found its shared memory base off a 1024-byte boundary";
         case 0x2ff: return "flash found its shared memory base off a 1024-byte boundary";
         case 0x301: return "self-test wait on a barrier nothing arrives on";
+        case 0x312: return "row-kernel copy warp waiting for the compute warps to finish a tile";
+        case 0x313: return "row-kernel compute warp waiting for a tile to land";
+        case 0x314: return "row-kernel compute warp waiting for the other warps' partial sums";
         default: return "unknown role";
     }
 }

@@ -219,6 +219,32 @@ int fk_flash_fwd_host(const uint16_t* q_host, const uint16_t* k_host, const uint
                       uint16_t* o_host, float* lse_host, uint32_t planes, uint32_t seq, float scale,
                       int causal);
 
+/* ---------------------------------------------------------------- row kernels
+ *
+ * The memory-bound kernels either side of attention and GEMM, over rows of 128 bf16 columns
+ * (row-major, packed; 16-byte aligned buffers; `destination` may equal `source`). The
+ * reference launches them with tensor maps over [128, 128] tiles; these entries take the
+ * buffers themselves because a tile of whole rows is contiguous and moves by bulk copy.
+ * `device_status` as for the GEMM. Asynchronous on `stream`.
+ *
+ * fk_softmax_rows:   `kernels::softmax_rows` (examples/src/softmax.rs:176-186, run :215-300):
+ *                    y = 2^(x - max(x)) / sum, per row of [planes, rows_per_plane, 128];
+ *                    rows_per_plane % 128 == 0.
+ * fk_layernorm_rows: `kernels::layernorm_rows` (examples/src/layernorm.rs:140-214):
+ *                    y = gamma * (x - mean) / sqrt(var + epsilon) + beta per row of [rows, 128];
+ *                    gamma, beta [128] bf16; rows % 128 == 0.
+ * fk_groupnorm_tile: `kernels::groupnorm_tile` (examples/src/layernorm.rs:232-306):
+ *                    y = (x - mean) / sqrt(var + epsilon) with the statistics of each
+ *                    [128, 128] tile of [rows, 128]; rows % 128 == 0. */
+uint32_t fk_rows_shared_bytes(void);
+uint32_t fk_rows_threads(void);
+int fk_softmax_rows(const void* source, void* destination, uint32_t rows_per_plane, uint32_t planes,
+                    void* stream, uint32_t* device_status);
+int fk_layernorm_rows(const void* source, const void* gamma, const void* beta, void* destination,
+                      uint32_t rows, float epsilon, void* stream, uint32_t* device_status);
+int fk_groupnorm_tile(const void* source, void* destination, uint32_t rows, float epsilon,
+                      void* stream, uint32_t* device_status);
+
 /* ---------------------------------------------------------------- waits and status
  *
  * `watchdog::wait` / `wait_event` (src/watchdog.rs:300-332): poll with a

@@ -53,6 +53,28 @@ _lib.fko_flash_stage.argtypes = [c_int, c_size_t, c_size_t, _u16p]
 _lib.fko_flash_stage.restype = None
 _lib.fko_flash_rows.argtypes = [_u16p, _u16p, _u16p, c_size_t, c_size_t, c_size_t, c_double, c_int, _f64p, ctypes.c_void_p]
 _lib.fko_flash_rows.restype = None
+_lib.fko_softmax_input.argtypes = [c_size_t] * 3
+_lib.fko_softmax_input.restype = c_float
+_lib.fko_softmax_expected.argtypes = [c_size_t] * 3
+_lib.fko_softmax_expected.restype = c_double
+_lib.fko_softmax_stage.argtypes = [c_size_t, c_size_t, _u16p]
+_lib.fko_softmax_stage.restype = None
+_lib.fko_softmax_rows.argtypes = [_u16p, c_size_t, _f64p]
+_lib.fko_softmax_rows.restype = None
+_lib.fko_layernorm_value.argtypes = [c_size_t, c_size_t]
+_lib.fko_layernorm_value.restype = c_float
+_lib.fko_layernorm_input.argtypes = [c_size_t, c_size_t]
+_lib.fko_layernorm_input.restype = c_float
+_lib.fko_layernorm_gamma.argtypes = [c_size_t]
+_lib.fko_layernorm_gamma.restype = c_float
+_lib.fko_layernorm_beta.argtypes = [c_size_t]
+_lib.fko_layernorm_beta.restype = c_float
+_lib.fko_layernorm_stage.argtypes = [c_size_t, _u16p, _u16p, _u16p]
+_lib.fko_layernorm_stage.restype = None
+_lib.fko_layernorm_rows.argtypes = [_u16p, _u16p, _u16p, c_size_t, c_double, _f64p]
+_lib.fko_layernorm_rows.restype = None
+_lib.fko_groupnorm_tiles.argtypes = [_u16p, c_size_t, c_double, _f64p]
+_lib.fko_groupnorm_tiles.restype = None
 
 
 def threads() -> int:
@@ -180,3 +202,46 @@ def flash_rows(q: np.ndarray, k: np.ndarray, v: np.ndarray, row0: int, rows: int
     lse = np.empty(rows, dtype=np.float64)
     _lib.fko_flash_rows(q, k, v, sequence, row0, rows, scale, int(causal), out, lse.ctypes.data)
     return out, lse
+
+
+def softmax_stage(rows: int, planes: int) -> np.ndarray:
+    """The reference's softmax seed as [planes, rows, 128] bf16 words (examples/src/softmax.rs:195-215)."""
+    out = np.empty((planes, rows, 128), dtype=np.uint16)
+    _lib.fko_softmax_stage(rows, planes, out)
+    return out
+
+
+def softmax_expected(plane: int, row: int, column: int) -> float:
+    return _lib.fko_softmax_expected(plane, row, column)
+
+
+def softmax_rows(x: np.ndarray) -> np.ndarray:
+    """f64 base-2 softmax over the last axis (128) of bf16 words."""
+    x = np.ascontiguousarray(x, dtype=np.uint16)
+    out = np.empty(x.shape, dtype=np.float64)
+    _lib.fko_softmax_rows(x.reshape(-1, 128), x.size // 128, out.reshape(-1, 128))
+    return out
+
+
+def layernorm_stage(rows: int):
+    """The reference's layernorm seed: (x [rows, 128], gamma [128], beta [128]) as bf16 words."""
+    x = np.empty((rows, 128), dtype=np.uint16)
+    gamma = np.empty(128, dtype=np.uint16)
+    beta = np.empty(128, dtype=np.uint16)
+    _lib.fko_layernorm_stage(rows, x, gamma, beta)
+    return x, gamma, beta
+
+
+def layernorm_rows(x: np.ndarray, gamma: np.ndarray, beta: np.ndarray, epsilon: float) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.uint16).reshape(-1, 128)
+    out = np.empty(x.shape, dtype=np.float64)
+    _lib.fko_layernorm_rows(x, np.ascontiguousarray(gamma, dtype=np.uint16), np.ascontiguousarray(beta, dtype=np.uint16),
+                            x.shape[0], epsilon, out)
+    return out
+
+
+def groupnorm_tiles(x: np.ndarray, epsilon: float) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.uint16).reshape(-1, 128)
+    out = np.empty(x.shape, dtype=np.float64)
+    _lib.fko_groupnorm_tiles(x, x.shape[0], epsilon, out)
+    return out

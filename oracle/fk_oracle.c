@@ -301,3 +301,108 @@ void fko_flash_rows(const uint16_t* q, const uint16_t* k, const uint16_t* v, siz
         free(weights);
     }
 }
+
+/* ---------------------------------------------------------------- row kernels */
+
+/* examples/src/softmax.rs:195-202 -- every row a permutation of the multiples of 1/8 below 16. */
+static size_t softmax_permutation(size_t plane, size_t row, size_t column) {
+    const size_t stride = 11 + 2 * (row / 128 % 63);
+    return (53 * plane + 37 * row + stride * column) % 128;
+}
+float fko_softmax_input(size_t plane, size_t row, size_t column) {
+    return (float)softmax_permutation(plane, row, column) / 8.0f;
+}
+/* examples/src/softmax.rs:204-215 -- [planes, rows, 128] bf16. */
+void fko_softmax_stage(size_t rows, size_t planes, uint16_t* out) {
+    for (size_t plane = 0; plane < planes; ++plane)
+        for (size_t row = 0; row < rows; ++row)
+            for (size_t column = 0; column < 128; ++column)
+                out[(plane * rows + row) * 128 + column] = fko_to_bf16(fko_softmax_input(plane, row, column));
+}
+/* The closed form the reference checks its seed against (:276-279): weight 2^(p/8 - 127/8) over
+ * the sum of all 128 weights. */
+double fko_softmax_expected(size_t plane, size_t row, size_t column) {
+    double total = 0.0;
+    for (size_t value = 0; value < 128; ++value) total += exp2((double)value / 8.0 - 127.0 / 8.0);
+    return exp2((double)softmax_permutation(plane, row, column) / 8.0 - 127.0 / 8.0) / total;
+}
+/* The kernel's function over arbitrary bf16 rows (softmax.rs:137-160), in f64:
+ * 2^(x - max) / sum over the 128 columns of each row. */
+void fko_softmax_rows(const uint16_t* x, size_t rows, double* out) {
+#pragma omp parallel for schedule(static)
+    for (size_t row = 0; row < rows; ++row) {
+        double peak = -INFINITY, total = 0.0;
+        for (size_t c = 0; c < 128; ++c) {
+            const double v = (double)fko_from_bf16(x[row * 128 + c]);
+            if (v > peak) peak = v;
+        }
+        for (size_t c = 0; c < 128; ++c) {
+            out[row * 128 + c] = exp2((double)fko_from_bf16(x[row * 128 + c]) - peak);
+            total += out[row * 128 + c];
+        }
+        for (size_t c = 0; c < 128; ++c) out[row * 128 + c] /= total;
+    }
+}
+
+/* examples/src/layernorm.rs:330-352 -- the seed and the parameter vectors. */
+static size_t layernorm_permutation(size_t row, size_t column) {
+    const size_t stride = 11 + 2 * (row / 128 % 63);
+    return (37 * row + stride * column) % 128;
+}
+float fko_layernorm_value(size_t p, size_t row) {
+    const float magnitude = 16.0f + (float)(p % 32) / 2.0f;
+    const float boost = (float)(1 << (1 + row % 3));
+    const float sign[4] = {1.0f, -0.5f, boost, -boost / 2.0f};
+    return magnitude * sign[p / 32];
+}
+float fko_layernorm_input(size_t row, size_t column) {
+    return fko_layernorm_value(layernorm_permutation(row, column), row);
+}
+float fko_layernorm_gamma(size_t column) { return 1.0f + (float)column / 128.0f; }
+float fko_layernorm_beta(size_t column) { return 2.0f + (float)column / 64.0f; }
+void fko_layernorm_stage(size_t rows, uint16_t* x, uint16_t* gamma, uint16_t* beta) {
+    for (size_t row = 0; row < rows; ++row)
+        for (size_t column = 0; column < 128; ++column)
+            x[row * 128 + column] = fko_to_bf16(fko_layernorm_input(row, column));
+    for (size_t column = 0; column < 128; ++column) {
+        gamma[column] = fko_to_bf16(fko_layernorm_gamma(column));
+        beta[column] = fko_to_bf16(fko_layernorm_beta(column));
+    }
+}
+/* examples/src/layernorm.rs:354-360, 425-433 -- per-row statistics in f64, population variance,
+ * gamma * (x - mean) / sqrt(var + eps) + beta; over arbitrary bf16 inputs. */
+void fko_layernorm_rows(const uint16_t* x, const uint16_t* gamma, const uint16_t* beta, size_t rows,
+                        double epsilon, double* out) {
+#pragma omp parallel for schedule(static)
+    for (size_t row = 0; row < rows; ++row) {
+        double mean = 0.0, variance = 0.0;
+        for (size_t c = 0; c < 128; ++c) mean += (double)fko_from_bf16(x[row * 128 + c]);
+        mean /= 128.0;
+        for (size_t c = 0; c < 128; ++c) {
+            const double d = (double)fko_from_bf16(x[row * 128 + c]) - mean;
+            variance += d * d;
+        }
+        const double deviation = 1.0 / sqrt(variance / 128.0 + epsilon);
+        for (size_t c = 0; c < 128; ++c)
+            out[row * 128 + c] = (double)fko_from_bf16(gamma[c]) *
+                                     (((double)fko_from_bf16(x[row * 128 + c]) - mean) * deviation) +
+                                 (double)fko_from_bf16(beta[c]);
+    }
+}
+/* examples/src/layernorm.rs:480-489, 560-566 -- the same statistic over each [128, 128] tile. */
+void fko_groupnorm_tiles(const uint16_t* x, size_t rows, double epsilon, double* out) {
+#pragma omp parallel for schedule(static)
+    for (size_t tile = 0; tile < rows / 128; ++tile) {
+        const uint16_t* in = x + tile * 128 * 128;
+        double mean = 0.0, variance = 0.0;
+        for (size_t i = 0; i < 128 * 128; ++i) mean += (double)fko_from_bf16(in[i]);
+        mean /= 128.0 * 128.0;
+        for (size_t i = 0; i < 128 * 128; ++i) {
+            const double d = (double)fko_from_bf16(in[i]) - mean;
+            variance += d * d;
+        }
+        const double deviation = 1.0 / sqrt(variance / (128.0 * 128.0) + epsilon);
+        for (size_t i = 0; i < 128 * 128; ++i)
+            out[tile * 128 * 128 + i] = ((double)fko_from_bf16(in[i]) - mean) * deviation;
+    }
+}

@@ -149,3 +149,33 @@ def test_bf16_add_rounds_the_exact_sum_once():
     added = np.array([word(v) for v in (1.0, 1.0, 3.0, 4.0, 1.0, 1000.0)], dtype=np.uint16)
     scalar = [oracle.bf16_add(int(h), int(a)) for h, a in zip(held, added)]
     assert list(oracle.bf16_add_words(held, added)) == scalar
+
+
+def test_row_kernel_seeds_have_the_properties_the_reference_states():
+    """examples/src/softmax.rs:12-17 (every row a permutation of the multiples of 1/8 below 16, closed
+    form of the answer), examples/src/layernorm.rs:309-312 (no row variance under 835) and :22-26
+    (rows of different boost classes have different statistics, so the two norms differ)."""
+    words = oracle.softmax_stage(256, 2)
+    values = oracle.bf16_to_f32(words)
+    for plane in range(2):
+        for row in range(0, 256, 5):
+            assert sorted(values[plane, row] * 8) == list(range(128))
+    reference = oracle.softmax_rows(words)
+    for plane, row, column in ((0, 0, 0), (1, 255, 127), (0, 128, 64), (1, 3, 9)):
+        assert abs(reference[plane, row, column] / oracle.softmax_expected(plane, row, column) - 1) < 1e-12
+    assert abs(reference.sum(axis=-1) - 1).max() < 1e-12
+    # The closest pair of outputs of a row is 9.05 % apart (2^(1/8) - 1), far above the 2^-8 tolerance.
+    ordered = np.sort(reference[0, 0])
+    assert abs((ordered[1:] / ordered[:-1]).min() - 2 ** 0.125) < 1e-9
+
+    x, gamma, beta = oracle.layernorm_stage(384)
+    wide = oracle.bf16_to_f32(x).astype(np.float64)
+    assert wide.var(axis=1).min() > 835
+    assert oracle.from_bf16(int(gamma[64])) == 1.5 and oracle.from_bf16(int(beta[64])) == 3.0
+    rows_ = oracle.layernorm_rows(x, gamma, beta, 1e-5)
+    by_hand = (wide[7] - wide[7].mean()) / np.sqrt(wide[7].var() + 1e-5) * oracle.bf16_to_f32(gamma) + oracle.bf16_to_f32(beta)
+    assert abs(rows_[7] - by_hand).max() < 1e-9
+    tiles = oracle.groupnorm_tiles(x, 1e-5)
+    for tile in range(3):
+        block = wide[128 * tile:128 * tile + 128]
+        assert abs(tiles[128 * tile:128 * tile + 128] - (block - block.mean()) / np.sqrt(block.var() + 1e-5)).max() < 1e-9
