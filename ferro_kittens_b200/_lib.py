@@ -94,6 +94,10 @@ SIGNATURES = {
                              c_uint32, c_float, c_int, c_void_p, c_void_p]),
     "fk_flash_fwd_host": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_uint32,
                                   c_uint32, c_float, c_int]),
+    "fk_flash_bwd_shared_bytes": (c_uint32, []),
+    "fk_flash_bwd_threads": (c_uint32, []),
+    "fk_flash_bwd_workspace_bytes": (c_uint64, [c_uint32, c_uint32]),
+    "fk_flash_bwd": (c_int, [c_void_p] * 10 + [c_uint32, c_uint32, c_float, c_int, c_void_p, c_void_p]),
     "fk_rows_shared_bytes": (c_uint32, []),
     "fk_rows_threads": (c_uint32, []),
     "fk_softmax_rows": (c_int, [c_void_p, c_void_p, c_uint32, c_uint32, c_void_p, c_void_p]),

@@ -19,7 +19,7 @@ CSRC = PACKAGE / "csrc"
 LIBRARY = PACKAGE / "libferro_kittens_b200.so"
 CUBLASLT_LIBRARY = PACKAGE / "libfk_cublaslt.so"
 
-SOURCES = ["host.cu", "gemm.cu", "flash.cu", "rows.cu"]
+SOURCES = ["host.cu", "gemm.cu", "flash.cu", "flash_bwd.cu", "rows.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

@@ -1,0 +1,428 @@
+// Flash-attention backward, D = 128, for sm_100a: dQ, dK, dV from Q, K, V, O, dO and the forward's
+// log-sum-exp, bf16 in and out, fp32 accumulation.
+//
+// The reference has no backward kernel; it carries the pieces one is built from -- the
+// transposed-operand MMAs (`mma_atb`, `mma_atbt`, src/mma.rs:314-376), the transposed causal mask
+// (`make_causal_t_at`, src/reg.rs:1432-1434) and the row/column vector loads for a saved LSE
+// (src/global.rs:573-654) -- and its forward's output is this kernel's input. The arithmetic is the
+// standard one:
+//
+//   P = exp(scale S - lse),  S = Q K^T          dV = P^T dO
+//   dP = dO V^T,  delta = rowsum(dO * O)         dS = scale P * (dP - delta)
+//   dQ = dS K                                    dK = dS^T Q
+//
+// Three launches, nothing atomic, results independent of scheduling:
+//   1. `stats`: delta and lse * log2(e) per query row (memory-bound, reads O and dO once).
+//   2. one CTA per 128-key block owns K_j, V_j and the accumulators dV_j, dK_j in tensor memory and
+//      streams the query blocks past them. It computes the TRANSPOSED tiles S^T = K_j Q_i^T and
+//      dP^T = V_j dO_i^T so that keys are the tensor-memory lanes: P^T and dS^T are then A operands
+//      from tensor memory of dV_j += P^T dO_i and dK_j += dS^T Q_i, with dO_i and Q_i read MN-major
+//      from the same shared tiles the first two MMAs read K-major.
+//   3. one CTA per 128-query block owns Q_i, dO_i and dQ_i and streams the key blocks: S = Q_i K_j^T,
+//      dP = dO_i V_j^T, dQ_i += dS K_j. (S and dP are computed twice overall: 7 tile MMAs per tile
+//      pair instead of 5, the price of not adding into dQ from many CTAs.)
+// Launches 2 and 3 are one kernel template. Roles per CTA: warps 0-7 the element-wise step (warps
+// 0-3 columns 0-63, warps 4-7 columns 64-127 of the same 32 lanes; no reduction crosses a thread),
+// warp 8 the loader (TMA tiles through a two-stage ring, the per-column statistics by bulk copy),
+// warp 9 the MMA issue. Tensor memory: T1 (S or S^T; bf16 P over it) | T2 (dP; bf16 dS over it) |
+// accumulator 0 | accumulator 1, 128 columns each. Every wait is bounded.
+
+#include "fk_host.h"
+#include "fk_layout.h"
+#include "fk_ptx.cuh"
+
+namespace fk {
+namespace flash_bwd {
+
+constexpr uint32_t kRows = 128;  // rows of every tile: a query block or a key block
+constexpr uint32_t kHead = 128;
+constexpr uint32_t kStages = 2;
+constexpr uint32_t kElementWarps = 8;
+constexpr uint32_t kLoaderWarp = kElementWarps;
+constexpr uint32_t kMmaWarp = kElementWarps + 1;
+constexpr uint32_t kThreads = (kElementWarps + 2) * 32;
+constexpr uint32_t kSubtileBytes = kRows * 64 * 2;
+constexpr uint32_t kTileBytes = 2 * kSubtileBytes;
+constexpr uint32_t kStatsBytes = 2 * kRows * 4;  // lse * log2(e) and delta of one query block
+constexpr uint32_t kTmemColumns = 512;
+constexpr uint32_t kT1 = 0, kT2 = 128, kAcc0 = 256, kAcc1 = 384;
+
+struct Plan {
+    SharedPlan resident, ring, stats, resident_full, full, empty, t_full, p_ready, acc_done, tmem_slot,
+        stop, end;
+    constexpr Plan()
+        : resident(SharedPlan{}.tile_ring(kRows, kHead, 2, 2)),
+          ring(resident.tile_ring(kRows, kHead, 2, 2 * kStages)),
+          stats(ring.reserve(kStages * kStatsBytes, 16)),
+          resident_full(stats.semaphore()),
+          full(resident_full.semaphores(kStages)),
+          empty(full.semaphores(kStages)),
+          t_full(empty.semaphore()),
+          p_ready(t_full.semaphore()),
+          acc_done(p_ready.semaphore()),
+          tmem_slot(acc_done.tmem_slot()),
+          stop(tmem_slot.word()),
+          end(stop) {}
+};
+constexpr Plan kPlan{};
+constexpr uint32_t kBaseAlign = 1024;
+constexpr uint32_t kSharedBytes = static_cast<uint32_t>(kPlan.end.bytes());
+static_assert(kSharedBytes <= 232448, "plan exceeds the opt-in shared memory of an sm_100 CTA");
+
+enum StallCode : uint32_t {
+    kStallLoader = 0x401,
+    kStallMmaResident = 0x402,
+    kStallMmaStream = 0x403,
+    kStallMmaP = 0x404,
+    kStallElementT = 0x405,
+    kStallElementAcc = 0x406,
+    kMisaligned = 0x4ff,
+};
+
+// delta = rowsum(dO * O) and lse * log2(e), one query row per 16 lanes.
+__global__ void __launch_bounds__(256) stats_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
+                                                    const float* __restrict__ lse, float* __restrict__ stats,
+                                                    uint32_t planes, uint32_t seq) {
+    const uint64_t rows = static_cast<uint64_t>(planes) * seq;
+    const uint32_t lane = threadIdx.x & 31, sub = lane >> 4, chunk = lane & 15;
+    const uint64_t warps = static_cast<uint64_t>(gridDim.x) * (blockDim.x >> 5);
+    for (uint64_t pair = static_cast<uint64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); 2 * pair < rows;
+         pair += warps) {
+        const uint64_t row = 2 * pair + sub;
+        float total = 0.0f;
+        if (row < rows) {
+            const uint4 a = *reinterpret_cast<const uint4*>(o + row * kHead + 8 * chunk);
+            const uint4 b = *reinterpret_cast<const uint4*>(d_o + row * kHead + 8 * chunk);
+            const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (uint32_t i = 0; i < 4; ++i)
+                total += __uint_as_float(aw[i] << 16) * __uint_as_float(bw[i] << 16) +
+                         __uint_as_float(aw[i] & 0xffff0000u) * __uint_as_float(bw[i] & 0xffff0000u);
+        }
+#pragma unroll
+        for (uint32_t mask = 8; mask > 0; mask >>= 1) total += __shfl_xor_sync(0xffffffffu, total, mask);
+        if (row < rows && chunk == 0) {
+            const uint64_t plane = row / seq, at = row % seq;
+            stats[(2 * plane) * seq + at] = lse[row] * 1.4426950408889634f;
+            stats[(2 * plane + 1) * seq + at] = total;
+        }
+    }
+}
+
+// KV = true: the CTA owns a key block (resident K_j, V_j; streams Q_i, dO_i; lanes are keys).
+// KV = false: it owns a query block (resident Q_i, dO_i; streams K_j, V_j; lanes are queries).
+template <bool KV>
+__global__ void __launch_bounds__(kThreads, 1)
+    backward_kernel(const __grid_constant__ CUtensorMap r0_map, const __grid_constant__ CUtensorMap r1_map,
+                    const __grid_constant__ CUtensorMap x0_map, const __grid_constant__ CUtensorMap x1_map,
+                    const __grid_constant__ CUtensorMap out0_map, const __grid_constant__ CUtensorMap out1_map,
+                    const float* __restrict__ stats, uint32_t seq, float scale, uint32_t causal, uint32_t* status) {
+    extern __shared__ __align__(1024) uint8_t dynamic_shared[];
+    const uint32_t base = smem_u32(dynamic_shared);
+    if (base & (kBaseAlign - 1)) {
+        if (threadIdx.x == 0 && status) atomicCAS(status, 0u, static_cast<uint32_t>(kMisaligned));
+        return;
+    }
+    const uint32_t resident = base + kPlan.resident.at;
+    const uint32_t ring = base + kPlan.ring.at;
+    const uint32_t stats_smem = base + kPlan.stats.at;
+    const float* const stats_view = reinterpret_cast<const float*>(dynamic_shared + kPlan.stats.at);
+    const uint32_t resident_full = base + kPlan.resident_full.at;
+    const uint32_t full = base + kPlan.full.at;
+    const uint32_t empty = base + kPlan.empty.at;
+    const uint32_t t_full = base + kPlan.t_full.at;
+    const uint32_t p_ready = base + kPlan.p_ready.at;
+    const uint32_t acc_done = base + kPlan.acc_done.at;
+    const uint32_t slot = base + kPlan.tmem_slot.at;
+    volatile uint32_t* stop_flag = reinterpret_cast<volatile uint32_t*>(dynamic_shared + kPlan.stop.at);
+    volatile uint32_t* slot_ptr = reinterpret_cast<volatile uint32_t*>(dynamic_shared + kPlan.tmem_slot.at);
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t owner = blockIdx.x;  // the key block (KV) or query block this CTA owns
+    const uint32_t plane = blockIdx.y;
+    const uint32_t blocks = seq / kRows;
+    // Streamed blocks: all of them, or under a causal mask the query blocks at and after the key
+    // block (KV) / the key blocks up to and including the query block.
+    const uint32_t first = (causal && KV) ? owner : 0u;
+    const uint32_t count = causal ? (KV ? blocks - owner : owner + 1u) : blocks;
+
+    if (threadIdx.x == 0) {
+        mbar_init(resident_full, 1);
+        for (uint32_t s = 0; s < kStages; ++s) {
+            mbar_init(full + 8 * s, 1);
+            mbar_init(empty + 8 * s, 1);
+        }
+        mbar_init(t_full, 1);
+        mbar_init(p_ready, kElementWarps);
+        mbar_init(acc_done, 1);
+        *stop_flag = 0;
+        fence_mbarrier_init();
+        prefetch_tensormap(&r0_map);
+        prefetch_tensormap(&r1_map);
+        prefetch_tensormap(&x0_map);
+        prefetch_tensormap(&x1_map);
+    }
+    if (warp == kMmaWarp) {
+        tmem_alloc<1>(slot, kTmemColumns);
+        tmem_relinquish<1>();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *slot_ptr;
+    const StallSite site{status, stop_flag, 0};
+
+    if (warp == kLoaderWarp) {
+        // ------------------------------------------------ loader
+        if (lane == 0) {
+            mbar_arrive_expect_tx(resident_full, 2 * kTileBytes);
+            for (uint32_t half = 0; half < 2; ++half) {
+                tma_load_3d(resident + half * kSubtileBytes, &r0_map, static_cast<int>(64 * half),
+                            static_cast<int>(kRows * owner), static_cast<int>(plane), resident_full);
+                tma_load_3d(resident + kTileBytes + half * kSubtileBytes, &r1_map, static_cast<int>(64 * half),
+                            static_cast<int>(kRows * owner), static_cast<int>(plane), resident_full);
+            }
+            for (uint32_t n = 0; n < count; ++n) {
+                const uint32_t s = n % kStages, block = first + n;
+                if (!mbar_wait(empty + 8 * s, ((n / kStages) & 1u) ^ 1u, site, kStallLoader, n)) break;
+                mbar_arrive_expect_tx(full + 8 * s, 2 * kTileBytes + (KV ? kStatsBytes : 0u));
+                const uint32_t x0 = ring + (2 * s) * kTileBytes, x1 = x0 + kTileBytes;
+                for (uint32_t half = 0; half < 2; ++half) {
+                    tma_load_3d(x0 + half * kSubtileBytes, &x0_map, static_cast<int>(64 * half),
+                                static_cast<int>(kRows * block), static_cast<int>(plane), full + 8 * s);
+                    tma_load_3d(x1 + half * kSubtileBytes, &x1_map, static_cast<int>(64 * half),
+                                static_cast<int>(kRows * block), static_cast<int>(plane), full + 8 * s);
+                }
+                if (KV) {
+                    // The streamed query block's statistics, one value per COLUMN of the transposed tiles.
+                    const float* source = stats + (2 * static_cast<size_t>(plane)) * seq + kRows * block;
+                    for (uint32_t which = 0; which < 2; ++which)
+                        asm volatile(
+                            "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                stats_smem + s * kStatsBytes + which * kRows * 4),
+                            "l"(source + which * static_cast<size_t>(seq)), "r"(kRows * 4), "r"(full + 8 * s)
+                            : "memory");
+                }
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ------------------------------------------------ MMA issue (whole warp, lane 0 predicated on)
+        const uint32_t leader = lane == 0 ? 1u : 0u;
+        constexpr uint32_t idesc_ss = instruction_descriptor(kRows, kRows, false, false);
+        constexpr uint32_t idesc_ts = instruction_descriptor(kRows, kHead, false, true);
+        auto wait = [&](uint32_t bar, uint32_t parity, uint32_t code, uint32_t detail) {
+            uint32_t ok = 1;
+            if (lane == 0) ok = mbar_wait(bar, parity, site, code, detail) ? 1u : 0u;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (ok) tc_fence_after_sync();
+            return ok != 0;
+        };
+        // T = A . B^T over d = 128, both tiles K-major: two stacked [128, 64] subtiles, four K=16 chunks each.
+        auto transposed_product = [&](uint32_t t_column, uint32_t a_tile, uint32_t b_tile) {
+            const uint64_t a_desc = operand_descriptor(a_tile, kKMajorLeadingBytes);
+            const uint64_t b_desc = operand_descriptor(b_tile, kKMajorLeadingBytes);
+#pragma unroll
+            for (uint32_t chunk = 0; chunk < kHead / 16; ++chunk) {
+                const uint64_t step = ((chunk / 4) * kSubtileBytes + (chunk % 4) * kKMajorChunkBytes) >> 4;
+                mma_ss_if<1>(leader, tmem + t_column, a_desc + step, b_desc + step, idesc_ss, chunk != 0);
+            }
+        };
+        // ACC (+)= A . B over the tile's 128 rows: A is the bf16 the element-wise warps left over T
+        // (rows 0-63 of the contraction in columns 0-31, rows 64-127 in columns 64-95), B the streamed
+        // tile read MN-major: 16 rows per chunk, the second 64 head columns one subtile on.
+        auto accumulate = [&](uint32_t acc_column, uint32_t t_column, uint32_t b_tile, bool keep) {
+            const uint64_t b_desc = operand_descriptor(b_tile, kSubtileBytes);
+#pragma unroll
+            for (uint32_t chunk = 0; chunk < kRows / 16; ++chunk)
+                mma_ts_if(leader, tmem + acc_column, tmem + t_column + 64 * (chunk / 4) + 8 * (chunk % 4),
+                          b_desc + ((chunk * kMnMajorChunkBytes) >> 4), idesc_ts, (keep || chunk != 0) ? 1u : 0u);
+        };
+
+        bool live = wait(resident_full, 0, kStallMmaResident, 0);
+        for (uint32_t n = 0; live && n < count; ++n) {
+            const uint32_t s = n % kStages;
+            if (!wait(full + 8 * s, (n / kStages) & 1u, kStallMmaStream, n)) break;
+            const uint32_t x0 = ring + (2 * s) * kTileBytes, x1 = x0 + kTileBytes;
+            transposed_product(kT1, resident, x0);               // S^T = K Q^T   |  S = Q K^T
+            transposed_product(kT2, resident + kTileBytes, x1);  // dP^T = V dO^T | dP = dO V^T
+            mma_commit_if<1>(leader, t_full);
+            if (!wait(p_ready, n & 1u, kStallMmaP, n)) break;
+            if (KV) accumulate(kAcc0, kT1, x1, n != 0);          // dV += P^T dO
+            accumulate(kAcc1, kT2, x0, n != 0);                  // dK += dS^T Q  |  dQ += dS K
+            mma_commit_if<1>(leader, empty + 8 * s);
+        }
+        mma_commit_if<1>(leader, acc_done);
+        __syncwarp();
+    } else {
+        // ------------------------------------------------ element-wise step and epilogue
+        const uint32_t half = warp >> 2;            // which 64 columns of T / 64 head columns of an accumulator
+        const uint32_t quadrant = warp & 3u;        // tensor-memory lanes this warp may touch
+        const uint32_t row = 32 * quadrant + lane;  // lane of the tiles = row of the owned block
+        const uint32_t lane_base = (32 * quadrant) << 16;
+        const float scale_log2 = scale * 1.4426950408889634f;
+        float row_lse = 0.0f, row_delta = 0.0f;
+        if (!KV) {
+            row_lse = stats[(2 * static_cast<size_t>(plane)) * seq + kRows * owner + row];
+            row_delta = stats[(2 * static_cast<size_t>(plane) + 1) * seq + kRows * owner + row];
+        }
+        bool live = true;
+        for (uint32_t n = 0; live && n < count; ++n) {
+            const uint32_t s = n % kStages, block = first + n;
+            if (!mbar_wait(t_full, n & 1u, site, kStallElementT, n)) {
+                live = false;
+                break;
+            }
+            tc_fence_after_sync();
+            // The column statistics arrived by bulk copy on the stage's own barrier (complete by now:
+            // the MMAs just waited for were issued after it); observe it before reading them.
+            if (KV && !mbar_wait(full + 8 * s, (n / kStages) & 1u, site, kStallElementT, n)) {
+                live = false;
+                break;
+            }
+            const bool diagonal = causal && block == owner;
+            const float* const column_stats = stats_view + s * (kStatsBytes / 4);
+#pragma unroll 1
+            for (uint32_t c = 0; c < 2; ++c) {
+                const uint32_t column0 = 64 * half + 32 * c;
+                uint32_t score[32], slope[32];
+                tmem_ld_32x32(tmem + lane_base + kT1 + column0, score);
+                tmem_ld_32x32(tmem + lane_base + kT2 + column0, slope);
+                tmem_wait_ld();
+                uint32_t p_words[16], ds_words[16];
+#pragma unroll
+                for (uint32_t i = 0; i < 16; ++i) {
+                    float p[2], ds[2];
+#pragma unroll
+                    for (uint32_t e = 0; e < 2; ++e) {
+                        const uint32_t column = column0 + 2 * i + e;
+                        const float lse2 = KV ? column_stats[column] : row_lse;
+                        const float delta = KV ? column_stats[kRows + column] : row_delta;
+                        // KV: lane = key, column = query, visible iff key <= query. Otherwise lane = query.
+                        const bool hidden = diagonal && (KV ? column < row : column > row);
+                        const float weight =
+                            hidden ? 0.0f : ex2_approx(__uint_as_float(score[2 * i + e]) * scale_log2 - lse2);
+                        p[e] = weight;
+                        ds[e] = weight * (__uint_as_float(slope[2 * i + e]) - delta) * scale;
+                    }
+                    p_words[i] = pack_bf16x2(p[0], p[1]);
+                    ds_words[i] = pack_bf16x2(ds[0], ds[1]);
+                }
+                // Over columns of this warp's own half that it has already read.
+                tmem_st_32x16(tmem + lane_base + kT1 + 64 * half + 16 * c, p_words);
+                tmem_st_32x16(tmem + lane_base + kT2 + 64 * half + 16 * c, ds_words);
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_ready);
+        }
+
+        if (live && !mbar_wait(acc_done, 0, site, kStallElementAcc, count)) live = false;
+        if (live) {
+            tc_fence_after_sync();
+            // The resident tiles are dead once the last MMA retired: they stage the two outputs. This
+            // warp owns rows [32 q, 32 q + 32) of the [128, 64] subtile of head columns 64 half...
+#pragma unroll 1
+            for (uint32_t which = KV ? 0u : 1u; which < 2; ++which) {
+                const uint32_t acc = tmem + lane_base + (which ? kAcc1 : kAcc0) + 64 * half;
+                const uint32_t subtile = resident + which * kTileBytes + half * kSubtileBytes;
+#pragma unroll 1
+                for (uint32_t c = 0; c < 2; ++c) {
+                    uint32_t value[32];
+                    tmem_ld_32x32(acc + 32 * c, value);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (uint32_t i = 0; i < 4; ++i) {
+                        const uint32_t* v = value + 8 * i;
+                        st_shared_v4(subtile + swizzled_chunk_offset(row, 4 * c + i, 0),
+                                     pack_bf16x2(__uint_as_float(v[0]), __uint_as_float(v[1])),
+                                     pack_bf16x2(__uint_as_float(v[2]), __uint_as_float(v[3])),
+                                     pack_bf16x2(__uint_as_float(v[4]), __uint_as_float(v[5])),
+                                     pack_bf16x2(__uint_as_float(v[6]), __uint_as_float(v[7])));
+                    }
+                }
+                fence_proxy_async_shared();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_3d(which ? &out1_map : &out0_map, subtile + 32 * quadrant * 128,
+                                 static_cast<int>(64 * half), static_cast<int>(kRows * owner + 32 * quadrant),
+                                 static_cast<int>(plane));
+                    tma_store_commit();
+                }
+            }
+        }
+        if (lane == 0) tma_store_wait_all();
+    }
+
+    // ---------------------------------------------------- teardown
+    if (*stop_flag) {
+        for (int i = 0; i < 256; ++i) __nanosleep(1000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == kMmaWarp) tmem_dealloc<1>(tmem, kTmemColumns);
+}
+
+}  // namespace flash_bwd
+}  // namespace fk
+
+// ------------------------------------------------------------------ C ABI
+
+using namespace fk;
+
+extern "C" uint32_t fk_flash_bwd_shared_bytes(void) { return flash_bwd::kSharedBytes; }
+extern "C" uint32_t fk_flash_bwd_threads(void) { return flash_bwd::kThreads; }
+extern "C" uint64_t fk_flash_bwd_workspace_bytes(uint32_t planes, uint32_t seq) {
+    return 2ull * planes * seq * sizeof(float);
+}
+
+extern "C" int fk_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                            const float* lse, void* dq, void* dk, void* dv, float* workspace, uint32_t planes,
+                            uint32_t seq, float scale, int causal, void* stream, uint32_t* device_status) {
+    if (!q || !k || !v || !o || !d_o || !lse || !dq || !dk || !dv || !workspace)
+        return fk_fail(FK_ERR_INVALID, "an operand pointer is null");
+    if (seq == 0 || seq % flash_bwd::kRows || planes == 0)
+        return fk_fail(FK_ERR_SHAPE, "%u queries x %u heads does not divide the %u queries a tile owns", seq, planes,
+                       flash_bwd::kRows);
+    if (planes > 65535) return fk_fail(FK_ERR_SHAPE, "%u planes is past the 65535 a launch takes", planes);
+    if ((reinterpret_cast<uintptr_t>(workspace) | reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(d_o)) & 15u)
+        return fk_fail(FK_ERR_ALIGNMENT, "the workspace, O and dO want 16-byte alignment");
+    alignas(64) CUtensorMap maps[7];
+    const void* loads[4] = {q, k, v, d_o};
+    void* stores[3] = {dq, dk, dv};
+    int status = FK_OK;
+    for (int i = 0; i < 4 && status == FK_OK; ++i)
+        status = fk_encode_bf16_panels(&maps[i], reinterpret_cast<uint64_t>(loads[i]), flash_bwd::kRows,
+                                       flash_bwd::kHead, seq, planes);
+    for (int i = 0; i < 3 && status == FK_OK; ++i)
+        status = fk_encode_bf16_panels(&maps[4 + i], reinterpret_cast<uint64_t>(stores[i]), 32, flash_bwd::kHead,
+                                       seq, planes);
+    if (status != FK_OK) return status;
+    uint32_t limit = 0;
+    status = fk_admit_shared_plan(reinterpret_cast<const void*>(flash_bwd::backward_kernel<true>),
+                                  flash_bwd::kSharedBytes, &limit);
+    if (status == FK_OK)
+        status = fk_admit_shared_plan(reinterpret_cast<const void*>(flash_bwd::backward_kernel<false>),
+                                      flash_bwd::kSharedBytes, &limit);
+    if (status != FK_OK) return status;
+
+    cudaStream_t on = static_cast<cudaStream_t>(stream);
+    const uint64_t rows = static_cast<uint64_t>(planes) * seq;
+    const uint32_t stat_blocks = static_cast<uint32_t>((rows / 2 + 7) / 8 < 148 * 8 ? (rows / 2 + 7) / 8 : 148 * 8);
+    flash_bwd::stats_kernel<<<stat_blocks ? stat_blocks : 1, 256, 0, on>>>(
+        static_cast<const uint16_t*>(o), static_cast<const uint16_t*>(d_o), lse, workspace, planes, seq);
+    FK_CUDA(cudaGetLastError());
+    const dim3 grid(seq / flash_bwd::kRows, planes, 1);
+    const CUtensorMap &q_map = maps[0], &k_map = maps[1], &v_map = maps[2], &do_map = maps[3];
+    const CUtensorMap &dq_map = maps[4], &dk_map = maps[5], &dv_map = maps[6];
+    // Key-block owners: resident K, V; streamed Q, dO; outputs dV (accumulator 0) and dK (accumulator 1).
+    flash_bwd::backward_kernel<true><<<grid, flash_bwd::kThreads, flash_bwd::kSharedBytes, on>>>(
+        k_map, v_map, q_map, do_map, dv_map, dk_map, workspace, seq, scale, causal ? 1u : 0u, device_status);
+    FK_CUDA(cudaGetLastError());
+    // Query-block owners: resident Q, dO; streamed K, V; output dQ (accumulator 1).
+    flash_bwd::backward_kernel<false><<<grid, flash_bwd::kThreads, flash_bwd::kSharedBytes, on>>>(
+        q_map, do_map, k_map, v_map, dq_map, dq_map, workspace, seq, scale, causal ? 1u : 0u, device_status);
+    FK_CUDA(cudaGetLastError());
+    return FK_OK;
+}

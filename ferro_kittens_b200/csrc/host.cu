@@ -319,6 +319,13 @@ static const char* stall_role(uint32_t code) {
         case 0x1ff: return "gemm found its shared memory base off a 1024-byte boundary";
         case 0x2ff: return "flash found its shared memory base off a 1024-byte boundary";
         case 0x301: return "self-test wait on a barrier nothing arrives on";
+        case 0x401: return "flash backward loader waiting for a free ring stage";
+        case 0x402: return "flash backward MMA warp waiting for its resident tiles";
+        case 0x403: return "flash backward MMA warp waiting for a streamed block";
+        case 0x404: return "flash backward MMA warp waiting for P and dS";
+        case 0x405: return "flash backward element-wise warp waiting for S and dP";
+        case 0x406: return "flash backward element-wise warp waiting for the accumulators";
+        case 0x4ff: return "flash backward found its shared memory base off a 1024-byte boundary";
         case 0x312: return "row-kernel copy warp waiting for the compute warps to finish a tile";
         case 0x313: return "row-kernel compute warp waiting for a tile to land";
         case 0x314: return "row-kernel compute warp waiting for the other warps' partial sums";

@@ -219,6 +219,21 @@ int fk_flash_fwd_host(const uint16_t* q_host, const uint16_t* k_host, const uint
                       uint16_t* o_host, float* lse_host, uint32_t planes, uint32_t seq, float scale,
                       int causal);
 
+/* Flash-attention backward, D = 128: dQ, dK, dV from Q, K, V, O, dO and the log-sum-exp the
+ * forward wrote (natural log, [planes, seq] fp32). The reference has no backward kernel; it
+ * carries its pieces (`mma_atb` / `mma_atbt`, src/mma.rs:314-376; `make_causal_t_at`,
+ * src/reg.rs:1432-1434; LSE vector loads, src/global.rs:573-654) and names it the next caller of
+ * the forward's LSE. All tensors packed [planes, seq, 128] bf16; seq % 128 == 0. `workspace` is
+ * fk_flash_bwd_workspace_bytes(planes, seq) bytes of device memory, 16-byte aligned, written by
+ * the call (per-row statistics); nothing is allocated. Three launches on `stream`, no atomics:
+ * results do not depend on scheduling. `device_status` as for the GEMM. */
+uint32_t fk_flash_bwd_shared_bytes(void);
+uint32_t fk_flash_bwd_threads(void);
+uint64_t fk_flash_bwd_workspace_bytes(uint32_t planes, uint32_t seq);
+int fk_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                 const float* lse, void* dq, void* dk, void* dv, float* workspace, uint32_t planes,
+                 uint32_t seq, float scale, int causal, void* stream, uint32_t* device_status);
+
 /* ---------------------------------------------------------------- row kernels
  *
  * The memory-bound kernels either side of attention and GEMM, over rows of 128 bf16 columns

@@ -75,6 +75,8 @@ _lib.fko_layernorm_rows.argtypes = [_u16p, _u16p, _u16p, c_size_t, c_double, _f6
 _lib.fko_layernorm_rows.restype = None
 _lib.fko_groupnorm_tiles.argtypes = [_u16p, c_size_t, c_double, _f64p]
 _lib.fko_groupnorm_tiles.restype = None
+_lib.fko_flash_backward.argtypes = [_u16p, _u16p, _u16p, _u16p, c_size_t, c_double, c_int, _f64p, _f64p, _f64p]
+_lib.fko_flash_backward.restype = None
 
 
 def threads() -> int:
@@ -245,3 +247,12 @@ def groupnorm_tiles(x: np.ndarray, epsilon: float) -> np.ndarray:
     out = np.empty(x.shape, dtype=np.float64)
     _lib.fko_groupnorm_tiles(x, x.shape[0], epsilon, out)
     return out
+
+
+def flash_backward(q: np.ndarray, k: np.ndarray, v: np.ndarray, d_out: np.ndarray, scale: float, causal: bool):
+    """f64 gradients (dq, dk, dv) of one [sequence, 128] plane of bf16 words."""
+    q, k, v, d_out = (np.ascontiguousarray(x, dtype=np.uint16) for x in (q, k, v, d_out))
+    sequence = q.shape[0]
+    dq, dk, dv = (np.empty((sequence, 128), dtype=np.float64) for _ in range(3))
+    _lib.fko_flash_backward(q, k, v, d_out, sequence, scale, int(causal), dq, dk, dv)
+    return dq, dk, dv

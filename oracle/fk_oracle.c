@@ -406,3 +406,54 @@ void fko_groupnorm_tiles(const uint16_t* x, size_t rows, double epsilon, double*
             out[tile * 128 * 128 + i] = ((double)fko_from_bf16(in[i]) - mean) * deviation;
     }
 }
+
+/* ---------------------------------------------------------------- attention backward
+ *
+ * The gradients of the function fko_flash_rows computes, for one [sequence, 128] plane, in f64
+ * over bf16 inputs: P from the stable softmax of the scaled scores, dV = P^T dO, dP = dO V^T,
+ * dS = P * (dP - rowsum(P * dP)), dQ = scale dS K, dK = scale dS^T Q. The reference has no
+ * backward; this restates the textbook derivative of its forward (examples/src/flash_forward.rs:419-440).
+ */
+void fko_flash_backward(const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint16_t* d_out,
+                        size_t sequence, double scale, int causal, double* dq, double* dk, double* dv) {
+    for (size_t i = 0; i < sequence * 128; ++i) dq[i] = dk[i] = dv[i] = 0.0;
+    double* weights = (double*)malloc(sequence * sizeof(double));
+    double* slopes = (double*)malloc(sequence * sizeof(double));
+    for (size_t row = 0; row < sequence; ++row) {
+        const size_t keys = causal ? row + 1 : sequence;
+        double qw[128], gw[128];
+        for (size_t d = 0; d < 128; ++d) {
+            qw[d] = (double)fko_from_bf16(q[row * 128 + d]);
+            gw[d] = (double)fko_from_bf16(d_out[row * 128 + d]);
+        }
+        double max = -INFINITY, total = 0.0, inner = 0.0;
+        for (size_t key = 0; key < keys; ++key) {
+            double dot = 0.0, slope = 0.0;
+            for (size_t d = 0; d < 128; ++d) {
+                dot += qw[d] * (double)fko_from_bf16(k[key * 128 + d]);
+                slope += gw[d] * (double)fko_from_bf16(v[key * 128 + d]);
+            }
+            weights[key] = scale * dot;
+            slopes[key] = slope;
+            if (weights[key] > max) max = weights[key];
+        }
+        for (size_t key = 0; key < keys; ++key) {
+            weights[key] = exp(weights[key] - max);
+            total += weights[key];
+        }
+        for (size_t key = 0; key < keys; ++key) {
+            weights[key] /= total;
+            inner += weights[key] * slopes[key];
+        }
+        for (size_t key = 0; key < keys; ++key) {
+            const double p = weights[key], ds = scale * p * (slopes[key] - inner);
+            for (size_t d = 0; d < 128; ++d) {
+                dv[key * 128 + d] += p * gw[d];
+                dq[row * 128 + d] += ds * (double)fko_from_bf16(k[key * 128 + d]);
+                dk[key * 128 + d] += ds * qw[d];
+            }
+        }
+    }
+    free(weights);
+    free(slopes);
+}

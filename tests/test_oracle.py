@@ -179,3 +179,23 @@ def test_row_kernel_seeds_have_the_properties_the_reference_states():
     for tile in range(3):
         block = wide[128 * tile:128 * tile + 128]
         assert abs(tiles[128 * tile:128 * tile + 128] - (block - block.mean()) / np.sqrt(block.var() + 1e-5)).max() < 1e-9
+
+
+def test_attention_backward_oracle_matches_float64_autograd():
+    """The backward oracle is the textbook derivative of the forward the reference checks against
+    (examples/src/flash_forward.rs:419-440); an independent implementation (torch autograd in
+    float64) pins it."""
+    import torch
+
+    generator = torch.Generator().manual_seed(0)
+    for causal in (False, True):
+        q, k, v, g = (torch.randn((160, 128), generator=generator).to(torch.bfloat16) for _ in range(4))
+        words = lambda t: t.view(torch.int16).numpy().view(np.uint16)  # noqa: E731
+        dq, dk, dv = oracle.flash_backward(words(q), words(k), words(v), words(g), 0.125, causal)
+        qd, kd, vd = (t.double().requires_grad_() for t in (q, k, v))
+        scores = qd @ kd.T * 0.125
+        if causal:
+            scores = scores.masked_fill(torch.triu(torch.ones(160, 160, dtype=torch.bool), 1), float("-inf"))
+        (torch.softmax(scores, dim=-1) @ vd).backward(g.double())
+        for mine, theirs in ((dq, qd), (dk, kd), (dv, vd)):
+            assert np.abs(mine - theirs.grad.numpy()).max() < 1e-12
