@@ -21,7 +21,9 @@
 //   3. one CTA per 128-query block owns Q_i, dO_i and dQ_i and streams the key blocks: S = Q_i K_j^T,
 //      dP = dO_i V_j^T, dQ_i += dS K_j. (S and dP are computed twice overall: 7 tile MMAs per tile
 //      pair instead of 5, the price of not adding into dQ from many CTAs.)
-// Launches 2 and 3 are one kernel template. Roles per CTA: warps 0-7 the element-wise step (warps
+// Launches 2 and 3 are one kernel template. The element-wise step is split in two (P from S, then dS
+// from dP and the P kept in registers) and the MMA issue order interleaves blocks, so that the tensor
+// pipe works on one of the two fp32 tiles while the element-wise warps work on the other. Roles per CTA: warps 0-7 the element-wise step (warps
 // 0-3 columns 0-63, warps 4-7 columns 64-127 of the same 32 lanes; no reduction crosses a thread),
 // warp 8 the loader (TMA tiles through a two-stage ring, the per-column statistics by bulk copy),
 // warp 9 the MMA issue. Tensor memory: T1 (S or S^T; bf16 P over it) | T2 (dP; bf16 dS over it) |
@@ -48,8 +50,8 @@ constexpr uint32_t kTmemColumns = 512;
 constexpr uint32_t kT1 = 0, kT2 = 128, kAcc0 = 256, kAcc1 = 384;
 
 struct Plan {
-    SharedPlan resident, ring, stats, resident_full, full, empty, t_full, p_ready, acc_done, tmem_slot,
-        stop, end;
+    SharedPlan resident, ring, stats, resident_full, full, empty, t1_full, t2_full, p_ready, ds_ready, acc_done,
+        tmem_slot, stop, end;
     constexpr Plan()
         : resident(SharedPlan{}.tile_ring(kRows, kHead, 2, 2)),
           ring(resident.tile_ring(kRows, kHead, 2, 2 * kStages)),
@@ -57,9 +59,11 @@ struct Plan {
           resident_full(stats.semaphore()),
           full(resident_full.semaphores(kStages)),
           empty(full.semaphores(kStages)),
-          t_full(empty.semaphore()),
-          p_ready(t_full.semaphore()),
-          acc_done(p_ready.semaphore()),
+          t1_full(empty.semaphore()),
+          t2_full(t1_full.semaphore()),
+          p_ready(t2_full.semaphore()),
+          ds_ready(p_ready.semaphore()),
+          acc_done(ds_ready.semaphore()),
           tmem_slot(acc_done.tmem_slot()),
           stop(tmem_slot.word()),
           end(stop) {}
@@ -76,6 +80,8 @@ enum StallCode : uint32_t {
     kStallMmaP = 0x404,
     kStallElementT = 0x405,
     kStallElementAcc = 0x406,
+    kStallMmaDs = 0x407,
+    kStallElementT2 = 0x408,
     kMisaligned = 0x4ff,
 };
 
@@ -130,8 +136,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t resident_full = base + kPlan.resident_full.at;
     const uint32_t full = base + kPlan.full.at;
     const uint32_t empty = base + kPlan.empty.at;
-    const uint32_t t_full = base + kPlan.t_full.at;
+    const uint32_t t1_full = base + kPlan.t1_full.at;
+    const uint32_t t2_full = base + kPlan.t2_full.at;
     const uint32_t p_ready = base + kPlan.p_ready.at;
+    const uint32_t ds_ready = base + kPlan.ds_ready.at;
     const uint32_t acc_done = base + kPlan.acc_done.at;
     const uint32_t slot = base + kPlan.tmem_slot.at;
     volatile uint32_t* stop_flag = reinterpret_cast<volatile uint32_t*>(dynamic_shared + kPlan.stop.at);
@@ -153,8 +161,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             mbar_init(full + 8 * s, 1);
             mbar_init(empty + 8 * s, 1);
         }
-        mbar_init(t_full, 1);
+        mbar_init(t1_full, 1);
+        mbar_init(t2_full, 1);
         mbar_init(p_ready, kElementWarps);
+        mbar_init(ds_ready, kElementWarps);
         mbar_init(acc_done, 1);
         *stop_flag = 0;
         fence_mbarrier_init();
@@ -239,18 +249,37 @@ __global__ void __launch_bounds__(kThreads, 1)
                           b_desc + ((chunk * kMnMajorChunkBytes) >> 4), idesc_ts, (keep || chunk != 0) ? 1u : 0u);
         };
 
+        // Issue order per block n: [P(n) ready] dV += P^T dO; S(n+1); [dS(n) ready] dK/dQ += dS^T Q;
+        // dP(n+1). The tensor pipe runs in issue order, so S(n+1) cannot overwrite P(n) before the MMA
+        // that reads it, nor dP(n+1) dS(n); and while the element-wise warps work on one of the two
+        // tiles the pipe has the other's products to run.
         bool live = wait(resident_full, 0, kStallMmaResident, 0);
+        if (live && count != 0) live = wait(full, 0, kStallMmaStream, 0);
+        if (live && count != 0) {
+            transposed_product(kT1, resident, ring);                            // S^T = K Q^T   |  S = Q K^T
+            mma_commit_if<1>(leader, t1_full);
+            transposed_product(kT2, resident + kTileBytes, ring + kTileBytes);  // dP^T = V dO^T | dP = dO V^T
+            mma_commit_if<1>(leader, t2_full);
+        }
         for (uint32_t n = 0; live && n < count; ++n) {
-            const uint32_t s = n % kStages;
-            if (!wait(full + 8 * s, (n / kStages) & 1u, kStallMmaStream, n)) break;
+            const uint32_t s = n % kStages, next = (n + 1) % kStages;
             const uint32_t x0 = ring + (2 * s) * kTileBytes, x1 = x0 + kTileBytes;
-            transposed_product(kT1, resident, x0);               // S^T = K Q^T   |  S = Q K^T
-            transposed_product(kT2, resident + kTileBytes, x1);  // dP^T = V dO^T | dP = dO V^T
-            mma_commit_if<1>(leader, t_full);
+            const uint32_t y0 = ring + (2 * next) * kTileBytes, y1 = y0 + kTileBytes;
+            const bool more = n + 1 < count;
             if (!wait(p_ready, n & 1u, kStallMmaP, n)) break;
-            if (KV) accumulate(kAcc0, kT1, x1, n != 0);          // dV += P^T dO
-            accumulate(kAcc1, kT2, x0, n != 0);                  // dK += dS^T Q  |  dQ += dS K
+            if (KV) accumulate(kAcc0, kT1, x1, n != 0);  // dV += P^T dO
+            if (more) {
+                if (!wait(full + 8 * next, ((n + 1) / kStages) & 1u, kStallMmaStream, n + 1)) break;
+                transposed_product(kT1, resident, y0);
+                mma_commit_if<1>(leader, t1_full);
+            }
+            if (!wait(ds_ready, n & 1u, kStallMmaDs, n)) break;
+            accumulate(kAcc1, kT2, x0, n != 0);  // dK += dS^T Q  |  dQ += dS K
             mma_commit_if<1>(leader, empty + 8 * s);
+            if (more) {
+                transposed_product(kT2, resident + kTileBytes, y1);
+                mma_commit_if<1>(leader, t2_full);
+            }
         }
         mma_commit_if<1>(leader, acc_done);
         __syncwarp();
@@ -269,7 +298,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         bool live = true;
         for (uint32_t n = 0; live && n < count; ++n) {
             const uint32_t s = n % kStages, block = first + n;
-            if (!mbar_wait(t_full, n & 1u, site, kStallElementT, n)) {
+            // ---- first half of the step: P from S, while the pipe computes dP
+            if (!mbar_wait(t1_full, n & 1u, site, kStallElementT, n)) {
                 live = false;
                 break;
             }
@@ -282,40 +312,63 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             const bool diagonal = causal && block == owner;
             const float* const column_stats = stats_view + s * (kStatsBytes / 4);
-#pragma unroll 1
+            float p[64];
+#pragma unroll
             for (uint32_t c = 0; c < 2; ++c) {
                 const uint32_t column0 = 64 * half + 32 * c;
-                uint32_t score[32], slope[32];
+                uint32_t score[32];
                 tmem_ld_32x32(tmem + lane_base + kT1 + column0, score);
+                tmem_wait_ld();
+                uint32_t p_words[16];
+#pragma unroll
+                for (uint32_t i = 0; i < 32; ++i) {
+                    const uint32_t column = column0 + i;
+                    const float lse2 = KV ? column_stats[column] : row_lse;
+                    // KV: lane = key, column = query, visible iff key <= query. Otherwise lane = query.
+                    const bool hidden = diagonal && (KV ? column < row : column > row);
+                    p[32 * c + i] = hidden ? 0.0f : ex2_approx(__uint_as_float(score[i]) * scale_log2 - lse2);
+                }
+                if (KV) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 16; ++i) p_words[i] = pack_bf16x2(p[32 * c + 2 * i], p[32 * c + 2 * i + 1]);
+                    // Over columns of this warp's own half that it has already read.
+                    tmem_st_32x16(tmem + lane_base + kT1 + 64 * half + 16 * c, p_words);
+                }
+            }
+            if (KV) tmem_wait_st();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_ready);  // P is in place (KV), and S has been consumed
+
+            // ---- second half: dS from dP and the P still in registers, while the pipe runs dV and S(n+1)
+            if (!mbar_wait(t2_full, n & 1u, site, kStallElementT2, n)) {
+                live = false;
+                break;
+            }
+            tc_fence_after_sync();
+#pragma unroll
+            for (uint32_t c = 0; c < 2; ++c) {
+                const uint32_t column0 = 64 * half + 32 * c;
+                uint32_t slope[32];
                 tmem_ld_32x32(tmem + lane_base + kT2 + column0, slope);
                 tmem_wait_ld();
-                uint32_t p_words[16], ds_words[16];
+                uint32_t ds_words[16];
 #pragma unroll
                 for (uint32_t i = 0; i < 16; ++i) {
-                    float p[2], ds[2];
+                    float ds[2];
 #pragma unroll
                     for (uint32_t e = 0; e < 2; ++e) {
-                        const uint32_t column = column0 + 2 * i + e;
-                        const float lse2 = KV ? column_stats[column] : row_lse;
-                        const float delta = KV ? column_stats[kRows + column] : row_delta;
-                        // KV: lane = key, column = query, visible iff key <= query. Otherwise lane = query.
-                        const bool hidden = diagonal && (KV ? column < row : column > row);
-                        const float weight =
-                            hidden ? 0.0f : ex2_approx(__uint_as_float(score[2 * i + e]) * scale_log2 - lse2);
-                        p[e] = weight;
-                        ds[e] = weight * (__uint_as_float(slope[2 * i + e]) - delta) * scale;
+                        const float delta = KV ? column_stats[kRows + column0 + 2 * i + e] : row_delta;
+                        ds[e] = p[32 * c + 2 * i + e] * (__uint_as_float(slope[2 * i + e]) - delta) * scale;
                     }
-                    p_words[i] = pack_bf16x2(p[0], p[1]);
                     ds_words[i] = pack_bf16x2(ds[0], ds[1]);
                 }
-                // Over columns of this warp's own half that it has already read.
-                tmem_st_32x16(tmem + lane_base + kT1 + 64 * half + 16 * c, p_words);
                 tmem_st_32x16(tmem + lane_base + kT2 + 64 * half + 16 * c, ds_words);
             }
             tmem_wait_st();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_ready);
+            if (lane == 0) mbar_arrive(ds_ready);
         }
 
         if (live && !mbar_wait(acc_done, 0, site, kStallElementAcc, count)) live = false;

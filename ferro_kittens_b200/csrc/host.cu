@@ -325,6 +325,8 @@ static const char* stall_role(uint32_t code) {
         case 0x404: return "flash backward MMA warp waiting for P and dS";
         case 0x405: return "flash backward element-wise warp waiting for S and dP";
         case 0x406: return "flash backward element-wise warp waiting for the accumulators";
+        case 0x407: return "flash backward MMA warp waiting for dS";
+        case 0x408: return "flash backward element-wise warp waiting for dP";
         case 0x4ff: return "flash backward found its shared memory base off a 1024-byte boundary";
         case 0x312: return "row-kernel copy warp waiting for the compute warps to finish a tile";
         case 0x313: return "row-kernel compute warp waiting for a tile to land";
