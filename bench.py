@@ -292,7 +292,31 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     flash_seconds = max_over_ranks(time_steps(flash_step, args.steps, args.warmup, barrier))
     flash_flops = 4.0 * planes_total * FLASH["seq"] ** 2 * 128
     flash_value = flash_flops * args.steps / flash_seconds / 1e12
-    del qkv, out, lse
+
+    # ---- its backward on the same shard: dQ, dK, dV from the forward's O and LSE
+    d_out = torch.randn(qkv[0].shape, generator=generator, device=device).to(torch.bfloat16)
+    grads = [torch.empty_like(qkv[0]) for _ in range(3)]
+    workspace = torch.empty(library().fk_flash_bwd_workspace_bytes(p1 - p0, FLASH["seq"]) // 4,
+                            dtype=torch.float32, device=device)
+
+    def flash_bwd_step():
+        check(library().fk_flash_bwd(qkv[0].data_ptr(), qkv[1].data_ptr(), qkv[2].data_ptr(), out.data_ptr(),
+                                     d_out.data_ptr(), lse.data_ptr(), grads[0].data_ptr(), grads[1].data_ptr(),
+                                     grads[2].data_ptr(), workspace.data_ptr(), p1 - p0, FLASH["seq"], 128 ** -0.5,
+                                     int(FLASH["causal"]), stream, flash_status.data_ptr()))
+
+    flash_bwd_step()
+    gemm.check_status(flash_status)
+    leaves = [t[:1].float().requires_grad_() for t in qkv]
+    torch.nn.functional.scaled_dot_product_attention(*[t.unsqueeze(0) for t in leaves]).backward(
+        d_out[:1].float().unsqueeze(0))
+    bwd_error = max(((g[:1].float() - leaf.grad).abs().max() / leaf.grad.abs().max()).item()
+                    for g, leaf in zip(grads, leaves))
+    if not bwd_error <= 2e-2:
+        raise RuntimeError(f"flash backward disagrees with fp32 autograd: {bwd_error} of the largest gradient")
+    bwd_seconds = max_over_ranks(time_steps(flash_bwd_step, args.steps, args.warmup, barrier))
+    bwd_value = 2.5 * flash_flops * args.steps / bwd_seconds / 1e12
+    del qkv, out, lse, d_out, grads, workspace, leaves
 
     # ---- the row kernels either side of the two contractions: rows split across ranks, HBM roofline
     from ferro_kittens_b200 import rows as row_kernels
@@ -389,6 +413,11 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                           "frac_of_measured_peak": flash_value / world / peaks["burst"],
                           "frac_of_nominal_2250": flash_value / world / 2250.0,
                           "max_abs_diff_vs_sdpa": flash_error},
+            "flash_bwd": {"config": {k: v for k, v in FLASH.items()}, "value": bwd_value, "unit": "TFLOP/s",
+                          "flops_counted": "10 * planes * seq^2 * 128 (five tile products; seven are executed)",
+                          "ms_per_step": bwd_seconds / args.steps * 1e3,
+                          "frac_of_measured_peak": bwd_value / world / peaks["burst"],
+                          "max_error_over_max_gradient_vs_fp32_autograd": bwd_error},
             "row_kernels": {"config": {"rows": rows_total, "columns": 128, "seed": ROW_KERNEL_SEED,
                                        "bytes_per_element": 4, "sharding": f"rows over {world} rank(s)"},
                             "peak": peaks["hbm"], "peak_unit": "GB/s", "peak_source": peaks["source"], **row_results},
@@ -442,6 +471,19 @@ def run_only(args, local_rank: int) -> None:
                           "ms_per_step": seconds / args.steps * 1e3,
                           "gbs": 4.0 * args.rows * 128 * args.steps / seconds / 1e9}), flush=True)
         return
+    elif args.only == "flash_bwd":
+        from ferro_kittens_b200 import flash_backward, flash_forward
+
+        planes, seq = args.planes, args.seq
+        generator = torch.Generator(device=device).manual_seed(FLASH["seed"])
+        q, kk, v, d_out = (torch.randn((planes, seq, 128), generator=generator, device=device).to(torch.bfloat16)
+                           for _ in range(4))
+        out, lse = flash_forward.run(q, kk, v, causal=args.causal, status=status)
+        workspace = torch.empty(2 * planes * seq, dtype=torch.float32, device=device)
+        fn = lambda: flash_backward.run(q, kk, v, out, d_out, lse, causal=args.causal, status=status,  # noqa: E731
+                                        workspace=workspace)
+        flops = 10.0 * planes * seq * seq * 128 * (0.5 if args.causal else 1.0)
+        name = f"flash_bwd_planes{planes}_seq{seq}_{'causal' if args.causal else 'full'}"
     else:
         planes, seq = args.planes, args.seq
         generator = torch.Generator(device=device).manual_seed(FLASH["seed"])
@@ -462,7 +504,7 @@ def run_only(args, local_rank: int) -> None:
 
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--only", choices=["gemm", "flash", "softmax", "layernorm", "groupnorm"],
+    parser.add_argument("--only", choices=["gemm", "flash", "flash_bwd", "softmax", "layernorm", "groupnorm"],
                         help="run one kernel alone (for profiling)")
     parser.add_argument("--rows", type=int, default=1 << 20, help="rows of 128 columns for the row kernels")
     parser.add_argument("--m", type=int, default=8192)

@@ -12,7 +12,7 @@
 //   dQ = dS K                                    dK = dS^T Q
 //
 // Three launches, nothing atomic, results independent of scheduling:
-//   1. `stats`: delta and lse * log2(e) per query row (memory-bound, reads O and dO once).
+//   1. `stats`: -delta and -lse * log2(e) per query row (memory-bound, reads O and dO once).
 //   2. one CTA per 128-key block owns K_j, V_j and the accumulators dV_j, dK_j in tensor memory and
 //      streams the query blocks past them. It computes the TRANSPOSED tiles S^T = K_j Q_i^T and
 //      dP^T = V_j dO_i^T so that keys are the tensor-memory lanes: P^T and dS^T are then A operands
@@ -23,10 +23,11 @@
 //      pair instead of 5, the price of not adding into dQ from many CTAs.)
 // Launches 2 and 3 are one kernel template. The element-wise step is split in two (P from S, then dS
 // from dP and the P kept in registers) and the MMA issue order interleaves blocks, so that the tensor
-// pipe works on one of the two fp32 tiles while the element-wise warps work on the other. Roles per CTA: warps 0-7 the element-wise step (warps
-// 0-3 columns 0-63, warps 4-7 columns 64-127 of the same 32 lanes; no reduction crosses a thread),
-// warp 8 the loader (TMA tiles through a two-stage ring, the per-column statistics by bulk copy),
-// warp 9 the MMA issue. Tensor memory: T1 (S or S^T; bf16 P over it) | T2 (dP; bf16 dS over it) |
+// pipe works on one of the two fp32 tiles while the element-wise warps work on the other. Roles per
+// CTA: warps 0-7 the element-wise step (two warps per lane quadrant, 64 columns each; no reduction
+// crosses a thread; four per quadrant measured slower), warp 8 the loader (TMA tiles through a
+// two-stage ring, the per-column statistics by bulk copy), warp 9 the MMA issue. Tensor memory: T1 (S or S^T; bf16 P over it) |
+// T2 (dP; bf16 dS over it) |
 // accumulator 0 | accumulator 1, 128 columns each. Every wait is bounded.
 
 #include "fk_host.h"
@@ -39,7 +40,12 @@ namespace flash_bwd {
 constexpr uint32_t kRows = 128;  // rows of every tile: a query block or a key block
 constexpr uint32_t kHead = 128;
 constexpr uint32_t kStages = 2;
-constexpr uint32_t kElementWarps = 8;
+#ifndef FK_BWD_ELEMENT_WARPS
+#define FK_BWD_ELEMENT_WARPS 8
+#endif
+constexpr uint32_t kElementWarps = FK_BWD_ELEMENT_WARPS;  // 8 or 16: four per lane quadrant split the columns
+constexpr uint32_t kThreadColumns = 128 / (kElementWarps / 4);  // columns of T a thread owns: 64 or 32
+static_assert(kElementWarps == 8 || kElementWarps == 16, "two or four warps per lane quadrant");
 constexpr uint32_t kLoaderWarp = kElementWarps;
 constexpr uint32_t kMmaWarp = kElementWarps + 1;
 constexpr uint32_t kThreads = (kElementWarps + 2) * 32;
@@ -51,7 +57,7 @@ constexpr uint32_t kT1 = 0, kT2 = 128, kAcc0 = 256, kAcc1 = 384;
 
 struct Plan {
     SharedPlan resident, ring, stats, resident_full, full, empty, t1_full, t2_full, p_ready, ds_ready, acc_done,
-        tmem_slot, stop, end;
+        staged, tmem_slot, stop, end;
     constexpr Plan()
         : resident(SharedPlan{}.tile_ring(kRows, kHead, 2, 2)),
           ring(resident.tile_ring(kRows, kHead, 2, 2 * kStages)),
@@ -64,7 +70,8 @@ struct Plan {
           p_ready(t2_full.semaphore()),
           ds_ready(p_ready.semaphore()),
           acc_done(ds_ready.semaphore()),
-          tmem_slot(acc_done.tmem_slot()),
+          staged(acc_done.semaphores(16)),  // [quadrant][column half][output]: one arrival each
+          tmem_slot(staged.tmem_slot()),
           stop(tmem_slot.word()),
           end(stop) {}
 };
@@ -85,7 +92,7 @@ enum StallCode : uint32_t {
     kMisaligned = 0x4ff,
 };
 
-// delta = rowsum(dO * O) and lse * log2(e), one query row per 16 lanes.
+// -lse * log2(e) and -delta = -rowsum(dO * O) (negated: they enter as addends), one query row per 16 lanes.
 __global__ void __launch_bounds__(256) stats_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
                                                     const float* __restrict__ lse, float* __restrict__ stats,
                                                     uint32_t planes, uint32_t seq) {
@@ -109,8 +116,8 @@ __global__ void __launch_bounds__(256) stats_kernel(const uint16_t* __restrict__
         for (uint32_t mask = 8; mask > 0; mask >>= 1) total += __shfl_xor_sync(0xffffffffu, total, mask);
         if (row < rows && chunk == 0) {
             const uint64_t plane = row / seq, at = row % seq;
-            stats[(2 * plane) * seq + at] = lse[row] * 1.4426950408889634f;
-            stats[(2 * plane + 1) * seq + at] = total;
+            stats[(2 * plane) * seq + at] = -lse[row] * 1.4426950408889634f;
+            stats[(2 * plane + 1) * seq + at] = -total;
         }
     }
 }
@@ -132,7 +139,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t resident = base + kPlan.resident.at;
     const uint32_t ring = base + kPlan.ring.at;
     const uint32_t stats_smem = base + kPlan.stats.at;
-    const float* const stats_view = reinterpret_cast<const float*>(dynamic_shared + kPlan.stats.at);
     const uint32_t resident_full = base + kPlan.resident_full.at;
     const uint32_t full = base + kPlan.full.at;
     const uint32_t empty = base + kPlan.empty.at;
@@ -141,6 +147,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t p_ready = base + kPlan.p_ready.at;
     const uint32_t ds_ready = base + kPlan.ds_ready.at;
     const uint32_t acc_done = base + kPlan.acc_done.at;
+    const uint32_t staged = base + kPlan.staged.at;
     const uint32_t slot = base + kPlan.tmem_slot.at;
     volatile uint32_t* stop_flag = reinterpret_cast<volatile uint32_t*>(dynamic_shared + kPlan.stop.at);
     volatile uint32_t* slot_ptr = reinterpret_cast<volatile uint32_t*>(dynamic_shared + kPlan.tmem_slot.at);
@@ -166,6 +173,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         mbar_init(p_ready, kElementWarps);
         mbar_init(ds_ready, kElementWarps);
         mbar_init(acc_done, 1);
+        for (uint32_t i = 0; i < 16; ++i) mbar_init(staged + 8 * i, 1);
         *stop_flag = 0;
         fence_mbarrier_init();
         prefetch_tensormap(&r0_map);
@@ -239,13 +247,14 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
         };
         // ACC (+)= A . B over the tile's 128 rows: A is the bf16 the element-wise warps left over T
-        // (rows 0-63 of the contraction in columns 0-31, rows 64-127 in columns 64-95), B the streamed
+        // (a thread's kThreadColumns contraction rows packed into the first half of its own columns), B the streamed
         // tile read MN-major: 16 rows per chunk, the second 64 head columns one subtile on.
         auto accumulate = [&](uint32_t acc_column, uint32_t t_column, uint32_t b_tile, bool keep) {
             const uint64_t b_desc = operand_descriptor(b_tile, kSubtileBytes);
 #pragma unroll
             for (uint32_t chunk = 0; chunk < kRows / 16; ++chunk)
-                mma_ts_if(leader, tmem + acc_column, tmem + t_column + 64 * (chunk / 4) + 8 * (chunk % 4),
+                mma_ts_if(leader, tmem + acc_column,
+                          tmem + t_column + kThreadColumns * (16 * chunk / kThreadColumns) + (16 * chunk % kThreadColumns) / 2,
                           b_desc + ((chunk * kMnMajorChunkBytes) >> 4), idesc_ts, (keep || chunk != 0) ? 1u : 0u);
         };
 
@@ -285,12 +294,16 @@ __global__ void __launch_bounds__(kThreads, 1)
         __syncwarp();
     } else {
         // ------------------------------------------------ element-wise step and epilogue
-        const uint32_t half = warp >> 2;            // which 64 columns of T / 64 head columns of an accumulator
+        const uint32_t part = warp >> 2;            // which kThreadColumns columns of T / head columns of an accumulator
         const uint32_t quadrant = warp & 3u;        // tensor-memory lanes this warp may touch
         const uint32_t row = 32 * quadrant + lane;  // lane of the tiles = row of the owned block
         const uint32_t lane_base = (32 * quadrant) << 16;
+        const uint32_t column0 = kThreadColumns * part;
+        constexpr uint32_t kChunks = kThreadColumns / 32;
         const float scale_log2 = scale * 1.4426950408889634f;
-        float row_lse = 0.0f, row_delta = 0.0f;
+        const float2 scale_log2_pair = make_float2(scale_log2, scale_log2);
+        const float2 scale_pair = make_float2(scale, scale);
+        float row_lse = 0.0f, row_delta = 0.0f;  // negated, as the workspace holds them
         if (!KV) {
             row_lse = stats[(2 * static_cast<size_t>(plane)) * seq + kRows * owner + row];
             row_delta = stats[(2 * static_cast<size_t>(plane) + 1) * seq + kRows * owner + row];
@@ -311,28 +324,47 @@ __global__ void __launch_bounds__(kThreads, 1)
                 break;
             }
             const bool diagonal = causal && block == owner;
-            const float* const column_stats = stats_view + s * (kStatsBytes / 4);
-            float p[64];
+            const uint32_t column_stats = stats_smem + s * kStatsBytes + column0 * 4;
+            float2 p[kThreadColumns / 2];
 #pragma unroll
-            for (uint32_t c = 0; c < 2; ++c) {
-                const uint32_t column0 = 64 * half + 32 * c;
+            for (uint32_t c = 0; c < kChunks; ++c) {
                 uint32_t score[32];
-                tmem_ld_32x32(tmem + lane_base + kT1 + column0, score);
-                tmem_wait_ld();
-                uint32_t p_words[16];
-#pragma unroll
-                for (uint32_t i = 0; i < 32; ++i) {
-                    const uint32_t column = column0 + i;
-                    const float lse2 = KV ? column_stats[column] : row_lse;
-                    // KV: lane = key, column = query, visible iff key <= query. Otherwise lane = query.
-                    const bool hidden = diagonal && (KV ? column < row : column > row);
-                    p[32 * c + i] = hidden ? 0.0f : ex2_approx(__uint_as_float(score[i]) * scale_log2 - lse2);
-                }
+                tmem_ld_32x32(tmem + lane_base + kT1 + column0 + 32 * c, score);
+                float2 offset[16];
                 if (KV) {
 #pragma unroll
-                    for (uint32_t i = 0; i < 16; ++i) p_words[i] = pack_bf16x2(p[32 * c + 2 * i], p[32 * c + 2 * i + 1]);
-                    // Over columns of this warp's own half that it has already read.
-                    tmem_st_32x16(tmem + lane_base + kT1 + 64 * half + 16 * c, p_words);
+                    for (uint32_t i = 0; i < 8; ++i) {
+                        uint32_t words[4];
+                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(words[0]), "=r"(words[1]), "=r"(words[2]), "=r"(words[3])
+                                     : "r"(column_stats + 128 * c + 16 * i));
+                        offset[2 * i] = make_float2(__uint_as_float(words[0]), __uint_as_float(words[1]));
+                        offset[2 * i + 1] = make_float2(__uint_as_float(words[2]), __uint_as_float(words[3]));
+                    }
+                }
+                tmem_wait_ld();
+#pragma unroll
+                for (uint32_t i = 0; i < 16; ++i) {
+                    const float2 x = __ffma2_rn(make_float2(__uint_as_float(score[2 * i]), __uint_as_float(score[2 * i + 1])),
+                                                scale_log2_pair, KV ? offset[i] : make_float2(row_lse, row_lse));
+                    p[16 * c + i] = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+                }
+                if (diagonal) {
+                    // KV: lane = key, column = query, visible iff key <= query. Otherwise lane = query.
+#pragma unroll
+                    for (uint32_t i = 0; i < 16; ++i) {
+                        const uint32_t column = column0 + 32 * c + 2 * i;
+                        if (KV ? column < row : column > row) p[16 * c + i].x = 0.0f;
+                        if (KV ? column + 1 < row : column + 1 > row) p[16 * c + i].y = 0.0f;
+                    }
+                }
+                if (KV) {
+                    uint32_t p_words[16];
+#pragma unroll
+                    for (uint32_t i = 0; i < 16; ++i) p_words[i] = pack_bf16x2(p[16 * c + i].x, p[16 * c + i].y);
+                    // Over the first half of this thread's own columns, all of which it has read by now
+                    // or (chunk 1's scores) lie in the second half.
+                    tmem_st_32x16(tmem + lane_base + kT1 + column0 + 16 * c, p_words);
                 }
             }
             if (KV) tmem_wait_st();
@@ -347,23 +379,32 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             tc_fence_after_sync();
 #pragma unroll
-            for (uint32_t c = 0; c < 2; ++c) {
-                const uint32_t column0 = 64 * half + 32 * c;
+            for (uint32_t c = 0; c < kChunks; ++c) {
                 uint32_t slope[32];
-                tmem_ld_32x32(tmem + lane_base + kT2 + column0, slope);
+                tmem_ld_32x32(tmem + lane_base + kT2 + column0 + 32 * c, slope);
+                float2 offset[16];
+                if (KV) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 8; ++i) {
+                        uint32_t words[4];
+                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(words[0]), "=r"(words[1]), "=r"(words[2]), "=r"(words[3])
+                                     : "r"(column_stats + kRows * 4 + 128 * c + 16 * i));
+                        offset[2 * i] = make_float2(__uint_as_float(words[0]), __uint_as_float(words[1]));
+                        offset[2 * i + 1] = make_float2(__uint_as_float(words[2]), __uint_as_float(words[3]));
+                    }
+                }
                 tmem_wait_ld();
                 uint32_t ds_words[16];
 #pragma unroll
                 for (uint32_t i = 0; i < 16; ++i) {
-                    float ds[2];
-#pragma unroll
-                    for (uint32_t e = 0; e < 2; ++e) {
-                        const float delta = KV ? column_stats[kRows + column0 + 2 * i + e] : row_delta;
-                        ds[e] = p[32 * c + 2 * i + e] * (__uint_as_float(slope[2 * i + e]) - delta) * scale;
-                    }
-                    ds_words[i] = pack_bf16x2(ds[0], ds[1]);
+                    // dS = scale * P * (dP - delta)
+                    const float2 centred = __fadd2_rn(make_float2(__uint_as_float(slope[2 * i]), __uint_as_float(slope[2 * i + 1])),
+                                                      KV ? offset[i] : make_float2(row_delta, row_delta));
+                    const float2 ds = __fmul2_rn(__fmul2_rn(p[16 * c + i], scale_pair), centred);
+                    ds_words[i] = pack_bf16x2(ds.x, ds.y);
                 }
-                tmem_st_32x16(tmem + lane_base + kT2 + 64 * half + 16 * c, ds_words);
+                tmem_st_32x16(tmem + lane_base + kT2 + column0 + 16 * c, ds_words);
             }
             tmem_wait_st();
             tc_fence_before_sync();
@@ -375,20 +416,22 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (live) {
             tc_fence_after_sync();
             // The resident tiles are dead once the last MMA retired: they stage the two outputs. This
-            // warp owns rows [32 q, 32 q + 32) of the [128, 64] subtile of head columns 64 half...
+            // warp owns rows [32 q, 32 q + 32) x kThreadColumns head columns of an accumulator; a store
+            // box is [32, 64], which one warp fills alone or two fill between them (the second arrives
+            // on the box's barrier, the first waits for it and stores).
 #pragma unroll 1
-            for (uint32_t which = KV ? 0u : 1u; which < 2; ++which) {
-                const uint32_t acc = tmem + lane_base + (which ? kAcc1 : kAcc0) + 64 * half;
+            for (uint32_t which = KV ? 0u : 1u; which < 2 && live; ++which) {
+                const uint32_t half = column0 / 64;
                 const uint32_t subtile = resident + which * kTileBytes + half * kSubtileBytes;
 #pragma unroll 1
-                for (uint32_t c = 0; c < 2; ++c) {
+                for (uint32_t c = 0; c < kChunks; ++c) {
                     uint32_t value[32];
-                    tmem_ld_32x32(acc + 32 * c, value);
+                    tmem_ld_32x32(tmem + lane_base + (which ? kAcc1 : kAcc0) + column0 + 32 * c, value);
                     tmem_wait_ld();
 #pragma unroll
                     for (uint32_t i = 0; i < 4; ++i) {
                         const uint32_t* v = value + 8 * i;
-                        st_shared_v4(subtile + swizzled_chunk_offset(row, 4 * c + i, 0),
+                        st_shared_v4(subtile + swizzled_chunk_offset(row, ((column0 + 32 * c) % 64) / 8 + i, 0),
                                      pack_bf16x2(__uint_as_float(v[0]), __uint_as_float(v[1])),
                                      pack_bf16x2(__uint_as_float(v[2]), __uint_as_float(v[3])),
                                      pack_bf16x2(__uint_as_float(v[4]), __uint_as_float(v[5])),
@@ -397,7 +440,18 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
                 fence_proxy_async_shared();
                 __syncwarp();
-                if (lane == 0) {
+                bool stores = true;
+                if (kThreadColumns == 32) {
+                    const uint32_t pair_bar = staged + 8 * (2 * (2 * quadrant + half) + which);
+                    if (part & 1u) {
+                        if (lane == 0) mbar_arrive(pair_bar);
+                        stores = false;
+                    } else if (!mbar_wait(pair_bar, 0, site, kStallElementAcc, 100 + which)) {
+                        live = false;
+                        stores = false;
+                    }
+                }
+                if (stores && lane == 0) {
                     tma_store_3d(which ? &out1_map : &out0_map, subtile + 32 * quadrant * 128,
                                  static_cast<int>(64 * half), static_cast<int>(kRows * owner + 32 * quadrant),
                                  static_cast<int>(plane));

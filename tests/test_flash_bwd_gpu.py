@@ -76,10 +76,10 @@ def test_sharp_rows_and_a_caller_workspace(device):
                                     workspace=workspace)
     torch.cuda.synchronize(device)
     gemm.check_status(status)
-    # The workspace holds lse * log2(e) and rowsum(dO * O).
-    assert torch.allclose(workspace.view(planes, 2, sequence)[:, 0], lse * 1.4426950408889634, rtol=1e-6, atol=1e-6)
+    # The workspace holds -lse * log2(e) and -rowsum(dO * O): they enter the kernels as addends.
+    assert torch.allclose(workspace.view(planes, 2, sequence)[:, 0], -lse * 1.4426950408889634, rtol=1e-6, atol=1e-6)
     delta = (out.float() * d_out.float()).sum(dim=-1)
-    assert torch.allclose(workspace.view(planes, 2, sequence)[:, 1], delta, rtol=1e-4, atol=1e-3)
+    assert torch.allclose(workspace.view(planes, 2, sequence)[:, 1], -delta, rtol=1e-4, atol=1e-3)
     for plane in range(planes):
         expected = oracle.flash_backward(_words(q[plane]), _words(k[plane]), _words(v[plane]), _words(d_out[plane]),
                                          scale, True)
