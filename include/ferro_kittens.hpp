@@ -225,4 +225,49 @@ inline void run(void* stream, uint64_t q, uint64_t k, uint64_t v, uint64_t o_bf1
 
 }  // namespace flash_forward
 
+/// Flash-attention backward (no kernel of this name in the crate; see fk_flash_bwd): gradients of
+/// `flash_forward::run` with respect to q, k, v from its output and log-sum-exp. `workspace` holds
+/// `workspace_floats(planes, sequence)` floats on the device.
+namespace flash_backward {
+
+inline std::size_t workspace_floats(uint32_t planes, uint32_t sequence) {
+    return static_cast<std::size_t>(fk_flash_bwd_workspace_bytes(planes, sequence) / sizeof(float));
+}
+inline void run(void* stream, uint64_t q, uint64_t k, uint64_t v, uint64_t o, uint64_t d_o, const float* lse,
+                uint64_t dq, uint64_t dk, uint64_t dv, float* workspace, uint32_t planes, uint32_t sequence,
+                float scale, bool causal, uint32_t* status = nullptr) {
+    check(fk_flash_bwd(reinterpret_cast<const void*>(q), reinterpret_cast<const void*>(k),
+                       reinterpret_cast<const void*>(v), reinterpret_cast<const void*>(o),
+                       reinterpret_cast<const void*>(d_o), lse, reinterpret_cast<void*>(dq),
+                       reinterpret_cast<void*>(dk), reinterpret_cast<void*>(dv), workspace, planes, sequence, scale,
+                       causal ? 1 : 0, stream, status));
+}
+
+}  // namespace flash_backward
+
+/// The row kernels (examples/src/softmax.rs, examples/src/layernorm.rs), over rows of 128 bf16 columns.
+namespace rows {
+
+constexpr std::size_t ROWS = 128, COLUMNS = 128;
+constexpr float EPSILON = 1e-5f;  // examples/src/layernorm.rs:313
+
+inline void softmax_rows(void* stream, uint64_t source, uint64_t destination, uint32_t rows_per_plane,
+                         uint32_t planes, uint32_t* status = nullptr) {
+    check(fk_softmax_rows(reinterpret_cast<const void*>(source), reinterpret_cast<void*>(destination), rows_per_plane,
+                          planes, stream, status));
+}
+inline void layernorm_rows(void* stream, uint64_t source, uint64_t gamma, uint64_t beta, uint64_t destination,
+                           uint32_t row_count, float epsilon = EPSILON, uint32_t* status = nullptr) {
+    check(fk_layernorm_rows(reinterpret_cast<const void*>(source), reinterpret_cast<const void*>(gamma),
+                            reinterpret_cast<const void*>(beta), reinterpret_cast<void*>(destination), row_count,
+                            epsilon, stream, status));
+}
+inline void groupnorm_tile(void* stream, uint64_t source, uint64_t destination, uint32_t row_count,
+                           float epsilon = EPSILON, uint32_t* status = nullptr) {
+    check(fk_groupnorm_tile(reinterpret_cast<const void*>(source), reinterpret_cast<void*>(destination), row_count,
+                            epsilon, stream, status));
+}
+
+}  // namespace rows
+
 }  // namespace kittens
