@@ -322,8 +322,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     from ferro_kittens_b200 import rows as row_kernels
 
     rows_total = ROW_KERNEL_ROWS
-    r0, r1 = rows_total * rank // world, rows_total * (rank + 1) // world
-    r0, r1 = r0 // 128 * 128, r1 // 128 * 128
+    r0, r1 = shard.row_tiles(rows_total, world, rank)
     generator = torch.Generator(device=device).manual_seed(ROW_KERNEL_SEED)
     activations = (torch.randn((r1 - r0, 128), generator=generator, device=device) * 2).to(torch.bfloat16)
     normalised = torch.empty_like(activations)

@@ -477,25 +477,99 @@ extern "C" int fk_gemm_bf16(const void* a, const void* b, void* c, uint32_t m, u
     return fk_gemm(a, b, c, m, n, k, ldc, group, 0, stream, device_status);
 }
 
+// Streams and events of the pipelined host-buffer entry, one set per device, created on first use.
+namespace {
+constexpr uint32_t kHostChunks = 8;
+struct HostPipeline {
+    cudaStream_t upload = nullptr, compute = nullptr, download = nullptr;
+    cudaEvent_t a_ready = nullptr, b_ready[kHostChunks] = {}, c_ready[kHostChunks] = {}, idle = nullptr;
+};
+std::mutex host_pipeline_guard;
+HostPipeline host_pipelines[64];
+
+int host_pipeline(HostPipeline** out) {
+    int device = 0;
+    FK_CUDA(cudaGetDevice(&device));
+    if (device >= 64) return fk_fail(FK_ERR_INVALID, "device index out of range");
+    std::lock_guard<std::mutex> lock(host_pipeline_guard);
+    HostPipeline& pipe = host_pipelines[device];
+    if (!pipe.upload) {
+        FK_CUDA(cudaStreamCreateWithFlags(&pipe.upload, cudaStreamNonBlocking));
+        FK_CUDA(cudaStreamCreateWithFlags(&pipe.compute, cudaStreamNonBlocking));
+        FK_CUDA(cudaStreamCreateWithFlags(&pipe.download, cudaStreamNonBlocking));
+        FK_CUDA(cudaEventCreateWithFlags(&pipe.a_ready, cudaEventDisableTiming));
+        FK_CUDA(cudaEventCreateWithFlags(&pipe.idle, cudaEventDisableTiming));
+        for (uint32_t i = 0; i < kHostChunks; ++i) {
+            FK_CUDA(cudaEventCreateWithFlags(&pipe.b_ready[i], cudaEventDisableTiming));
+            FK_CUDA(cudaEventCreateWithFlags(&pipe.c_ready[i], cudaEventDisableTiming));
+        }
+    }
+    *out = &pipe;
+    return FK_OK;
+}
+}  // namespace
+
+// Upload, compute and read-back overlap: A goes up first, then B in column chunks; the GEMM of a
+// chunk starts when its rows of B have landed, and its columns of C go back (a strided copy into the
+// caller's [m, n]) while later chunks upload and compute. PCIe is full duplex, so the whole call
+// costs about the upload alone; done in sequence it cost upload + compute + read-back. The copies
+// overlap only from page-locked host memory; from pageable memory the call is still correct.
 extern "C" int fk_gemm_bf16_host(const uint16_t* a_host, const uint16_t* b_host, uint16_t* c_host,
                                  uint32_t m, uint32_t n, uint32_t k, uint32_t group) {
     if (!a_host || !b_host || !c_host) return fk_fail(FK_ERR_INVALID, "an operand pointer is null");
+    if (m == 0 || n == 0 || k == 0 || m % (2 * gemm::kBlockM) || n % gemm::kBlockN || k % gemm::kBlockK)
+        return fk_fail(FK_ERR_SHAPE, "%ux%ux%u does not divide the %ux%ux%u tiling", m, n, k,
+                       2 * gemm::kBlockM, gemm::kBlockN, gemm::kBlockK);
     const size_t a_bytes = size_t(m) * k * 2, b_bytes = size_t(n) * k * 2, c_bytes = size_t(m) * n * 2;
     void *a = nullptr, *b = nullptr, *c = nullptr;
     uint32_t* status_words = nullptr;
+    HostPipeline* pipe = nullptr;
     int status = scratch(0, a_bytes, &a);
     if (status == FK_OK) status = scratch(1, b_bytes, &b);
     if (status == FK_OK) status = scratch(2, c_bytes, &c);
     if (status == FK_OK) status = scratch_status(&status_words);
+    if (status == FK_OK) status = host_pipeline(&pipe);
     if (status != FK_OK) return status;
-    cudaStream_t stream = nullptr;
-    FK_CUDA(cudaMemsetAsync(status_words, 0, 32, stream));
-    FK_CUDA(cudaMemcpyAsync(a, a_host, a_bytes, cudaMemcpyHostToDevice, stream));
-    FK_CUDA(cudaMemcpyAsync(b, b_host, b_bytes, cudaMemcpyHostToDevice, stream));
-    status = fk_gemm_bf16(a, b, c, m, n, k, n, group, stream, status_words);
+
+    // Whole 256-column tiles per chunk, at most kHostChunks chunks.
+    const uint32_t tiles = n / gemm::kBlockN;
+    const uint32_t chunk_tiles = (tiles + kHostChunks - 1) / kHostChunks;
+    const uint32_t chunk = chunk_tiles * gemm::kBlockN;
+    const uint32_t chunks = (n + chunk - 1) / chunk;
+
+    // The staging buffers are shared with earlier calls on the default stream: start after them.
+    FK_CUDA(cudaEventRecord(pipe->idle, nullptr));
+    FK_CUDA(cudaStreamWaitEvent(pipe->upload, pipe->idle, 0));
+    FK_CUDA(cudaStreamWaitEvent(pipe->compute, pipe->idle, 0));
+    FK_CUDA(cudaStreamWaitEvent(pipe->download, pipe->idle, 0));
+    FK_CUDA(cudaMemsetAsync(status_words, 0, 32, pipe->compute));
+    FK_CUDA(cudaMemcpyAsync(a, a_host, a_bytes, cudaMemcpyHostToDevice, pipe->upload));
+    FK_CUDA(cudaEventRecord(pipe->a_ready, pipe->upload));
+    FK_CUDA(cudaStreamWaitEvent(pipe->compute, pipe->a_ready, 0));
+    for (uint32_t i = 0; i < chunks; ++i) {
+        const uint32_t column0 = i * chunk, columns = (n - column0 < chunk) ? n - column0 : chunk;
+        uint8_t* b_chunk = static_cast<uint8_t*>(b) + size_t(column0) * k * 2;
+        uint8_t* c_chunk = static_cast<uint8_t*>(c) + size_t(column0) * 2;
+        FK_CUDA(cudaMemcpyAsync(b_chunk, b_host + size_t(column0) * k, size_t(columns) * k * 2,
+                                cudaMemcpyHostToDevice, pipe->upload));
+        FK_CUDA(cudaEventRecord(pipe->b_ready[i], pipe->upload));
+        FK_CUDA(cudaStreamWaitEvent(pipe->compute, pipe->b_ready[i], 0));
+        status = fk_gemm_bf16(a, b_chunk, c_chunk, m, columns, k, n, group, pipe->compute, status_words);
+        if (status != FK_OK) break;
+        FK_CUDA(cudaEventRecord(pipe->c_ready[i], pipe->compute));
+        FK_CUDA(cudaStreamWaitEvent(pipe->download, pipe->c_ready[i], 0));
+        FK_CUDA(cudaMemcpy2DAsync(c_host + column0, size_t(n) * 2, c_chunk, size_t(n) * 2, size_t(columns) * 2, m,
+                                  cudaMemcpyDeviceToHost, pipe->download));
+    }
+    // Whatever happened, leave no work of this call in flight behind the return.
+    const cudaError_t up = cudaStreamSynchronize(pipe->upload);
+    const cudaError_t run = cudaStreamSynchronize(pipe->compute);
+    const cudaError_t down = cudaStreamSynchronize(pipe->download);
     if (status != FK_OK) return status;
-    FK_CUDA(cudaMemcpyAsync(c_host, c, c_bytes, cudaMemcpyDeviceToHost, stream));
-    return fk_status_check(status_words, stream);
+    FK_CUDA(up);
+    FK_CUDA(run);
+    FK_CUDA(down);
+    return fk_status_check(status_words, pipe->compute);
 }
 
 // ------------------------------------------------------------------ no-allocation variant

@@ -2,7 +2,9 @@
 no collective on the data path.
 
 The GEMM replicates A and gives each rank a contiguous block of B's rows (C's
-columns); attention gives each rank a contiguous range of (batch x head) planes.
+columns); attention (forward and backward) gives each rank a contiguous range of
+(batch x head) planes; the row kernels give each rank a contiguous range of whole
+128-row tiles.
 """
 from __future__ import annotations
 
@@ -32,3 +34,12 @@ def planes(total: int, world: int, rank: int) -> tuple[int, int]:
     base, extra = divmod(total, world)
     start = rank * base + min(rank, extra)
     return start, start + base + (1 if rank < extra else 0)
+
+
+def row_tiles(rows: int, world: int, rank: int, tile: int = 128) -> tuple[int, int]:
+    """[start, stop) of the rows rank ``rank`` owns, in whole ``tile``-row tiles (the unit the
+    whole-tile statistic is taken over, so no tile is ever split between GPUs)."""
+    if rows % tile:
+        raise ValueError(f"{rows} rows is not a whole number of {tile}-row tiles")
+    start, stop = planes(rows // tile, world, rank)
+    return start * tile, stop * tile

@@ -35,6 +35,16 @@ def test_planes_tile_the_batch():
         assert all(a[1] == b[0] for a, b in zip(blocks, blocks[1:]))
 
 
+def test_row_tiles_never_split_a_tile():
+    for rows, world in [(4 * 1024 * 1024, 8), (128 * 7, 4), (128, 2), (128 * 149, 8)]:
+        blocks = [shard.row_tiles(rows, world, rank) for rank in range(world)]
+        assert blocks[0][0] == 0 and blocks[-1][1] == rows
+        assert all(a[1] == b[0] for a, b in zip(blocks, blocks[1:]))
+        assert all(start % 128 == 0 and stop % 128 == 0 for start, stop in blocks)
+    with pytest.raises(ValueError):
+        shard.row_tiles(130, 2, 0)
+
+
 def _free_port() -> int:
     with socket.socket() as probe:
         probe.bind(("127.0.0.1", 0))
