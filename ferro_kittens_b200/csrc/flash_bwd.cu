@@ -26,7 +26,8 @@
 // pipe works on one of the two fp32 tiles while the element-wise warps work on the other. Roles per
 // CTA: warps 0-7 the element-wise step (two warps per lane quadrant, 64 columns each; no reduction
 // crosses a thread; four per quadrant measured slower), warp 8 the loader (TMA tiles through a
-// two-stage ring, the per-column statistics by bulk copy), warp 9 the MMA issue. Tensor memory: T1 (S or S^T; bf16 P over it) |
+// three-slot ring for the tile a block reads last, the per-column statistics by bulk copy), warp 9 the
+// MMA issue, warp 10 a second loader (a two-slot ring for the other streamed tile). Tensor memory: T1 (S or S^T; bf16 P over it) |
 // T2 (dP; bf16 dS over it) |
 // accumulator 0 | accumulator 1, 128 columns each. Every wait is bounded.
 
@@ -39,16 +40,18 @@ namespace flash_bwd {
 
 constexpr uint32_t kRows = 128;  // rows of every tile: a query block or a key block
 constexpr uint32_t kHead = 128;
-constexpr uint32_t kStages = 2;
-#ifndef FK_BWD_ELEMENT_WARPS
-#define FK_BWD_ELEMENT_WARPS 8
-#endif
-constexpr uint32_t kElementWarps = FK_BWD_ELEMENT_WARPS;  // 8 or 16: four per lane quadrant split the columns
-constexpr uint32_t kThreadColumns = 128 / (kElementWarps / 4);  // columns of T a thread owns: 64 or 32
-static_assert(kElementWarps == 8 || kElementWarps == 16, "two or four warps per lane quadrant");
-constexpr uint32_t kLoaderWarp = kElementWarps;
+// The two streamed tiles of a block leave their slots at different times (the second MMA pair
+// reads x0 last, after dS is ready), so each has its own ring; a single two-slot ring made every
+// block wait out a TMA round trip.
+constexpr uint32_t kSlots0 = 3;  // Q_i (key-block owners) / K_j: read by the first and the last product of a block
+constexpr uint32_t kSlots1 = 2;  // dO_i / V_j
+constexpr uint32_t kSlotsStats = 2;
+constexpr uint32_t kElementWarps = 8;     // two per lane quadrant, 64 columns of T each (four measured slower)
+constexpr uint32_t kThreadColumns = 64;   // columns of T a thread owns
+constexpr uint32_t kLoaderWarp = kElementWarps;       // x0 ring and the column statistics
 constexpr uint32_t kMmaWarp = kElementWarps + 1;
-constexpr uint32_t kThreads = (kElementWarps + 2) * 32;
+constexpr uint32_t kLoaderWarp1 = kElementWarps + 2;  // x1 ring
+constexpr uint32_t kThreads = (kElementWarps + 3) * 32;
 constexpr uint32_t kSubtileBytes = kRows * 64 * 2;
 constexpr uint32_t kTileBytes = 2 * kSubtileBytes;
 constexpr uint32_t kStatsBytes = 2 * kRows * 4;  // lse * log2(e) and delta of one query block
@@ -56,22 +59,26 @@ constexpr uint32_t kTmemColumns = 512;
 constexpr uint32_t kT1 = 0, kT2 = 128, kAcc0 = 256, kAcc1 = 384;
 
 struct Plan {
-    SharedPlan resident, ring, stats, resident_full, full, empty, t1_full, t2_full, p_ready, ds_ready, acc_done,
-        staged, tmem_slot, stop, end;
+    SharedPlan resident, ring0, ring1, stats, resident_full, full0, empty0, full1, empty1, stats_full, stats_empty,
+        t1_full, t2_full, p_ready, ds_ready, acc_done, tmem_slot, stop, end;
     constexpr Plan()
         : resident(SharedPlan{}.tile_ring(kRows, kHead, 2, 2)),
-          ring(resident.tile_ring(kRows, kHead, 2, 2 * kStages)),
-          stats(ring.reserve(kStages * kStatsBytes, 16)),
+          ring0(resident.tile_ring(kRows, kHead, 2, kSlots0)),
+          ring1(ring0.tile_ring(kRows, kHead, 2, kSlots1)),
+          stats(ring1.reserve(kSlotsStats * kStatsBytes, 16)),
           resident_full(stats.semaphore()),
-          full(resident_full.semaphores(kStages)),
-          empty(full.semaphores(kStages)),
-          t1_full(empty.semaphore()),
+          full0(resident_full.semaphores(kSlots0)),
+          empty0(full0.semaphores(kSlots0)),
+          full1(empty0.semaphores(kSlots1)),
+          empty1(full1.semaphores(kSlots1)),
+          stats_full(empty1.semaphores(kSlotsStats)),
+          stats_empty(stats_full.semaphores(kSlotsStats)),
+          t1_full(stats_empty.semaphore()),
           t2_full(t1_full.semaphore()),
           p_ready(t2_full.semaphore()),
           ds_ready(p_ready.semaphore()),
           acc_done(ds_ready.semaphore()),
-          staged(acc_done.semaphores(16)),  // [quadrant][column half][output]: one arrival each
-          tmem_slot(staged.tmem_slot()),
+          tmem_slot(acc_done.tmem_slot()),
           stop(tmem_slot.word()),
           end(stop) {}
 };
@@ -137,17 +144,18 @@ __global__ void __launch_bounds__(kThreads, 1)
         return;
     }
     const uint32_t resident = base + kPlan.resident.at;
-    const uint32_t ring = base + kPlan.ring.at;
+    const uint32_t ring0 = base + kPlan.ring0.at;
+    const uint32_t ring1 = base + kPlan.ring1.at;
     const uint32_t stats_smem = base + kPlan.stats.at;
     const uint32_t resident_full = base + kPlan.resident_full.at;
-    const uint32_t full = base + kPlan.full.at;
-    const uint32_t empty = base + kPlan.empty.at;
+    const uint32_t full0 = base + kPlan.full0.at, empty0 = base + kPlan.empty0.at;
+    const uint32_t full1 = base + kPlan.full1.at, empty1 = base + kPlan.empty1.at;
+    const uint32_t stats_full = base + kPlan.stats_full.at, stats_empty = base + kPlan.stats_empty.at;
     const uint32_t t1_full = base + kPlan.t1_full.at;
     const uint32_t t2_full = base + kPlan.t2_full.at;
     const uint32_t p_ready = base + kPlan.p_ready.at;
     const uint32_t ds_ready = base + kPlan.ds_ready.at;
     const uint32_t acc_done = base + kPlan.acc_done.at;
-    const uint32_t staged = base + kPlan.staged.at;
     const uint32_t slot = base + kPlan.tmem_slot.at;
     volatile uint32_t* stop_flag = reinterpret_cast<volatile uint32_t*>(dynamic_shared + kPlan.stop.at);
     volatile uint32_t* slot_ptr = reinterpret_cast<volatile uint32_t*>(dynamic_shared + kPlan.tmem_slot.at);
@@ -164,16 +172,23 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     if (threadIdx.x == 0) {
         mbar_init(resident_full, 1);
-        for (uint32_t s = 0; s < kStages; ++s) {
-            mbar_init(full + 8 * s, 1);
-            mbar_init(empty + 8 * s, 1);
+        for (uint32_t i = 0; i < kSlots0; ++i) {
+            mbar_init(full0 + 8 * i, 1);
+            mbar_init(empty0 + 8 * i, 1);
+        }
+        for (uint32_t i = 0; i < kSlots1; ++i) {
+            mbar_init(full1 + 8 * i, 1);
+            mbar_init(empty1 + 8 * i, 1);
+        }
+        for (uint32_t i = 0; i < kSlotsStats; ++i) {
+            mbar_init(stats_full + 8 * i, 1);
+            mbar_init(stats_empty + 8 * i, kElementWarps);
         }
         mbar_init(t1_full, 1);
         mbar_init(t2_full, 1);
         mbar_init(p_ready, kElementWarps);
         mbar_init(ds_ready, kElementWarps);
         mbar_init(acc_done, 1);
-        for (uint32_t i = 0; i < 16; ++i) mbar_init(staged + 8 * i, 1);
         *stop_flag = 0;
         fence_mbarrier_init();
         prefetch_tensormap(&r0_map);
@@ -190,9 +205,18 @@ __global__ void __launch_bounds__(kThreads, 1)
     tc_fence_after_sync();
     const uint32_t tmem = *slot_ptr;
     const StallSite site{status, stop_flag, 0};
+#ifdef FK_BWD_TRACE
+    // Development build: clock stamps of the first blocks of CTA (0, 0), after the status words.
+    auto trace = [&](uint32_t role, uint32_t block, uint32_t point) {
+        if (blockIdx.x == 0 && blockIdx.y == 0 && block < 24 && lane == 0)
+            reinterpret_cast<long long*>(status + 8)[(role * 24 + block) * 4 + point] = clock64();
+    };
+#else
+    auto trace = [](uint32_t, uint32_t, uint32_t) {};
+#endif
 
     if (warp == kLoaderWarp) {
-        // ------------------------------------------------ loader
+        // ------------------------------------------------ loader: resident tiles, the x0 ring, the statistics
         if (lane == 0) {
             mbar_arrive_expect_tx(resident_full, 2 * kTileBytes);
             for (uint32_t half = 0; half < 2; ++half) {
@@ -202,26 +226,37 @@ __global__ void __launch_bounds__(kThreads, 1)
                             static_cast<int>(kRows * owner), static_cast<int>(plane), resident_full);
             }
             for (uint32_t n = 0; n < count; ++n) {
-                const uint32_t s = n % kStages, block = first + n;
-                if (!mbar_wait(empty + 8 * s, ((n / kStages) & 1u) ^ 1u, site, kStallLoader, n)) break;
-                mbar_arrive_expect_tx(full + 8 * s, 2 * kTileBytes + (KV ? kStatsBytes : 0u));
-                const uint32_t x0 = ring + (2 * s) * kTileBytes, x1 = x0 + kTileBytes;
-                for (uint32_t half = 0; half < 2; ++half) {
-                    tma_load_3d(x0 + half * kSubtileBytes, &x0_map, static_cast<int>(64 * half),
-                                static_cast<int>(kRows * block), static_cast<int>(plane), full + 8 * s);
-                    tma_load_3d(x1 + half * kSubtileBytes, &x1_map, static_cast<int>(64 * half),
-                                static_cast<int>(kRows * block), static_cast<int>(plane), full + 8 * s);
-                }
+                const uint32_t s = n % kSlots0, block = first + n;
+                if (!mbar_wait(empty0 + 8 * s, ((n / kSlots0) & 1u) ^ 1u, site, kStallLoader, n)) break;
+                mbar_arrive_expect_tx(full0 + 8 * s, kTileBytes);
+                for (uint32_t half = 0; half < 2; ++half)
+                    tma_load_3d(ring0 + s * kTileBytes + half * kSubtileBytes, &x0_map, static_cast<int>(64 * half),
+                                static_cast<int>(kRows * block), static_cast<int>(plane), full0 + 8 * s);
                 if (KV) {
                     // The streamed query block's statistics, one value per COLUMN of the transposed tiles.
+                    const uint32_t ss = n % kSlotsStats;
+                    if (!mbar_wait(stats_empty + 8 * ss, ((n / kSlotsStats) & 1u) ^ 1u, site, kStallLoader, n)) break;
+                    mbar_arrive_expect_tx(stats_full + 8 * ss, kStatsBytes);
                     const float* source = stats + (2 * static_cast<size_t>(plane)) * seq + kRows * block;
                     for (uint32_t which = 0; which < 2; ++which)
                         asm volatile(
                             "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                                stats_smem + s * kStatsBytes + which * kRows * 4),
-                            "l"(source + which * static_cast<size_t>(seq)), "r"(kRows * 4), "r"(full + 8 * s)
+                                stats_smem + ss * kStatsBytes + which * kRows * 4),
+                            "l"(source + which * static_cast<size_t>(seq)), "r"(kRows * 4), "r"(stats_full + 8 * ss)
                             : "memory");
                 }
+            }
+        }
+    } else if (warp == kLoaderWarp1) {
+        // ------------------------------------------------ loader: the x1 ring
+        if (lane == 0) {
+            for (uint32_t n = 0; n < count; ++n) {
+                const uint32_t s = n % kSlots1, block = first + n;
+                if (!mbar_wait(empty1 + 8 * s, ((n / kSlots1) & 1u) ^ 1u, site, kStallLoader, n)) break;
+                mbar_arrive_expect_tx(full1 + 8 * s, kTileBytes);
+                for (uint32_t half = 0; half < 2; ++half)
+                    tma_load_3d(ring1 + s * kTileBytes + half * kSubtileBytes, &x1_map, static_cast<int>(64 * half),
+                                static_cast<int>(kRows * block), static_cast<int>(plane), full1 + 8 * s);
             }
         }
     } else if (warp == kMmaWarp) {
@@ -261,38 +296,51 @@ __global__ void __launch_bounds__(kThreads, 1)
         // Issue order per block n: [P(n) ready] dV += P^T dO; S(n+1); [dS(n) ready] dK/dQ += dS^T Q;
         // dP(n+1). The tensor pipe runs in issue order, so S(n+1) cannot overwrite P(n) before the MMA
         // that reads it, nor dP(n+1) dS(n); and while the element-wise warps work on one of the two
-        // tiles the pipe has the other's products to run.
+        // tiles the pipe has the other's products to run. x1(n) is last read by dV's product (key-block
+        // owners) or by dP's (query-block owners); x0(n) by the block's last product.
+        const auto x0_of = [&](uint32_t n) { return ring0 + (n % kSlots0) * kTileBytes; };
+        const auto x1_of = [&](uint32_t n) { return ring1 + (n % kSlots1) * kTileBytes; };
         bool live = wait(resident_full, 0, kStallMmaResident, 0);
-        if (live && count != 0) live = wait(full, 0, kStallMmaStream, 0);
+        if (live && count != 0) live = wait(full0, 0, kStallMmaStream, 0);
         if (live && count != 0) {
-            transposed_product(kT1, resident, ring);                            // S^T = K Q^T   |  S = Q K^T
+            transposed_product(kT1, resident, x0_of(0));  // S^T = K Q^T   |  S = Q K^T
             mma_commit_if<1>(leader, t1_full);
-            transposed_product(kT2, resident + kTileBytes, ring + kTileBytes);  // dP^T = V dO^T | dP = dO V^T
+            live = wait(full1, 0, kStallMmaStream, 0);
+        }
+        if (live && count != 0) {
+            transposed_product(kT2, resident + kTileBytes, x1_of(0));  // dP^T = V dO^T | dP = dO V^T
             mma_commit_if<1>(leader, t2_full);
+            if (!KV) mma_commit_if<1>(leader, empty1);
         }
         for (uint32_t n = 0; live && n < count; ++n) {
-            const uint32_t s = n % kStages, next = (n + 1) % kStages;
-            const uint32_t x0 = ring + (2 * s) * kTileBytes, x1 = x0 + kTileBytes;
-            const uint32_t y0 = ring + (2 * next) * kTileBytes, y1 = y0 + kTileBytes;
             const bool more = n + 1 < count;
             if (!wait(p_ready, n & 1u, kStallMmaP, n)) break;
-            if (KV) accumulate(kAcc0, kT1, x1, n != 0);  // dV += P^T dO
+            trace(1, n, 0);
+            if (KV) {
+                accumulate(kAcc0, kT1, x1_of(n), n != 0);  // dV += P^T dO
+                mma_commit_if<1>(leader, empty1 + 8 * (n % kSlots1));
+            }
             if (more) {
-                if (!wait(full + 8 * next, ((n + 1) / kStages) & 1u, kStallMmaStream, n + 1)) break;
-                transposed_product(kT1, resident, y0);
+                if (!wait(full0 + 8 * ((n + 1) % kSlots0), ((n + 1) / kSlots0) & 1u, kStallMmaStream, n + 1)) break;
+                transposed_product(kT1, resident, x0_of(n + 1));
                 mma_commit_if<1>(leader, t1_full);
             }
+            trace(1, n, 1);
             if (!wait(ds_ready, n & 1u, kStallMmaDs, n)) break;
-            accumulate(kAcc1, kT2, x0, n != 0);  // dK += dS^T Q  |  dQ += dS K
-            mma_commit_if<1>(leader, empty + 8 * s);
+            trace(1, n, 2);
+            accumulate(kAcc1, kT2, x0_of(n), n != 0);  // dK += dS^T Q  |  dQ += dS K
+            mma_commit_if<1>(leader, empty0 + 8 * (n % kSlots0));
             if (more) {
-                transposed_product(kT2, resident + kTileBytes, y1);
+                if (!wait(full1 + 8 * ((n + 1) % kSlots1), ((n + 1) / kSlots1) & 1u, kStallMmaStream, n + 1)) break;
+                transposed_product(kT2, resident + kTileBytes, x1_of(n + 1));
                 mma_commit_if<1>(leader, t2_full);
+                if (!KV) mma_commit_if<1>(leader, empty1 + 8 * ((n + 1) % kSlots1));
             }
+            trace(1, n, 3);
         }
         mma_commit_if<1>(leader, acc_done);
         __syncwarp();
-    } else {
+    } else if (warp < kElementWarps) {
         // ------------------------------------------------ element-wise step and epilogue
         const uint32_t part = warp >> 2;            // which kThreadColumns columns of T / head columns of an accumulator
         const uint32_t quadrant = warp & 3u;        // tensor-memory lanes this warp may touch
@@ -310,16 +358,15 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         bool live = true;
         for (uint32_t n = 0; live && n < count; ++n) {
-            const uint32_t s = n % kStages, block = first + n;
+            const uint32_t s = n % kSlotsStats, block = first + n;
             // ---- first half of the step: P from S, while the pipe computes dP
             if (!mbar_wait(t1_full, n & 1u, site, kStallElementT, n)) {
                 live = false;
                 break;
             }
             tc_fence_after_sync();
-            // The column statistics arrived by bulk copy on the stage's own barrier (complete by now:
-            // the MMAs just waited for were issued after it); observe it before reading them.
-            if (KV && !mbar_wait(full + 8 * s, (n / kStages) & 1u, site, kStallElementT, n)) {
+            if (warp == 0) trace(0, n, 0);
+            if (KV && !mbar_wait(stats_full + 8 * s, (n / kSlotsStats) & 1u, site, kStallElementT, n)) {
                 live = false;
                 break;
             }
@@ -371,6 +418,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_ready);  // P is in place (KV), and S has been consumed
+            if (warp == 0) trace(0, n, 1);
 
             // ---- second half: dS from dP and the P still in registers, while the pipe runs dV and S(n+1)
             if (!mbar_wait(t2_full, n & 1u, site, kStallElementT2, n)) {
@@ -378,6 +426,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 break;
             }
             tc_fence_after_sync();
+            if (warp == 0) trace(0, n, 2);
 #pragma unroll
             for (uint32_t c = 0; c < kChunks; ++c) {
                 uint32_t slope[32];
@@ -409,16 +458,18 @@ __global__ void __launch_bounds__(kThreads, 1)
             tmem_wait_st();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(ds_ready);
+            if (lane == 0) {
+                mbar_arrive(ds_ready);
+                if (KV) mbar_arrive(stats_empty + 8 * s);  // the block's statistics have been read
+            }
+            if (warp == 0) trace(0, n, 3);
         }
 
         if (live && !mbar_wait(acc_done, 0, site, kStallElementAcc, count)) live = false;
         if (live) {
             tc_fence_after_sync();
             // The resident tiles are dead once the last MMA retired: they stage the two outputs. This
-            // warp owns rows [32 q, 32 q + 32) x kThreadColumns head columns of an accumulator; a store
-            // box is [32, 64], which one warp fills alone or two fill between them (the second arrives
-            // on the box's barrier, the first waits for it and stores).
+            // warp owns rows [32 q, 32 q + 32) x 64 head columns of an accumulator: one [32, 64] store box.
 #pragma unroll 1
             for (uint32_t which = KV ? 0u : 1u; which < 2 && live; ++which) {
                 const uint32_t half = column0 / 64;
@@ -440,18 +491,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
                 fence_proxy_async_shared();
                 __syncwarp();
-                bool stores = true;
-                if (kThreadColumns == 32) {
-                    const uint32_t pair_bar = staged + 8 * (2 * (2 * quadrant + half) + which);
-                    if (part & 1u) {
-                        if (lane == 0) mbar_arrive(pair_bar);
-                        stores = false;
-                    } else if (!mbar_wait(pair_bar, 0, site, kStallElementAcc, 100 + which)) {
-                        live = false;
-                        stores = false;
-                    }
-                }
-                if (stores && lane == 0) {
+                if (lane == 0) {
                     tma_store_3d(which ? &out1_map : &out0_map, subtile + 32 * quadrant * 128,
                                  static_cast<int>(64 * half), static_cast<int>(kRows * owner + 32 * quadrant),
                                  static_cast<int>(plane));
