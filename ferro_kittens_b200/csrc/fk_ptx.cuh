@@ -337,10 +337,21 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
         : "memory");
 }
 
-// Whole-warp forms: every lane executes the instruction stream and the lane whose `leader` is
-// non-zero issues. The issuing code then has no divergent branch around it, which lets the
-// compiler keep descriptors in the uniform datapath: measured thread-side cost per MMA 23-33
-// cycles against 44-70 for the same loop under `if (lane == 0)`.
+/// 1 in exactly one lane of a converged warp, 0 in the others. Use it as a BRANCH around the
+/// whole issuing role (`if (elect_one()) { waits, MMAs, commits }`): the compiler then knows the
+/// region runs in a single thread and emits the tight issue sequence -- 23 cycles of the thread's
+/// own instructions per tcgen05.mma, measured, against 71 under `if (lane == 0)` or under a
+/// lane-0 predicate, which it cannot tell from arbitrary divergence. Do not use the flag as a
+/// predicate next to other warp-level operations (shuffles, lane-0 waits): that form stalled a
+/// microbenchmark's bounded wait and faulted once in a kernel.
+__device__ __forceinline__ uint32_t elect_one() {
+    uint32_t flag;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(flag));
+    return flag;
+}
+
+// Predicated forms: every lane executes the instruction stream and the lane whose `leader` is
+// non-zero issues (inside an elected single-thread region `leader` is simply 1).
 template <int CTA_GROUP>
 __device__ __forceinline__ void mma_ss_if(uint32_t leader, uint32_t d_tmem, uint64_t a_desc,
                                           uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {

@@ -240,7 +240,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
     } else if (warp == kMmaWarp) {
         // ------------------------------------------------ MMA issue
-        if (lane == 0) {
+#ifndef FK_FLASH_ISSUE_ELECT
+#define FK_FLASH_ISSUE_ELECT 1
+#endif
+        // One thread issues. Chosen by elect.sync the compiler knows the region runs in a single
+        // thread (see the note at elect_one); chosen as lane 0 it does not.
+        if (FK_FLASH_ISSUE_ELECT ? elect_one() != 0 : lane == 0) {
             constexpr uint32_t idesc_qk = instruction_descriptor(kTileRows, kBlockKeys, false, false);
             constexpr uint32_t idesc_pv = instruction_descriptor(kTileRows, kHead, false, true);
 

@@ -260,14 +260,25 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
         }
     } else if (warp == kMmaWarp) {
-        // ------------------------------------------------ MMA issue (whole warp, lane 0 predicated on)
-        const uint32_t leader = lane == 0 ? 1u : 0u;
+        // ------------------------------------------------ MMA issue
+#ifndef FK_BWD_ISSUE_STYLE
+#define FK_BWD_ISSUE_STYLE 1
+#endif
+        // Style 0: the whole warp runs the code and lane 0 issues through predicated instructions.
+        // Style 1: one elected thread runs all of it, branches and waits included.
+        constexpr bool kElected = FK_BWD_ISSUE_STYLE == 1;
+        const uint32_t leader = kElected ? 1u : (lane == 0 ? 1u : 0u);
         constexpr uint32_t idesc_ss = instruction_descriptor(kRows, kRows, false, false);
         constexpr uint32_t idesc_ts = instruction_descriptor(kRows, kHead, false, true);
+        if (!kElected || elect_one()) {
         auto wait = [&](uint32_t bar, uint32_t parity, uint32_t code, uint32_t detail) {
             uint32_t ok = 1;
-            if (lane == 0) ok = mbar_wait(bar, parity, site, code, detail) ? 1u : 0u;
-            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (kElected) {
+                ok = mbar_wait(bar, parity, site, code, detail) ? 1u : 0u;
+            } else {
+                if (lane == 0) ok = mbar_wait(bar, parity, site, code, detail) ? 1u : 0u;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+            }
             if (ok) tc_fence_after_sync();
             return ok != 0;
         };
@@ -339,6 +350,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             trace(1, n, 3);
         }
         mma_commit_if<1>(leader, acc_done);
+        }
         __syncwarp();
     } else if (warp < kElementWarps) {
         // ------------------------------------------------ element-wise step and epilogue

@@ -210,7 +210,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         }
     } else if (warp == 1) {
         // ------------------------------------------------ MMA issue (leader only)
-        if (rank == 0 && lane == 0) {
+#ifndef FK_GEMM_ISSUE_ELECT
+#define FK_GEMM_ISSUE_ELECT 0
+#endif
+        if (rank == 0 && (FK_GEMM_ISSUE_ELECT ? elect_one() != 0 : lane == 0)) {
             const uint32_t idesc = plan.idesc;
             uint32_t drain = 0, count = 0;
             bool live = true;
