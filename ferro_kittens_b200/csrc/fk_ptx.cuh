@@ -84,7 +84,10 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
 // How long one try_wait may keep the thread suspended in hardware (ns). The
 // thread wakes as soon as the phase completes, so a long hint costs no latency;
 // it only keeps waiting roles from spending issue slots on polling.
-constexpr uint32_t kSuspendHintNs = 200000;
+#ifndef FK_SUSPEND_HINT_NS
+#define FK_SUSPEND_HINT_NS 200000
+#endif
+constexpr uint32_t kSuspendHintNs = FK_SUSPEND_HINT_NS;
 
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -110,7 +113,23 @@ struct StallSite {
     volatile uint32_t* stop; // shared: raised once any role gives up
     uint32_t peer_stop;      // shared::cluster address of the peer's flag, 0 if none
     long long budget = kWaitBudgetCycles;
+    bool spin = false;       // poll with test_wait instead of suspending in try_wait
 };
+
+/// The non-suspending probe. A thread suspended in try_wait takes a few hundred cycles to come back
+/// after the phase completes; a role on a kernel's critical path polls with this instead, at the
+/// price of the issue slots the polling takes (so not for roles that wait most of the time).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 
 /// Parity wait with a deadline. Returns false when the budget ran out or
 /// another role already raised `stop`; the caller must then fall through to
@@ -119,12 +138,12 @@ struct StallSite {
 /// stop flag of its watched builds.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const StallSite& site,
                                           uint32_t code, uint32_t detail) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (site.spin ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
     const long long start = clock64();
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 16; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
+            if (site.spin ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
         if (*site.stop) return false;
         if (clock64() - start > site.budget) {
             *site.stop = 1;

@@ -200,7 +200,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     tc_fence_after_sync();
     const uint32_t tmem = *slot_ptr;
 
-    const StallSite site{status, stop_flag, 0};
+    // Every role here sits on the tile's dependency chain: poll, do not suspend.
+    const StallSite site{status, stop_flag, 0, kWaitBudgetCycles, true};
 #ifdef FK_FLASH_TRACE
     // Development build: clock stamps of the first blocks of CTA (0, 0), after the status words.
     auto trace = [&](uint32_t role, uint32_t block, uint32_t point) {
@@ -467,6 +468,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 __syncwarp();
                 if (lane == 0) mbar_arrive(p_ready + 8 * t);
                 if (warp == 0) trace(t, j, 4);
+                trace(3 + warp, j, t);  // every softmax warp's arrival, per tile
             }
         }
 

@@ -35,6 +35,10 @@
 #include "fk_layout.h"
 #include "fk_ptx.cuh"
 
+#ifndef FK_BWD_SPIN
+#define FK_BWD_SPIN 0
+#endif
+
 namespace fk {
 namespace flash_bwd {
 
@@ -204,11 +208,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *slot_ptr;
-    const StallSite site{status, stop_flag, 0};
+    // Polling instead of suspending measured no better here (it pays in the forward).
+    const StallSite site{status, stop_flag, 0, kWaitBudgetCycles, FK_BWD_SPIN != 0};
 #ifdef FK_BWD_TRACE
-    // Development build: clock stamps of the first blocks of CTA (0, 0), after the status words.
+    // Development build: clock stamps of the first blocks of CTA (0, 0), after the status words
+    // (FK_BWD_TRACE=2: the key-block owners; 1: the query-block owners, whose launch comes second).
     auto trace = [&](uint32_t role, uint32_t block, uint32_t point) {
-        if (blockIdx.x == 0 && blockIdx.y == 0 && block < 24 && lane == 0)
+        if ((FK_BWD_TRACE == 2) == KV && blockIdx.x == 0 && blockIdx.y == 0 && block < 24 && lane == 0)
             reinterpret_cast<long long*>(status + 8)[(role * 24 + block) * 4 + point] = clock64();
     };
 #else
