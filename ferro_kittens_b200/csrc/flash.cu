@@ -50,10 +50,11 @@ constexpr float kRescaleThreshold = 8.0f;
 // Of the 16 pairs of scores in a 32-column chunk, the pairs whose bit is set here take their
 // 2^x from a polynomial on the FMA pipe instead of the ex2 unit: at D = 128 a score tile costs
 // as many ex2-unit cycles as tensor cycles. Measured on B200 in back-to-back launches (the
-// power-capped regime), two pairs of sixteen are the best share: +6 % non-causal, +3 % causal
-// over none; one pair is about as good, three or more lose again to the extra issue slots.
+// power-capped regime) the best share is four pairs of sixteen: +5 % over none, causal and not
+// (1048 vs 996, 1061 vs 1007 TFLOP/s); eight of sixteen gives the gain back to the issue slots.
+// Before the MMA role moved to an elected thread and the waits to polling the best share was two.
 #ifndef FK_FLASH_POLY_MASK
-#define FK_FLASH_POLY_MASK 0x0101u
+#define FK_FLASH_POLY_MASK 0x1111u
 #endif
 constexpr uint32_t kPolyMask = FK_FLASH_POLY_MASK;
 
