@@ -398,8 +398,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak,
                          # dram__bytes_read + write of one launch of this kernel on the full 16384^3 shape
-                         # (one ncu capture, 4 passes; see profiles/), scaled by the rank's share of N.
-                         "traffic": (9.70e9 + 0.598e9) * n_local / N, "traffic_unit": "bytes/launch",
+                         # (one ncu capture of four metrics at group 8; see profiles/), scaled by the rank's share of N.
+                         "traffic": (7.35e9 + 0.591e9) * n_local / N, "traffic_unit": "bytes/launch",
                          "algorithmic_flops_per_launch": 2.0 * M * n_local * K,
                          "peak_source": f"{peaks['source']} ({'sustained' if long_region else 'burst'} cuBLAS bf16)",
                          "frac_of_nominal_2250": achieved / 2250.0},

@@ -19,6 +19,16 @@ size_t fko_gemm_check_c(const uint16_t* observed, size_t m, size_t n, size_t k, 
 void fko_flash_stage(int which, size_t sequence, size_t heads, uint16_t* out);
 void fko_flash_rows(const uint16_t* q, const uint16_t* k, const uint16_t* v, size_t sequence, size_t row0,
                     size_t rows, double scale, int causal, double* out, double* lse);
+void fko_flash_backward(const uint16_t* q, const uint16_t* k, const uint16_t* v, const uint16_t* d_out, size_t sequence,
+                        double scale, int causal, double* dq, double* dk, double* dv);
+float fko_from_bf16(uint16_t bits);
+uint16_t fko_to_bf16(float value);
+void fko_softmax_stage(size_t rows, size_t planes, uint16_t* out);
+void fko_softmax_rows(const uint16_t* x, size_t rows, double* out);
+void fko_layernorm_stage(size_t rows, uint16_t* x, uint16_t* gamma, uint16_t* beta);
+void fko_layernorm_rows(const uint16_t* x, const uint16_t* gamma, const uint16_t* beta, size_t rows, double epsilon,
+                        double* out);
+void fko_groupnorm_tiles(const uint16_t* x, size_t rows, double epsilon, double* out);
 }
 
 #define CUDA(call)                                                                           \
@@ -115,6 +125,127 @@ static int flash_check() {
     return 0;
 }
 
+// examples/src/softmax.rs:215-300 and examples/src/layernorm.rs:380-470, 505-590: the three row kernels on the
+// reference's seeds, at its sizes and tolerances (2^-8 relative, 2^-7 relative, 2^-6 absolute).
+static int rows_check() {
+    const size_t rows = 256, planes = 2;
+    std::vector<uint16_t> x(planes * rows * 128), y(x.size());
+    fko_softmax_stage(rows, planes, x.data());
+    const uint64_t x_dev = stage(x);
+    void* y_dev = nullptr;
+    uint32_t* status = nullptr;
+    CUDA(cudaMalloc(&y_dev, x.size() * 2));
+    CUDA(cudaMalloc(reinterpret_cast<void**>(&status), 32));
+    CUDA(cudaMemset(status, 0, 32));
+    kittens::rows::softmax_rows(nullptr, x_dev, reinterpret_cast<uint64_t>(y_dev), rows, planes, status);
+    kittens::watchdog::wait(nullptr);
+    kittens::check(fk_status_check(status, nullptr));
+    CUDA(cudaMemcpy(y.data(), y_dev, y.size() * 2, cudaMemcpyDeviceToHost));
+    std::vector<double> expected(x.size());
+    fko_softmax_rows(x.data(), planes * rows, expected.data());
+    double worst_softmax = 0.0;
+    for (size_t i = 0; i < x.size(); ++i) {
+        const double error = std::fabs(fko_from_bf16(y[i]) / expected[i] - 1.0);
+        if (!(error <= 1.0 / 256.0)) {
+            std::printf("softmax [%zu] = %g, want %g\n", i, fko_from_bf16(y[i]), expected[i]);
+            return 1;
+        }
+        worst_softmax = error > worst_softmax ? error : worst_softmax;
+    }
+
+    std::vector<uint16_t> lx(rows * 128), gamma(128), beta(128), ly(lx.size());
+    fko_layernorm_stage(rows, lx.data(), gamma.data(), beta.data());
+    const uint64_t lx_dev = stage(lx), gamma_dev = stage(gamma), beta_dev = stage(beta);
+    kittens::rows::layernorm_rows(nullptr, lx_dev, gamma_dev, beta_dev, reinterpret_cast<uint64_t>(y_dev), rows,
+                                  kittens::rows::EPSILON, status);
+    kittens::watchdog::wait(nullptr);
+    CUDA(cudaMemcpy(ly.data(), y_dev, ly.size() * 2, cudaMemcpyDeviceToHost));
+    std::vector<double> layer(lx.size()), group(lx.size());
+    fko_layernorm_rows(lx.data(), gamma.data(), beta.data(), rows, kittens::rows::EPSILON, layer.data());
+    double worst_layer = 0.0, worst_group = 0.0;
+    for (size_t i = 0; i < lx.size(); ++i) {
+        const double error = std::fabs((fko_from_bf16(ly[i]) - layer[i]) / layer[i]);
+        if (!(error <= 1.0 / 128.0)) {
+            std::printf("layernorm [%zu] = %g, want %g\n", i, fko_from_bf16(ly[i]), layer[i]);
+            return 1;
+        }
+        worst_layer = error > worst_layer ? error : worst_layer;
+    }
+    kittens::rows::groupnorm_tile(nullptr, lx_dev, reinterpret_cast<uint64_t>(y_dev), rows, kittens::rows::EPSILON, status);
+    kittens::watchdog::wait(nullptr);
+    kittens::check(fk_status_check(status, nullptr));
+    CUDA(cudaMemcpy(ly.data(), y_dev, ly.size() * 2, cudaMemcpyDeviceToHost));
+    fko_groupnorm_tiles(lx.data(), rows, kittens::rows::EPSILON, group.data());
+    for (size_t i = 0; i < lx.size(); ++i) {
+        const double error = std::fabs(fko_from_bf16(ly[i]) - group[i]);
+        if (!(error <= 1.0 / 64.0)) {
+            std::printf("groupnorm [%zu] = %g, want %g\n", i, fko_from_bf16(ly[i]), group[i]);
+            return 1;
+        }
+        worst_group = error > worst_group ? error : worst_group;
+    }
+    std::printf("rows normalized: softmax %.2e, layernorm %.2e relative, whole-tile %.2e absolute\n", worst_softmax,
+                worst_layer, worst_group);
+    return 0;
+}
+
+// The backward of the attention check: gradients against the f64 derivative of the same reference.
+static int flash_backward_check() {
+    const size_t sequence = 256, heads = 2, head = 128, count = heads * sequence * head;
+    std::vector<uint16_t> q(count), k(count), v(count), d_out(count);
+    // Seeded uniform values in [-1, 1): the forward's lattice is the wrong input here (its keys carry a
+    // ramp up to 32 in one column, which dQ = dS K multiplies into the bf16 rounding of a dS row that
+    // sums to zero; the gradient's error is then set by that cancellation, not by the kernel).
+    uint64_t state = 0x9e3779b97f4a7c15ull;
+    for (std::vector<uint16_t>* tensor : {&q, &k, &v, &d_out})
+        for (uint16_t& word : *tensor) {
+            state = state * 6364136223846793005ull + 1442695040888963407ull;
+            word = fko_to_bf16(static_cast<float>(static_cast<int64_t>(state >> 40) - (1 << 23)) / static_cast<float>(1 << 23));
+        }
+    const uint64_t q_dev = stage(q), k_dev = stage(k), v_dev = stage(v), g_dev = stage(d_out);
+    void *o_dev = nullptr, *dq_dev = nullptr, *dk_dev = nullptr, *dv_dev = nullptr;
+    float *lse = nullptr, *workspace = nullptr;
+    uint32_t* status = nullptr;
+    for (void** p : {&o_dev, &dq_dev, &dk_dev, &dv_dev}) CUDA(cudaMalloc(p, count * 2));
+    CUDA(cudaMalloc(reinterpret_cast<void**>(&lse), heads * sequence * 4));
+    CUDA(cudaMalloc(reinterpret_cast<void**>(&workspace), kittens::flash_backward::workspace_floats(heads, sequence) * 4));
+    CUDA(cudaMalloc(reinterpret_cast<void**>(&status), 32));
+    CUDA(cudaMemset(status, 0, 32));
+    const float scale = kittens::flash_forward::SCALE;
+    kittens::flash_forward::run(nullptr, q_dev, k_dev, v_dev, reinterpret_cast<uint64_t>(o_dev), nullptr, lse, heads,
+                                sequence, scale, true, status);
+    kittens::flash_backward::run(nullptr, q_dev, k_dev, v_dev, reinterpret_cast<uint64_t>(o_dev), g_dev, lse,
+                                 reinterpret_cast<uint64_t>(dq_dev), reinterpret_cast<uint64_t>(dk_dev),
+                                 reinterpret_cast<uint64_t>(dv_dev), workspace, heads, sequence, scale, true, status);
+    kittens::watchdog::wait(nullptr);
+    kittens::check(fk_status_check(status, nullptr));
+    std::vector<uint16_t> got(count);
+    std::vector<double> dq(sequence * head), dk(dq.size()), dv(dq.size());
+    double worst = 0.0;
+    void* outputs[3] = {dq_dev, dk_dev, dv_dev};
+    for (size_t h = 0; h < heads; ++h) {
+        const size_t at = h * sequence * head;
+        fko_flash_backward(q.data() + at, k.data() + at, v.data() + at, d_out.data() + at, sequence, scale, 1, dq.data(),
+                           dk.data(), dv.data());
+        const std::vector<double>* wanted[3] = {&dq, &dk, &dv};
+        for (int which = 0; which < 3; ++which) {
+            CUDA(cudaMemcpy(got.data(), outputs[which], count * 2, cudaMemcpyDeviceToHost));
+            double largest = 0.0, error = 0.0;
+            for (size_t i = 0; i < sequence * head; ++i) {
+                largest = std::fmax(largest, std::fabs((*wanted[which])[i]));
+                error = std::fmax(error, std::fabs(fko_from_bf16(got[at + i]) - (*wanted[which])[i]));
+            }
+            if (!(error <= 2e-2 * largest)) {
+                std::printf("flash backward output %d head %zu: error %g of %g\n", which, h, error, largest);
+                return 1;
+            }
+            worst = std::fmax(worst, error / largest);
+        }
+    }
+    std::printf("flash backward %zux%zux%zu gradients, worst error %.2e of the largest entry\n", heads, sequence, head, worst);
+    return 0;
+}
+
 int main() {
     try {
         // Bad arguments come back as the crate's messages, before any launch.
@@ -127,6 +258,8 @@ int main() {
         }
         if (gemm_check()) return 1;
         if (flash_check()) return 1;
+        if (flash_backward_check()) return 1;
+        if (rows_check()) return 1;
     } catch (const kittens::Error& error) {
         std::printf("error %d: %s\n", error.code, error.what());
         return 1;
