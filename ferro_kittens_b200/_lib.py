@@ -84,6 +84,10 @@ SIGNATURES = {
                              c_uint32, c_void_p, c_void_p]),
     "fk_gemm_launch": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_uint32,
                                c_uint32, c_void_p, c_void_p]),
+    "fk_gemm_launch_fused": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32,
+                                     c_uint32, c_uint32, c_void_p, c_void_p]),
+    "fk_gemm_fused": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_uint32,
+                              c_uint32, c_uint32, c_void_p, c_void_p]),
     "fk_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_uint32, c_uint32,
                         c_uint32, c_void_p, c_void_p]),
     "fk_gemm_bf16_host": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_uint32]),

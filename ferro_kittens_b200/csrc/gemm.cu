@@ -96,6 +96,8 @@ struct Schedule {
     uint32_t items;      // whole + 2 * (tiles - whole): the rest are single halves
     uint32_t idesc;      // tcgen05 instruction descriptor (operand format differs by entry point)
     uint32_t accumulate; // non-zero: C += A . B^T through the copy engine's reduce-add
+    uint32_t relu;       // non-zero: max(x, 0) on the fp32 value before it is rounded
+    const uint16_t* bias;  // null, or n bf16 values added per column in fp32 before rounding
 };
 
 struct Item {
@@ -311,6 +313,36 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                     tmem_ld_32x32(t_row + pass * kStageColumns, lo);
                     tmem_ld_32x32(t_row + pass * kStageColumns + 32, hi);
                     tmem_wait_ld();
+                    if (plan.bias || plan.relu) {
+                        // The fused epilogue (a column-vector bias and a unary map on the register
+                        // tile, src/global.rs:410-416, src/reg.rs:261): every lane holds the same 64
+                        // columns, so the bias words are broadcast loads.
+                        const float floor = plan.relu ? 0.0f : -INFINITY;
+#pragma unroll
+                        for (uint32_t part = 0; part < 2; ++part) {
+                            uint32_t* const values = part ? hi : lo;
+                            uint32_t words[16];
+                            if (plan.bias) {
+                                const uint4* source = reinterpret_cast<const uint4*>(
+                                    plan.bias + item.column + pass * kStageColumns + 32 * part);
+#pragma unroll
+                                for (uint32_t q = 0; q < 4; ++q) {
+                                    const uint4 v = __ldg(source + q);
+                                    words[4 * q] = v.x, words[4 * q + 1] = v.y, words[4 * q + 2] = v.z, words[4 * q + 3] = v.w;
+                                }
+                            } else {
+#pragma unroll
+                                for (uint32_t q = 0; q < 16; ++q) words[q] = 0;
+                            }
+#pragma unroll
+                            for (uint32_t i = 0; i < 16; ++i) {
+                                const float even = __uint_as_float(values[2 * i]) + __uint_as_float(words[i] << 16);
+                                const float odd = __uint_as_float(values[2 * i + 1]) + __uint_as_float(words[i] & 0xffff0000u);
+                                values[2 * i] = __float_as_uint(fmaxf(even, floor));
+                                values[2 * i + 1] = __float_as_uint(fmaxf(odd, floor));
+                            }
+                        }
+                    }
 #pragma unroll
                     for (uint32_t i = 0; i < 16; ++i) {
                         held[pass][i] =
@@ -375,6 +407,8 @@ static Schedule schedule(uint32_t m, uint32_t n, uint32_t k, uint32_t group, uin
     plan.idesc = instruction_descriptor(2 * kBlockM, kBlockN, false, false,
                                         (flags & FK_GEMM_F16_OPERANDS) ? 0u : 1u);
     plan.accumulate = (flags & FK_GEMM_ACCUMULATE) ? 1u : 0u;
+    plan.relu = (flags & FK_GEMM_RELU) ? 1u : 0u;
+    plan.bias = nullptr;
     plan.m = m;
     plan.tiles_m = (m + kHalves * 2 * kBlockM - 1) / (kHalves * 2 * kBlockM);
     plan.tiles_n = n / kBlockN;
@@ -405,11 +439,13 @@ extern "C" uint32_t fk_gemm_grid(uint32_t m, uint32_t n, uint32_t sm_count) {
     return 2 * (plan.items < clusters ? plan.items : clusters);
 }
 
-extern "C" int fk_gemm_launch(const void* a_map, const void* b_map, const void* c_map, uint32_t m,
-                              uint32_t n, uint32_t k, uint32_t group, uint32_t flags, void* stream,
-                              uint32_t* device_status) {
-    if (flags & ~(FK_GEMM_F16_OPERANDS | FK_GEMM_ACCUMULATE))
+extern "C" int fk_gemm_launch_fused(const void* a_map, const void* b_map, const void* c_map,
+                                    const void* bias, uint32_t m, uint32_t n, uint32_t k, uint32_t group,
+                                    uint32_t flags, void* stream, uint32_t* device_status) {
+    if (flags & ~(FK_GEMM_F16_OPERANDS | FK_GEMM_ACCUMULATE | FK_GEMM_RELU))
         return fk_fail(FK_ERR_INVALID, "unknown GEMM flags 0x%x", flags);
+    if (reinterpret_cast<uintptr_t>(bias) & 15u)
+        return fk_fail(FK_ERR_ALIGNMENT, "the bias vector wants 16-byte alignment");
     if (!a_map || !b_map || !c_map) return fk_fail(FK_ERR_INVALID, "a tensor map pointer is null");
     if (m == 0 || n == 0 || k == 0 || m % (2 * gemm::kBlockM) || n % gemm::kBlockN ||
         k % gemm::kBlockK)
@@ -427,7 +463,8 @@ extern "C" int fk_gemm_launch(const void* a_map, const void* b_map, const void* 
     if (admitted != FK_OK) return admitted;
 
     const uint32_t clusters = static_cast<uint32_t>(sm_count) / 2;
-    const gemm::Schedule plan = gemm::schedule(m, n, k, group, clusters, flags);
+    gemm::Schedule plan = gemm::schedule(m, n, k, group, clusters, flags);
+    plan.bias = static_cast<const uint16_t*>(bias);
     const uint32_t grid = 2 * (plan.items < clusters ? plan.items : clusters);
     gemm::gemm_bf16_pair_kernel<<<grid, gemm::kThreads, gemm::kSharedBytes,
                                   static_cast<cudaStream_t>(stream)>>>(
@@ -435,6 +472,12 @@ extern "C" int fk_gemm_launch(const void* a_map, const void* b_map, const void* 
         *static_cast<const CUtensorMap*>(c_map), plan, device_status);
     FK_CUDA(cudaGetLastError());
     return FK_OK;
+}
+
+extern "C" int fk_gemm_launch(const void* a_map, const void* b_map, const void* c_map, uint32_t m,
+                              uint32_t n, uint32_t k, uint32_t group, uint32_t flags, void* stream,
+                              uint32_t* device_status) {
+    return fk_gemm_launch_fused(a_map, b_map, c_map, nullptr, m, n, k, group, flags, stream, device_status);
 }
 
 extern "C" int fk_gemm_bf16_launch(const void* a_map, const void* b_map, const void* c_map,
@@ -459,9 +502,9 @@ static int gemm_maps(const void* a, const void* b, void* c, uint32_t m, uint32_t
     return status;
 }
 
-extern "C" int fk_gemm(const void* a, const void* b, void* c, uint32_t m, uint32_t n, uint32_t k,
-                       uint32_t ldc, uint32_t group, uint32_t flags, void* stream,
-                       uint32_t* device_status) {
+extern "C" int fk_gemm_fused(const void* a, const void* b, void* c, const void* bias, uint32_t m,
+                             uint32_t n, uint32_t k, uint32_t ldc, uint32_t group, uint32_t flags,
+                             void* stream, uint32_t* device_status) {
     if (!a || !b || !c) return fk_fail(FK_ERR_INVALID, "an operand pointer is null");
     if (m == 0 || n == 0 || k == 0 || m % (2 * gemm::kBlockM) || n % gemm::kBlockN ||
         k % gemm::kBlockK)
@@ -471,7 +514,14 @@ extern "C" int fk_gemm(const void* a, const void* b, void* c, uint32_t m, uint32
     alignas(64) CUtensorMap maps[3];
     const int status = gemm_maps(a, b, c, m, n, k, ldc, maps, (flags & FK_GEMM_F16_OPERANDS) ? FK_F16 : FK_BF16);
     if (status != FK_OK) return status;
-    return fk_gemm_launch(&maps[0], &maps[1], &maps[2], m, n, k, group, flags, stream, device_status);
+    return fk_gemm_launch_fused(&maps[0], &maps[1], &maps[2], bias, m, n, k, group, flags, stream,
+                                device_status);
+}
+
+extern "C" int fk_gemm(const void* a, const void* b, void* c, uint32_t m, uint32_t n, uint32_t k,
+                       uint32_t ldc, uint32_t group, uint32_t flags, void* stream,
+                       uint32_t* device_status) {
+    return fk_gemm_fused(a, b, c, nullptr, m, n, k, ldc, group, flags, stream, device_status);
 }
 
 extern "C" int fk_gemm_bf16(const void* a, const void* b, void* c, uint32_t m, uint32_t n,

@@ -20,6 +20,8 @@ GROUP = 8
 F16_OPERANDS = 1
 #: C += A . B^T through the copy engine's reduce-add (src/shared.rs:974-1009).
 ACCUMULATE = 2
+#: max(x, 0) before the rounding (the `Relu` unary map, src/reg.rs:261).
+RELU = 4
 
 
 def tile_grid(m: int, n: int) -> tuple[int, int]:
@@ -61,8 +63,9 @@ def launch(a_map, b_map, c_map, m: int, n: int, k: int, group: int = GROUP, stat
 
 
 def run(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor | None = None, group: int = GROUP,
-        status: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
-    """``C[m, n] (+)= sum_k A[m, k] * B[n, k]``; A is [m, k], B is [n, k], both bf16 or both fp16 on
+        status: torch.Tensor | None = None, accumulate: bool = False, bias: torch.Tensor | None = None,
+        relu: bool = False) -> torch.Tensor:
+    """``C[m, n] (+)= map(sum_k A[m, k] * B[n, k] + bias[n])``; A is [m, k], B is [n, k], both bf16 or both fp16 on
     one GPU, C bf16. With ``accumulate`` the rounded product is added into ``c`` (in bf16, by the
     copy engine), which must then be given and hold values."""
     for name, tensor in (("a", a), ("b", b)):
@@ -84,11 +87,16 @@ def run(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor | None = None, group: 
         raise RuntimeError("c must live on a CUDA device: there is no CPU path")
     if c.dtype != torch.bfloat16 or c.dim() != 2 or c.stride(1) != 1 or c.shape != (m, n):
         raise ValueError("c must be an [m, n] bfloat16 tensor with unit column stride (rows may be padded)")
-    flags = (F16_OPERANDS if a.dtype == torch.float16 else 0) | (ACCUMULATE if accumulate else 0)
+    if bias is not None and (not bias.is_cuda or bias.dtype != torch.bfloat16 or bias.shape != (n,)
+                             or not bias.is_contiguous()):
+        raise ValueError("bias must be a contiguous bfloat16 [n] tensor on the device")
+    flags = ((F16_OPERANDS if a.dtype == torch.float16 else 0) | (ACCUMULATE if accumulate else 0)
+             | (RELU if relu else 0))
     with torch.cuda.device(a.device):
         handle = torch.cuda.current_stream().cuda_stream
-        check(library().fk_gemm(a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k, c.stride(0), group,
-                                flags, handle, status.data_ptr() if status is not None else None))
+        check(library().fk_gemm_fused(a.data_ptr(), b.data_ptr(), c.data_ptr(),
+                                      bias.data_ptr() if bias is not None else None, m, n, k, c.stride(0), group,
+                                      flags, handle, status.data_ptr() if status is not None else None))
     return c
 
 

@@ -165,9 +165,21 @@ int fk_gemm_bf16(const void* a, const void* b, void* c, uint32_t m, uint32_t n, 
  *                         `commit_add_2d`, src/epilogue.rs:789-812): the rounded bf16 tile is
  *                         added into C in bf16, C is never read by a thread, and C must hold
  *                         values beforehand.
- * fk_gemm_bf16_launch / fk_gemm_bf16 are these with flags = 0. */
+ *   FK_GEMM_RELU          max(x, 0) on the fp32 value before its one rounding to bf16: the `Relu`
+ *                         unary map on a register tile (src/reg.rs:261, 1502-1504).
+ * The `_fused` entries also take `bias`: null, or n bf16 values (16-byte aligned) added per column
+ * in fp32 before the rounding -- a column vector every row shares (`load_vec` / `add_col`,
+ * src/global.rs:410-416, as examples/src/layernorm.rs:200-203 uses them for beta). Bias first,
+ * then the map, then (with FK_GEMM_ACCUMULATE) the add into C.
+ * fk_gemm_bf16_launch / fk_gemm_bf16 are these with flags = 0 and no bias. */
 #define FK_GEMM_F16_OPERANDS 1u
 #define FK_GEMM_ACCUMULATE 2u
+#define FK_GEMM_RELU 4u
+int fk_gemm_launch_fused(const void* a_map, const void* b_map, const void* c_map, const void* bias, uint32_t m,
+                         uint32_t n, uint32_t k, uint32_t group, uint32_t flags, void* stream,
+                         uint32_t* device_status);
+int fk_gemm_fused(const void* a, const void* b, void* c, const void* bias, uint32_t m, uint32_t n, uint32_t k,
+                  uint32_t ldc, uint32_t group, uint32_t flags, void* stream, uint32_t* device_status);
 int fk_gemm_launch(const void* a_map, const void* b_map, const void* c_map, uint32_t m, uint32_t n,
                    uint32_t k, uint32_t group, uint32_t flags, void* stream, uint32_t* device_status);
 int fk_gemm(const void* a, const void* b, void* c, uint32_t m, uint32_t n, uint32_t k, uint32_t ldc,

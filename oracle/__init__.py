@@ -42,6 +42,8 @@ _lib.fko_gemm_check_c.argtypes = [_u16p, c_size_t, c_size_t, c_size_t, POINTER(c
 _lib.fko_gemm_check_c.restype = c_size_t
 _lib.fko_gemm_expected.argtypes = [c_size_t, c_size_t, c_size_t]
 _lib.fko_gemm_expected.restype = c_uint16
+_lib.fko_gemm_exact.argtypes = [c_size_t, c_size_t, c_size_t]
+_lib.fko_gemm_exact.restype = c_float
 _lib.fko_gemm_rows.argtypes = [_u16p, _u16p, c_size_t, c_size_t, c_size_t, c_size_t, ctypes.c_void_p, ctypes.c_void_p]
 _lib.fko_gemm_rows.restype = None
 _lib.fko_flash_permutation.argtypes = [c_size_t] * 4
@@ -172,6 +174,12 @@ def gemm_check_c(observed: np.ndarray, m: int, n: int, k: int) -> tuple[int, flo
 
 def gemm_expected(row: int, column: int, k: int) -> int:
     return _lib.fko_gemm_expected(row, column, k)
+
+
+def gemm_exact(m: int, n: int, k: int) -> np.ndarray:
+    """The [m, n] fp32 values of the integer-operand product before their rounding (7 x 21 distinct cells)."""
+    cells = np.array([[_lib.fko_gemm_exact(r, c, k) for c in range(21)] for r in range(7)], dtype=np.float32)
+    return cells[np.arange(m)[:, None] % 7, np.arange(n)[None, :] % 21]
 
 
 def gemm_rows(a: np.ndarray, b: np.ndarray, row0: int, rows: int, want_f64: bool = False):

@@ -184,6 +184,15 @@ uint16_t fko_gemm_expected(size_t row, size_t column, size_t k) {
     return fko_to_bf16(sum);
 }
 
+/* The same cell before its rounding: the running fp32 sum check_c's `exact` holds (:545-551), for the
+ * fused epilogue's oracle (bias and unary map apply to this value, then one rounding). */
+float fko_gemm_exact(size_t row, size_t column, size_t k) {
+    float sum = 0.0f;
+    for (size_t depth = 0; depth < k; ++depth)
+        sum += fko_gemm_a_value(row % 7, depth) * fko_gemm_b_value(column % 21, depth);
+    return sum;
+}
+
 /* ---------------------------------------------------------------- GEMM over arbitrary bf16 inputs
  *
  * The same contraction check_c's `exact` performs (:545-551: a running fp32

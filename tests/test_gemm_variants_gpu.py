@@ -100,5 +100,52 @@ def test_unknown_flags_and_missing_c_are_refused(device):
         gemm.run(a, a, accumulate=True)
     c = torch.zeros((256, 256), dtype=torch.bfloat16, device=device)
     with pytest.raises(FerroKittensError, match="unknown GEMM flags"):
-        check(library().fk_gemm(a.data_ptr(), a.data_ptr(), c.data_ptr(), 256, 256, 64, 256, 8, 4,
+        check(library().fk_gemm(a.data_ptr(), a.data_ptr(), c.data_ptr(), 256, 256, 64, 256, 8, 8,
                                 torch.cuda.current_stream().cuda_stream, None))
+
+
+@pytest.mark.parametrize("with_bias, relu", [(True, False), (False, True), (True, True)])
+def test_bias_and_relu_apply_before_the_one_rounding(device, with_bias, relu):
+    """The fused epilogue on the integer operands: bias[n] added and max(x, 0) taken on the fp32 value,
+    then one rounding -- exact against the oracle's unrounded cells."""
+    m, n, k = 1024, 768, 256
+    a = _device_words(oracle.gemm_stage("a", m, k), device, torch.bfloat16)
+    b = _device_words(oracle.gemm_stage("b", n, k), device, torch.bfloat16)
+    bias_values = ((np.arange(n) * 7) % 23 - 11).astype(np.float32) * 0.5
+    bias = _device_words(oracle.f32_to_bf16(bias_values), device, torch.bfloat16) if with_bias else None
+    status = gemm.new_status(device)
+    c = gemm.run(a, b, status=status, bias=bias, relu=relu)
+    torch.cuda.synchronize(device)
+    gemm.check_status(status)
+    expected = oracle.gemm_exact(m, n, k)
+    if with_bias:
+        expected = expected + bias_values[None, :]
+    if relu:
+        expected = np.maximum(expected, np.float32(0.0))
+    assert np.array_equal(_words(c), oracle.f32_to_bf16(expected))
+    if relu:
+        assert (c.float() >= 0).all() and (c == 0).any()
+
+
+def test_bias_relu_with_fp16_operands_and_accumulate(device):
+    m, n, k = 512, 512, 128
+    a = _device_words(oracle.gemm_stage_f16("a", m, k), device, torch.float16)
+    b = _device_words(oracle.gemm_stage_f16("b", n, k), device, torch.float16)
+    bias_values = ((np.arange(n) * 3) % 13 - 6).astype(np.float32)
+    bias = _device_words(oracle.f32_to_bf16(bias_values), device, torch.bfloat16)
+    held = oracle.f32_to_bf16(np.full((m, n), 1.5, dtype=np.float32))
+    c = _device_words(held.copy(), device, torch.bfloat16)
+    status = gemm.new_status(device)
+    gemm.run(a, b, c, status=status, accumulate=True, bias=bias, relu=True)
+    torch.cuda.synchronize(device)
+    gemm.check_status(status)
+    fused = oracle.f32_to_bf16(np.maximum(oracle.gemm_exact(m, n, k) + bias_values[None, :], np.float32(0.0)))
+    assert np.array_equal(_words(c), oracle.bf16_add_words(held, fused))
+
+
+def test_bias_guards(device):
+    a = torch.zeros((256, 64), dtype=torch.bfloat16, device=device)
+    with pytest.raises(ValueError, match="bias must be"):
+        gemm.run(a, a, bias=torch.zeros(128, dtype=torch.bfloat16, device=device))
+    with pytest.raises(ValueError, match="bias must be"):
+        gemm.run(a, a, bias=torch.zeros(256, dtype=torch.float32, device=device))
