@@ -532,10 +532,10 @@ extern "C" int fk_gemm_bf16(const void* a, const void* b, void* c, uint32_t m, u
 
 // Streams and events of the pipelined host-buffer entry, one set per device, created on first use.
 namespace {
-constexpr uint32_t kHostChunks = 8;
+constexpr uint32_t kHostChunks = 16;
 struct HostPipeline {
     cudaStream_t upload = nullptr, compute = nullptr, download = nullptr;
-    cudaEvent_t a_ready = nullptr, b_ready[kHostChunks] = {}, c_ready[kHostChunks] = {}, idle = nullptr;
+    cudaEvent_t b_ready = nullptr, a_ready[kHostChunks] = {}, c_ready[kHostChunks] = {}, idle = nullptr;
 };
 std::mutex host_pipeline_guard;
 HostPipeline host_pipelines[64];
@@ -550,10 +550,10 @@ int host_pipeline(HostPipeline** out) {
         FK_CUDA(cudaStreamCreateWithFlags(&pipe.upload, cudaStreamNonBlocking));
         FK_CUDA(cudaStreamCreateWithFlags(&pipe.compute, cudaStreamNonBlocking));
         FK_CUDA(cudaStreamCreateWithFlags(&pipe.download, cudaStreamNonBlocking));
-        FK_CUDA(cudaEventCreateWithFlags(&pipe.a_ready, cudaEventDisableTiming));
+        FK_CUDA(cudaEventCreateWithFlags(&pipe.b_ready, cudaEventDisableTiming));
         FK_CUDA(cudaEventCreateWithFlags(&pipe.idle, cudaEventDisableTiming));
         for (uint32_t i = 0; i < kHostChunks; ++i) {
-            FK_CUDA(cudaEventCreateWithFlags(&pipe.b_ready[i], cudaEventDisableTiming));
+            FK_CUDA(cudaEventCreateWithFlags(&pipe.a_ready[i], cudaEventDisableTiming));
             FK_CUDA(cudaEventCreateWithFlags(&pipe.c_ready[i], cudaEventDisableTiming));
         }
     }
@@ -562,11 +562,12 @@ int host_pipeline(HostPipeline** out) {
 }
 }  // namespace
 
-// Upload, compute and read-back overlap: A goes up first, then B in column chunks; the GEMM of a
-// chunk starts when its rows of B have landed, and its columns of C go back (a strided copy into the
-// caller's [m, n]) while later chunks upload and compute. PCIe is full duplex, so the whole call
-// costs about the upload alone; done in sequence it cost upload + compute + read-back. The copies
-// overlap only from page-locked host memory; from pageable memory the call is still correct.
+// Upload, compute and read-back overlap: B goes up first, then A in blocks of rows; the GEMM of a
+// block starts when its rows of A have landed, and its rows of C go back while later blocks upload and
+// compute. Row blocks keep every copy contiguous on both sides. PCIe is full duplex, so the whole call
+// costs about the upload alone plus the last block's GEMM and read-back; done in sequence it cost
+// upload + compute + read-back. The copies overlap only from page-locked host memory; from pageable
+// memory the call is still correct.
 extern "C" int fk_gemm_bf16_host(const uint16_t* a_host, const uint16_t* b_host, uint16_t* c_host,
                                  uint32_t m, uint32_t n, uint32_t k, uint32_t group) {
     if (!a_host || !b_host || !c_host) return fk_fail(FK_ERR_INVALID, "an operand pointer is null");
@@ -584,11 +585,11 @@ extern "C" int fk_gemm_bf16_host(const uint16_t* a_host, const uint16_t* b_host,
     if (status == FK_OK) status = host_pipeline(&pipe);
     if (status != FK_OK) return status;
 
-    // Whole 256-column tiles per chunk, at most kHostChunks chunks.
-    const uint32_t tiles = n / gemm::kBlockN;
-    const uint32_t chunk_tiles = (tiles + kHostChunks - 1) / kHostChunks;
-    const uint32_t chunk = chunk_tiles * gemm::kBlockN;
-    const uint32_t chunks = (n + chunk - 1) / chunk;
+    // Whole 512-row tiles per block, at most kHostChunks blocks.
+    const uint32_t tile_rows = 2 * gemm::kBlockM;
+    const uint32_t tiles = m / tile_rows;
+    const uint32_t chunk = ((tiles + kHostChunks - 1) / kHostChunks) * tile_rows;
+    const uint32_t chunks = (m + chunk - 1) / chunk;
 
     // The staging buffers are shared with earlier calls on the default stream: start after them.
     FK_CUDA(cudaEventRecord(pipe->idle, nullptr));
@@ -596,23 +597,23 @@ extern "C" int fk_gemm_bf16_host(const uint16_t* a_host, const uint16_t* b_host,
     FK_CUDA(cudaStreamWaitEvent(pipe->compute, pipe->idle, 0));
     FK_CUDA(cudaStreamWaitEvent(pipe->download, pipe->idle, 0));
     FK_CUDA(cudaMemsetAsync(status_words, 0, 32, pipe->compute));
-    FK_CUDA(cudaMemcpyAsync(a, a_host, a_bytes, cudaMemcpyHostToDevice, pipe->upload));
-    FK_CUDA(cudaEventRecord(pipe->a_ready, pipe->upload));
-    FK_CUDA(cudaStreamWaitEvent(pipe->compute, pipe->a_ready, 0));
+    FK_CUDA(cudaMemcpyAsync(b, b_host, b_bytes, cudaMemcpyHostToDevice, pipe->upload));
+    FK_CUDA(cudaEventRecord(pipe->b_ready, pipe->upload));
+    FK_CUDA(cudaStreamWaitEvent(pipe->compute, pipe->b_ready, 0));
     for (uint32_t i = 0; i < chunks; ++i) {
-        const uint32_t column0 = i * chunk, columns = (n - column0 < chunk) ? n - column0 : chunk;
-        uint8_t* b_chunk = static_cast<uint8_t*>(b) + size_t(column0) * k * 2;
-        uint8_t* c_chunk = static_cast<uint8_t*>(c) + size_t(column0) * 2;
-        FK_CUDA(cudaMemcpyAsync(b_chunk, b_host + size_t(column0) * k, size_t(columns) * k * 2,
-                                cudaMemcpyHostToDevice, pipe->upload));
-        FK_CUDA(cudaEventRecord(pipe->b_ready[i], pipe->upload));
-        FK_CUDA(cudaStreamWaitEvent(pipe->compute, pipe->b_ready[i], 0));
-        status = fk_gemm_bf16(a, b_chunk, c_chunk, m, columns, k, n, group, pipe->compute, status_words);
+        const uint32_t row0 = i * chunk, rows = (m - row0 < chunk) ? m - row0 : chunk;
+        uint8_t* a_chunk = static_cast<uint8_t*>(a) + size_t(row0) * k * 2;
+        uint8_t* c_chunk = static_cast<uint8_t*>(c) + size_t(row0) * n * 2;
+        FK_CUDA(cudaMemcpyAsync(a_chunk, a_host + size_t(row0) * k, size_t(rows) * k * 2, cudaMemcpyHostToDevice,
+                                pipe->upload));
+        FK_CUDA(cudaEventRecord(pipe->a_ready[i], pipe->upload));
+        FK_CUDA(cudaStreamWaitEvent(pipe->compute, pipe->a_ready[i], 0));
+        status = fk_gemm_bf16(a_chunk, b, c_chunk, rows, n, k, n, group, pipe->compute, status_words);
         if (status != FK_OK) break;
         FK_CUDA(cudaEventRecord(pipe->c_ready[i], pipe->compute));
         FK_CUDA(cudaStreamWaitEvent(pipe->download, pipe->c_ready[i], 0));
-        FK_CUDA(cudaMemcpy2DAsync(c_host + column0, size_t(n) * 2, c_chunk, size_t(n) * 2, size_t(columns) * 2, m,
-                                  cudaMemcpyDeviceToHost, pipe->download));
+        FK_CUDA(cudaMemcpyAsync(c_host + size_t(row0) * n, c_chunk, size_t(rows) * n * 2, cudaMemcpyDeviceToHost,
+                                pipe->download));
     }
     // Whatever happened, leave no work of this call in flight behind the return.
     const cudaError_t up = cudaStreamSynchronize(pipe->upload);

@@ -186,9 +186,11 @@ inline uint32_t grid(uint32_t m, uint32_t n, uint32_t sm_count = 148) { return f
 /// `gemm::run` between staging and read-back (examples/src/gemm.rs:506-536): build the maps,
 /// launch on `stream`. `status` is null or 4 zeroed device words (see fk_status_check).
 /// `flags`: FK_GEMM_F16_OPERANDS for fp16 A and B (examples/src/gemm_sol.rs), FK_GEMM_ACCUMULATE
-/// for C += A.B^T through the copy engine's reduce-add (src/shared.rs:974-1009).
+/// for C += A.B^T through the copy engine's reduce-add (src/shared.rs:974-1009), FK_GEMM_RELU for
+/// max(x, 0) before the rounding (src/reg.rs:261). `bias`: 0 or the device address of n bf16 values
+/// added per column in fp32 before the rounding (src/global.rs:410-416).
 inline void run(void* stream, uint64_t a, uint64_t b, uint64_t c, uint32_t m, uint32_t n, uint32_t k,
-                uint32_t group = GROUP, uint32_t* status = nullptr, uint32_t flags = 0) {
+                uint32_t group = GROUP, uint32_t* status = nullptr, uint32_t flags = 0, uint64_t bias = 0) {
     global::TensorMap a_map, b_map;
     if (flags & FK_GEMM_F16_OPERANDS) {
         using A16 = shared::SharedTile<shared::F16, BLOCK_M, BLOCK_K>;
@@ -200,7 +202,8 @@ inline void run(void* stream, uint64_t a, uint64_t b, uint64_t c, uint32_t m, ui
         b_map = global::GlobalLayout<shared::Bf16, 2>::packed(b, {k, n}).tensor_map<BTile>();
     }
     const auto c_map = global::GlobalLayout<shared::Bf16, 2>::packed(c, {n, m}).tensor_map<CStage>();
-    check(fk_gemm_launch(a_map.as_ptr(), b_map.as_ptr(), c_map.as_ptr(), m, n, k, group, flags, stream, status));
+    check(fk_gemm_launch_fused(a_map.as_ptr(), b_map.as_ptr(), c_map.as_ptr(), reinterpret_cast<const void*>(bias),
+                               m, n, k, group, flags, stream, status));
 }
 
 }  // namespace gemm

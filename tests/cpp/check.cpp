@@ -23,6 +23,7 @@ void fko_flash_backward(const uint16_t* q, const uint16_t* k, const uint16_t* v,
                         double scale, int causal, double* dq, double* dk, double* dv);
 float fko_from_bf16(uint16_t bits);
 uint16_t fko_to_bf16(float value);
+float fko_gemm_exact(size_t row, size_t column, size_t k);
 void fko_softmax_stage(size_t rows, size_t planes, uint16_t* out);
 void fko_softmax_rows(const uint16_t* x, size_t rows, double* out);
 void fko_layernorm_stage(size_t rows, uint16_t* x, uint16_t* gamma, uint16_t* beta);
@@ -85,6 +86,44 @@ static int gemm_check() {
         cudaFree(status);
     }
     return 0;
+}
+
+/* The fused epilogue through gemm::run: bias per column, then max(x, 0), then the one rounding;
+ * expected = the oracle's unrounded cell put through the same three steps. */
+static int gemm_fused_check() {
+    const size_t m = 512, n = 512, k = 256;
+    std::vector<uint16_t> a(m * k), b(n * k), c(m * n), bias(n);
+    fko_gemm_stage(0, m, k, a.data());
+    fko_gemm_stage(1, n, k, b.data());
+    for (size_t column = 0; column < n; ++column) bias[column] = fko_to_bf16(float(column % 9) - 4.0f);
+    const uint64_t a_dev = stage(a), b_dev = stage(b), bias_dev = stage(bias);
+    void* c_dev = nullptr;
+    uint32_t* status = nullptr;
+    CUDA(cudaMalloc(&c_dev, c.size() * 2));
+    CUDA(cudaMalloc(reinterpret_cast<void**>(&status), 32));
+    CUDA(cudaMemset(c_dev, 0, c.size() * 2));
+    CUDA(cudaMemset(status, 0, 32));
+    kittens::gemm::run(nullptr, a_dev, b_dev, reinterpret_cast<uint64_t>(c_dev), m, n, k, kittens::gemm::GROUP, status,
+                       FK_GEMM_RELU, bias_dev);
+    kittens::watchdog::wait(nullptr);
+    kittens::check(fk_status_check(status, nullptr));
+    CUDA(cudaMemcpy(c.data(), c_dev, c.size() * 2, cudaMemcpyDeviceToHost));
+    size_t wrong = 0, zeros = 0;
+    for (size_t row = 0; row < m; ++row)
+        for (size_t column = 0; column < n; ++column) {
+            const float value = fko_gemm_exact(row, column, k) + fko_from_bf16(bias[column]);
+            const uint16_t expected = fko_to_bf16(value > 0.0f ? value : 0.0f);
+            wrong += c[row * n + column] != expected;
+            zeros += expected == 0;
+        }
+    std::printf("gemm %zux%zux%zu + bias, relu: %zu of %zu elements wrong (%zu clamped to zero)\n", m, n, k, wrong,
+                m * n, zeros);
+    cudaFree(reinterpret_cast<void*>(a_dev));
+    cudaFree(reinterpret_cast<void*>(b_dev));
+    cudaFree(reinterpret_cast<void*>(bias_dev));
+    cudaFree(c_dev);
+    cudaFree(status);
+    return wrong != 0 || zeros == 0;
 }
 
 static int flash_check() {
@@ -257,6 +296,7 @@ int main() {
             if (std::string(error.what()).find("traversal group width of 0") == std::string::npos) throw;
         }
         if (gemm_check()) return 1;
+        if (gemm_fused_check()) return 1;
         if (flash_check()) return 1;
         if (flash_backward_check()) return 1;
         if (rows_check()) return 1;

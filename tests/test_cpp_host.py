@@ -40,4 +40,5 @@ def test_cpp_caller_runs_the_reference_checks(device):
     assert result.returncode == 0, result.stdout + result.stderr
     assert "check ok" in result.stdout
     assert "exact at groups" in result.stdout and "rows attended" in result.stdout
+    assert "+ bias, relu: 0 of" in result.stdout
     assert "gradients, worst error" in result.stdout and "rows normalized" in result.stdout
