@@ -29,4 +29,13 @@ int scratch(int slot, size_t bytes, void** out);
 /// 8 status words per device for the host-buffer entry points.
 int scratch_status(uint32_t** out);
 
+/// What a launch needs to know about the current device, asked of the runtime once per device:
+/// a launch of a few microseconds must not pay several attribute queries each time.
+struct DeviceFacts {
+    int device;
+    int sm_count;
+    int shared_optin_limit;  // cudaDevAttrMaxSharedMemoryPerBlockOptin
+};
+int device_facts(DeviceFacts* out);
+
 }  // namespace fk

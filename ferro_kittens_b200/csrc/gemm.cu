@@ -454,9 +454,10 @@ extern "C" int fk_gemm_launch_fused(const void* a_map, const void* b_map, const 
     if (group == 0)
         return fk_fail(FK_ERR_SHAPE, "a traversal group width of 0 has no tiles in it");
 
-    int device = 0, sm_count = 0;
-    FK_CUDA(cudaGetDevice(&device));
-    FK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
+    DeviceFacts facts;
+    const int known = device_facts(&facts);
+    if (known != FK_OK) return known;
+    const int sm_count = facts.sm_count;
     uint32_t limit = 0;
     const int admitted = fk_admit_shared_plan(
         reinterpret_cast<const void*>(gemm::gemm_bf16_pair_kernel), gemm::kSharedBytes, &limit);

@@ -236,20 +236,70 @@ extern "C" uint64_t fk_plan_tmem_slot(fk_plan_t* plan) {
 
 // ------------------------------------------------------------------ launch envelope
 
+namespace fk {
+
+int device_facts(DeviceFacts* out) {
+    static std::mutex guard;
+    static DeviceFacts known[64];
+    static bool valid[64] = {};
+    int device = 0;
+    FK_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= 64) return fk_fail(FK_ERR_INVALID, "device index %d out of range", device);
+    std::lock_guard<std::mutex> lock(guard);
+    if (!valid[device]) {
+        DeviceFacts facts{device, 0, 0};
+        FK_CUDA(cudaDeviceGetAttribute(&facts.sm_count, cudaDevAttrMultiProcessorCount, device));
+        FK_CUDA(cudaDeviceGetAttribute(&facts.shared_optin_limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+        known[device] = facts;
+        valid[device] = true;
+    }
+    *out = known[device];
+    return FK_OK;
+}
+
+}  // namespace fk
+
+// The admission is monotonic, so what has been granted to a (device, kernel) pair is remembered and a
+// repeated request within it costs a table look-up instead of two runtime queries.
 extern "C" int fk_admit_shared_plan(const void* kernel, uint32_t bytes, uint32_t* limit_out) {
     if (!kernel) return fk_fail(FK_ERR_INVALID, "the kernel pointer is null");
-    int device = 0, limit = 0;
-    FK_CUDA(cudaGetDevice(&device));
-    FK_CUDA(cudaDeviceGetAttribute(&limit, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+    fk::DeviceFacts facts;
+    const int known = fk::device_facts(&facts);
+    if (known != FK_OK) return known;
+    const int limit = facts.shared_optin_limit;
     if (limit_out) *limit_out = (uint32_t)limit;
     if (bytes > (uint32_t)limit)
         return fk_fail(FK_ERR_TOO_LARGE,
                        "shared plan of %u B is past this device's %d B opt-in limit per block", bytes,
                        limit);
+    struct Granted {
+        const void* kernel;
+        int device;
+        uint32_t bytes;
+    };
+    static std::mutex guard;
+    static Granted granted[64];
+    static uint32_t count = 0;
+    {
+        std::lock_guard<std::mutex> lock(guard);
+        for (uint32_t i = 0; i < count; ++i)
+            if (granted[i].kernel == kernel && granted[i].device == facts.device && bytes <= granted[i].bytes)
+                return FK_OK;
+    }
     cudaFuncAttributes attributes;
     FK_CUDA(cudaFuncGetAttributes(&attributes, kernel));
-    if ((int)bytes <= attributes.maxDynamicSharedSizeBytes) return FK_OK;  // never lowers
-    FK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    uint32_t now = (uint32_t)attributes.maxDynamicSharedSizeBytes;
+    if (bytes > now) {  // never lowers
+        FK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+        now = bytes;
+    }
+    std::lock_guard<std::mutex> lock(guard);
+    for (uint32_t i = 0; i < count; ++i)
+        if (granted[i].kernel == kernel && granted[i].device == facts.device) {
+            if (now > granted[i].bytes) granted[i].bytes = now;
+            return FK_OK;
+        }
+    if (count < 64) granted[count++] = Granted{kernel, facts.device, now};
     return FK_OK;
 }
 

@@ -302,9 +302,10 @@ static int launch_rows(const void* source, const void* gamma, const void* beta, 
     if (rows_total / rows::kTileRows > 0xffffffffull)
         return fk_fail(FK_ERR_SHAPE, "%llu rows is more tiles than a launch counts",
                        static_cast<unsigned long long>(rows_total));
-    int device = 0, sm_count = 0;
-    FK_CUDA(cudaGetDevice(&device));
-    FK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
+    DeviceFacts facts;
+    const int known = device_facts(&facts);
+    if (known != FK_OK) return known;
+    const int sm_count = facts.sm_count;
     uint32_t limit = 0;
     const int admitted =
         fk_admit_shared_plan(reinterpret_cast<const void*>(rows::rows_kernel<OP>), rows::kSharedBytes, &limit);
