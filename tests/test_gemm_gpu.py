@@ -113,14 +113,16 @@ def test_host_buffer_entry_point(device):
     assert wrong == 0
 
 
-@pytest.mark.parametrize("shape", [(16384, 16384, 16384)])
-def test_full_size_properties(device, shape):
-    """At the benchmark's size: sampled rows against the oracle, and the whole matrix against
-    a bf16 matmul by torch within one rounding."""
+@pytest.mark.parametrize("shape, seed, deviation", [((16384, 16384, 16384), 1, None), ((8192, 28672, 8192), 2, 0.02)])
+def test_full_size_properties(device, shape, seed, deviation):
+    """At the benchmark's sizes (the 16384-cubed case with N(0, 1)/sqrt(K) entries, the 8192 x 28672
+    x 8192 up-projection shape with N(0, 0.02)): sampled rows against the oracle, and the whole matrix
+    against a bf16 matmul by torch within one rounding."""
     m, n, k = shape
-    generator = torch.Generator(device=device).manual_seed(1)
-    a = (torch.randn((m, k), generator=generator, device=device) / math.sqrt(k)).to(torch.bfloat16)
-    b = (torch.randn((n, k), generator=generator, device=device) / math.sqrt(k)).to(torch.bfloat16)
+    generator = torch.Generator(device=device).manual_seed(seed)
+    deviation = deviation if deviation is not None else 1.0 / math.sqrt(k)
+    a = (torch.randn((m, k), generator=generator, device=device) * deviation).to(torch.bfloat16)
+    b = (torch.randn((n, k), generator=generator, device=device) * deviation).to(torch.bfloat16)
     c = _run_checked(a, b)
     rows = [0, 4097, m - 1]
     a_words = _to_words(a[rows].contiguous())
