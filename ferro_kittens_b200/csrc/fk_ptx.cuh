@@ -458,6 +458,25 @@ __device__ __forceinline__ float ex2_approx(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+
+// 2^x for a pair, on the FMA pipe: clamp, split x = n + f with f in [-0.5, 0.5] by the
+// 1.5 * 2^23 shift trick, a degree-3 minimax polynomial for 2^f (maximum relative error
+// 7.5e-5, far inside a rounding to bf16), then n added into the exponent field. The same
+// split the reference's `exp2_approx` makes (src/reg.rs:81-93), on packed fp32 pairs.
+__device__ __forceinline__ float2 exp2_pair_fma(float2 x) {
+    constexpr float kShift = 12582912.0f;  // 1.5 * 2^23
+    x.x = fmaxf(x.x, -125.0f);
+    x.y = fmaxf(x.y, -125.0f);
+    const float2 shifted = __fadd2_rn(x, make_float2(kShift, kShift));
+    const float2 whole = __fadd2_rn(shifted, make_float2(-kShift, -kShift));
+    const float2 f = __ffma2_rn(whole, make_float2(-1.0f, -1.0f), x);
+    float2 p = __ffma2_rn(f, make_float2(0.05517166f, 0.05517166f), make_float2(0.24261113f, 0.24261113f));
+    p = __ffma2_rn(p, f, make_float2(0.69326097f, 0.69326097f));
+    p = __ffma2_rn(p, f, make_float2(0.99992806f, 0.99992806f));
+    p.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(shifted.x) << 23));
+    p.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(shifted.y) << 23));
+    return p;
+}
 __device__ __forceinline__ float lg2_approx(float x) {
     float y;
     asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -111,25 +111,6 @@ __device__ __forceinline__ Extent extent(uint32_t q_row0, uint32_t seq, bool cau
     return e;
 }
 
-// 2^x for a pair, on the FMA pipe: clamp, split x = n + f with f in [-0.5, 0.5] by the
-// 1.5 * 2^23 shift trick, a degree-3 minimax polynomial for 2^f (maximum relative error
-// 7.5e-5, far inside P's rounding to bf16), then n added into the exponent field. The same
-// split the reference's `exp2_approx` makes (src/reg.rs:81-93), on packed fp32 pairs.
-__device__ __forceinline__ float2 exp2_pair_fma(float2 x) {
-    constexpr float kShift = 12582912.0f;  // 1.5 * 2^23
-    x.x = fmaxf(x.x, -125.0f);
-    x.y = fmaxf(x.y, -125.0f);
-    const float2 shifted = __fadd2_rn(x, make_float2(kShift, kShift));
-    const float2 whole = __fadd2_rn(shifted, make_float2(-kShift, -kShift));
-    const float2 f = __ffma2_rn(whole, make_float2(-1.0f, -1.0f), x);
-    float2 p = __ffma2_rn(f, make_float2(0.05517166f, 0.05517166f), make_float2(0.24261113f, 0.24261113f));
-    p = __ffma2_rn(p, f, make_float2(0.69326097f, 0.69326097f));
-    p = __ffma2_rn(p, f, make_float2(0.99992806f, 0.99992806f));
-    p.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(shifted.x) << 23));
-    p.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(shifted.y) << 23));
-    return p;
-}
-
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));

@@ -112,21 +112,6 @@ enum StallCode : uint32_t {
 // three quarters and more are slower than none.
 constexpr uint32_t kPolyMask = FK_BWD_POLY_MASK;
 
-__device__ __forceinline__ float2 exp2_pair_fma(float2 x) {
-    constexpr float kShift = 12582912.0f;  // 1.5 * 2^23
-    x.x = fmaxf(x.x, -125.0f);
-    x.y = fmaxf(x.y, -125.0f);
-    const float2 shifted = __fadd2_rn(x, make_float2(kShift, kShift));
-    const float2 whole = __fadd2_rn(shifted, make_float2(-kShift, -kShift));
-    const float2 f = __ffma2_rn(whole, make_float2(-1.0f, -1.0f), x);
-    float2 p = __ffma2_rn(f, make_float2(0.05517166f, 0.05517166f), make_float2(0.24261113f, 0.24261113f));
-    p = __ffma2_rn(p, f, make_float2(0.69326097f, 0.69326097f));
-    p = __ffma2_rn(p, f, make_float2(0.99992806f, 0.99992806f));
-    p.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(shifted.x) << 23));
-    p.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(shifted.y) << 23));
-    return p;
-}
-
 // -lse * log2(e) and -delta = -rowsum(dO * O) (negated: they enter as addends), one query row per 16 lanes.
 __global__ void __launch_bounds__(256) stats_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,
                                                     const float* __restrict__ lse, float* __restrict__ stats,

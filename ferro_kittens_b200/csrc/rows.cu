@@ -39,6 +39,14 @@ constexpr uint32_t kWarpRows = kTileRows / kComputeWarps;  // 8
 constexpr uint32_t kSteps = kWarpRows / 2;                 // two rows per warp-wide access
 constexpr uint32_t kThreads = (kComputeWarps + 1) * 32;
 
+// Of a lane's four pairs per row, the pairs whose bit is set take 2^x from the FMA-pipe polynomial
+// instead of the ex2 unit. Off by default: one pair of four measured +3 % at a power-capped clock and
+// nothing otherwise, and the polynomial's 7.5e-5 on top of the bf16 rounding crosses the 2^-8 gate.
+#ifndef FK_ROWS_POLY_MASK
+#define FK_ROWS_POLY_MASK 0x0u
+#endif
+constexpr uint32_t kPolyMask = FK_ROWS_POLY_MASK;
+
 enum Operation : int { kSoftmax = 0, kLayerNorm = 1, kGroupNorm = 2 };
 
 struct Plan {
@@ -85,16 +93,18 @@ __device__ __forceinline__ void bulk_store(void* dst, uint32_t src, uint32_t byt
 __device__ __forceinline__ void ld_shared_v4(uint32_t addr, uint32_t (&v)[4]) {
     asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(addr));
 }
-// Sum / max over the 16 lanes that hold one row.
+// Sum over the 16 lanes that hold one row.
 __device__ __forceinline__ float row_sum(float v) {
 #pragma unroll
     for (uint32_t mask = 8; mask > 0; mask >>= 1) v += __shfl_xor_sync(0xffffffffu, v, mask);
     return v;
 }
-__device__ __forceinline__ float row_max(float v) {
-#pragma unroll
-    for (uint32_t mask = 8; mask > 0; mask >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, mask));
-    return v;
+
+// Element-wise maximum of two packed bf16 pairs.
+__device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("max.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
 }
 
 template <int OP>
@@ -156,21 +166,22 @@ __global__ void __launch_bounds__(kThreads, 1) rows_kernel(const Arguments args,
         const uint32_t sub = lane >> 4;    // which of the two rows of a step
         const uint32_t chunk = lane & 15;  // which 8 columns of the row
         const uint32_t offset = (kWarpRows * warp + sub) * kRowBytes + chunk * 16;
-        float gamma[8], beta[8];
+        // Everything below works on packed fp32 pairs (add/mul/fma.f32x2): half the instructions of
+        // the scalar form, which is what keeps these kernels on the memory roofline when the chip
+        // runs at its power-capped clock.
+        float2 gamma[4], beta[4];
         if (OP == kLayerNorm) {
             const uint4 g = *reinterpret_cast<const uint4*>(args.gamma + 8 * chunk);
             const uint4 b = *reinterpret_cast<const uint4*>(args.beta + 8 * chunk);
             const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, bw[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
             for (uint32_t i = 0; i < 4; ++i) {
-                gamma[2 * i] = __uint_as_float(gw[i] << 16);
-                gamma[2 * i + 1] = __uint_as_float(gw[i] & 0xffff0000u);
-                beta[2 * i] = __uint_as_float(bw[i] << 16);
-                beta[2 * i + 1] = __uint_as_float(bw[i] & 0xffff0000u);
+                gamma[i] = make_float2(__uint_as_float(gw[i] << 16), __uint_as_float(gw[i] & 0xffff0000u));
+                beta[i] = make_float2(__uint_as_float(bw[i] << 16), __uint_as_float(bw[i] & 0xffff0000u));
             }
         }
         uint32_t agreements = 0;
-        // All eight warps fold their partial sums: a bounded rendezvous, alternating two barriers
+        // All compute warps fold their partial sums: a bounded rendezvous, alternating two barriers
         // and two halves of the scratch so that a fast warp's next use cannot overtake a slow one's read.
         auto tile_sum = [&](float value, bool& live) {
 #pragma unroll
@@ -186,92 +197,103 @@ __global__ void __launch_bounds__(kThreads, 1) rows_kernel(const Arguments args,
             for (uint32_t w = 0; w < kComputeWarps; ++w) total += partials[which * kComputeWarps + w];
             return total;
         };
+        // Sum of the eight values a lane holds of one row.
+        const auto lane_sum = [](const float2 (&v)[4]) {
+            const float2 pair = __fadd2_rn(__fadd2_rn(v[0], v[1]), __fadd2_rn(v[2], v[3]));
+            return pair.x + pair.y;
+        };
 
         bool live = true;
         for (uint32_t it = 0; live && it < count; ++it) {
             const uint32_t s = it % kStages;
             if (!mbar_wait(full + 8 * s, (it / kStages) & 1u, site, kStallCompute, it)) break;
             const uint32_t slot = ring + s * kTileBytes + offset;
-            float x[kSteps][8];
+            float2 x[kSteps][4];
+            uint32_t words[kSteps][4];
 #pragma unroll
             for (uint32_t step = 0; step < kSteps; ++step) {
-                uint32_t words[4];
-                ld_shared_v4(slot + step * 2 * kRowBytes, words);
+                ld_shared_v4(slot + step * 2 * kRowBytes, words[step]);
 #pragma unroll
-                for (uint32_t i = 0; i < 4; ++i) {
-                    x[step][2 * i] = __uint_as_float(words[i] << 16);
-                    x[step][2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u);
-                }
+                for (uint32_t i = 0; i < 4; ++i)
+                    x[step][i] = make_float2(__uint_as_float(words[step][i] << 16),
+                                             __uint_as_float(words[step][i] & 0xffff0000u));
             }
 
             if (OP == kSoftmax) {
                 // 2^(x - peak) / sum, the reference's three passes (softmax.rs:137-160) over registers.
+                // The peak is found on the packed bf16 words: the maximum of bf16 values is one of them.
 #pragma unroll
                 for (uint32_t step = 0; step < kSteps; ++step) {
-                    float peak = x[step][0];
+                    uint32_t top = max_bf16x2(max_bf16x2(words[step][0], words[step][1]),
+                                              max_bf16x2(words[step][2], words[step][3]));
 #pragma unroll
-                    for (uint32_t i = 1; i < 8; ++i) peak = fmaxf(peak, x[step][i]);
-                    peak = row_max(peak);
-                    float total = 0.0f;
+                    for (uint32_t mask = 8; mask > 0; mask >>= 1)
+                        top = max_bf16x2(top, __shfl_xor_sync(0xffffffffu, top, mask));
+                    const float peak = fmaxf(__uint_as_float(top << 16), __uint_as_float(top & 0xffff0000u));
+                    const float2 shift = make_float2(-peak, -peak);
 #pragma unroll
-                    for (uint32_t i = 0; i < 8; ++i) {
-                        x[step][i] = ex2_approx(x[step][i] - peak);
-                        total += x[step][i];
+                    for (uint32_t i = 0; i < 4; ++i) {
+                        const float2 d = __fadd2_rn(x[step][i], shift);
+                        x[step][i] = ((kPolyMask >> i) & 1u) ? exp2_pair_fma(d)
+                                                             : make_float2(ex2_approx(d.x), ex2_approx(d.y));
                     }
-                    const float scale = __frcp_rn(row_sum(total));
+                    const float scale = __frcp_rn(row_sum(lane_sum(x[step])));
+                    const float2 scale2 = make_float2(scale, scale);
 #pragma unroll
-                    for (uint32_t i = 0; i < 8; ++i) x[step][i] *= scale;
+                    for (uint32_t i = 0; i < 4; ++i) x[step][i] = __fmul2_rn(x[step][i], scale2);
                 }
             } else if (OP == kLayerNorm) {
                 // Mean, centred variance, then gamma * (x - mean) * rsqrt(var + eps) + beta
                 // (layernorm.rs:173-206).
 #pragma unroll
                 for (uint32_t step = 0; step < kSteps; ++step) {
-                    float total = 0.0f;
+                    const float mean = row_sum(lane_sum(x[step])) * (1.0f / kColumns);
+                    const float2 shift = make_float2(-mean, -mean);
+                    float2 square = make_float2(0.0f, 0.0f);
 #pragma unroll
-                    for (uint32_t i = 0; i < 8; ++i) total += x[step][i];
-                    const float mean = row_sum(total) * (1.0f / kColumns);
-                    float square = 0.0f;
-#pragma unroll
-                    for (uint32_t i = 0; i < 8; ++i) {
-                        x[step][i] -= mean;
-                        square += x[step][i] * x[step][i];
+                    for (uint32_t i = 0; i < 4; ++i) {
+                        x[step][i] = __fadd2_rn(x[step][i], shift);
+                        square = __ffma2_rn(x[step][i], x[step][i], square);
                     }
-                    const float deviation = rsqrtf(row_sum(square) * (1.0f / kColumns) + args.epsilon);
+                    const float deviation = rsqrtf(row_sum(square.x + square.y) * (1.0f / kColumns) + args.epsilon);
+                    const float2 deviation2 = make_float2(deviation, deviation);
 #pragma unroll
-                    for (uint32_t i = 0; i < 8; ++i) x[step][i] = x[step][i] * deviation * gamma[i] + beta[i];
+                    for (uint32_t i = 0; i < 4; ++i)
+                        x[step][i] = __ffma2_rn(__fmul2_rn(x[step][i], deviation2), gamma[i], beta[i]);
                 }
             } else {
                 // The same statistic over the whole tile (layernorm.rs:262-300).
                 constexpr float kScale = 1.0f / (kTileRows * kColumns);
-                float total = 0.0f;
+                float2 total = make_float2(0.0f, 0.0f);
 #pragma unroll
                 for (uint32_t step = 0; step < kSteps; ++step)
 #pragma unroll
-                    for (uint32_t i = 0; i < 8; ++i) total += x[step][i];
-                const float mean = tile_sum(total, live) * kScale;
+                    for (uint32_t i = 0; i < 4; ++i) total = __fadd2_rn(total, x[step][i]);
+                const float mean = tile_sum(total.x + total.y, live) * kScale;
                 if (!live) break;
-                float square = 0.0f;
+                const float2 shift = make_float2(-mean, -mean);
+                float2 square = make_float2(0.0f, 0.0f);
 #pragma unroll
                 for (uint32_t step = 0; step < kSteps; ++step)
 #pragma unroll
-                    for (uint32_t i = 0; i < 8; ++i) {
-                        x[step][i] -= mean;
-                        square += x[step][i] * x[step][i];
+                    for (uint32_t i = 0; i < 4; ++i) {
+                        x[step][i] = __fadd2_rn(x[step][i], shift);
+                        square = __ffma2_rn(x[step][i], x[step][i], square);
                     }
-                const float deviation = rsqrtf(tile_sum(square, live) * kScale + args.epsilon);
+                const float deviation = rsqrtf(tile_sum(square.x + square.y, live) * kScale + args.epsilon);
                 if (!live) break;
+                const float2 deviation2 = make_float2(deviation, deviation);
 #pragma unroll
                 for (uint32_t step = 0; step < kSteps; ++step)
 #pragma unroll
-                    for (uint32_t i = 0; i < 8; ++i) x[step][i] *= deviation;
+                    for (uint32_t i = 0; i < 4; ++i) x[step][i] = __fmul2_rn(x[step][i], deviation2);
             }
 
 #pragma unroll
             for (uint32_t step = 0; step < kSteps; ++step)
-                st_shared_v4(slot + step * 2 * kRowBytes, pack_bf16x2(x[step][0], x[step][1]),
-                             pack_bf16x2(x[step][2], x[step][3]), pack_bf16x2(x[step][4], x[step][5]),
-                             pack_bf16x2(x[step][6], x[step][7]));
+                st_shared_v4(slot + step * 2 * kRowBytes, pack_bf16x2(x[step][0].x, x[step][0].y),
+                             pack_bf16x2(x[step][1].x, x[step][1].y), pack_bf16x2(x[step][2].x, x[step][2].y),
+                             pack_bf16x2(x[step][3].x, x[step][3].y));
             // The bulk store reads the slot through the async proxy.
             fence_proxy_async_shared();
             __syncwarp();
