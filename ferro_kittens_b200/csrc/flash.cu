@@ -11,11 +11,12 @@
 // 128-row query tiles and ping-pongs them, so the tensor core works on one
 // tile while the CUDA cores run the other's softmax.
 //
-//   warps 0-3   softmax of query tile 0: one thread per row (tcgen05.ld 32x32b), running max
-//               and sum in registers, P written back to tensor memory as bf16 over S, the
-//               output accumulator rescaled in tensor memory only when the max moved by
-//               more than 2^8; final normalise, bf16 staging and TMA store.
-//   warps 4-7   the same for query tile 1.
+//   warps 0-7   softmax, all eight on one query tile at a time, alternating tiles: warps w and
+//               w + 4 own the same 32 rows (tcgen05.ld 32x32b, one thread per row) and 64 key
+//               columns each, swap half-row maxima through shared memory, keep running max and
+//               sum in registers, write P back to tensor memory as bf16 over S, rescale the
+//               output accumulator in tensor memory only when the max moved by more than 2^8;
+//               final normalise, bf16 staging and TMA store.
 //   warp 8      loader: Q once, then K(j), V(j) 128-key blocks through a ring of kSlots slots.
 //   warp 9      MMA issue: S_t = Q_t K(j)^T (8 x M128 N128 K16) and O_t += P_t V(j)
 //               (8 x M128 N128 K16, A from tensor memory), interleaved across the two tiles.
@@ -313,7 +314,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         // key columns 0-63 of a score block and warps 4-7 columns 64-127, so the two warps
         // that share a scheduler (and its ex2 unit) overlap one's exponentials with the
         // other's FMA-pipe work. Two sibling warps own the same 32 rows and swap half-row
-        // maxima through shared memory under a 64-thread named barrier.
+        // maxima through shared memory under a two-arrival mbarrier (a bounded wait).
         const uint32_t half = warp >> 2;         // which 64 key columns / 64 head columns
         const uint32_t quadrant = warp & 3u;     // tensor-memory lanes this warp may touch
         const uint32_t row = 32 * quadrant + lane;  // row of the tile this thread owns
