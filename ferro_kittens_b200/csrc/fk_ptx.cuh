@@ -220,6 +220,11 @@ __device__ __forceinline__ void tma_store_wait_read() {
 __device__ __forceinline__ void tma_store_wait_all() {
     asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
+/// Before a CTA exits: every store group has finished READING shared memory, which is all the CTA
+/// still owes them; the writes themselves complete with the grid, like any other store in flight.
+__device__ __forceinline__ void tma_store_wait_before_exit() {
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }

@@ -521,7 +521,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
             }
         }
-        if (lane == 0) tma_store_wait_all();
+        if (lane == 0) tma_store_wait_before_exit();
     }
 
     // ---------------------------------------------------- teardown

@@ -73,6 +73,8 @@ constexpr Plan kPlan{};
 constexpr uint32_t kBaseAlign = 1024;
 constexpr uint32_t kSharedBytes = static_cast<uint32_t>(kPlan.end.bytes());
 static_assert(kSharedBytes <= 232448, "plan exceeds the opt-in shared memory of an sm_100 CTA");
+static_assert(kEpilogueWarps * kPasses * kBandBytes <= kStages * kHalves * kATileBytes,
+              "the last item stages every pass of every epilogue warp in the A ring");
 static_assert(kPlan.a_ring.at % 1024 == 0 && kPlan.b_ring.at % 1024 == 0 &&
                   kPlan.bands.at % 1024 == 0,
               "swizzled tiles must start on a 1024-byte boundary");
@@ -154,6 +156,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const uint32_t peer = rank ^ 1u;
+#ifdef FK_GEMM_TRACE
+    // Development build: clock stamps of the leader CTA of cluster 0, after the status words.
+    auto trace = [&](uint32_t point) {
+        if (blockIdx.x == 0 && lane == 0) reinterpret_cast<long long*>(status + 4)[point] = clock64();
+    };
+#else
+    auto trace = [](uint32_t) {};
+#endif
+    if (warp == 0) trace(0);
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
@@ -175,6 +186,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     tc_fence_after_sync();
     if (warp == 1) tmem_relinquish<2>();
     const uint32_t tmem = *slot_ptr;
+    if (warp == 0) trace(1);
 
     const StallSite site{status, stop_flag, mapa(stop_addr, peer)};
 
@@ -194,10 +206,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 for (uint32_t k = 0; k < plan.k_blocks; ++k, ++fill) {
                     const uint32_t s = fill % kStages;
                     const uint32_t parity = (fill / kStages) & 1u;
+                    if (fill == 0) trace(12);
                     if (!mbar_wait(empty + 8 * s, parity ^ 1u, site, kStallProducer, fill)) {
                         live = false;
                         break;
                     }
+                    if (fill == 0) trace(13);
                     const uint32_t arrive_at = mapa(full + 8 * s, 0);
                     if (rank == 0) mbar_arrive_expect_tx(full + 8 * s, pair_bytes);
                     const int column = static_cast<int>(kBlockK * k);
@@ -207,6 +221,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                     if (item.halves == 2)
                         tma_load_2d_pair(a_ring + (s * kHalves + 1) * kATileBytes, &a_map, column,
                                          a_row + static_cast<int>(2 * kBlockM), arrive_at);
+                    if (k == 0) trace(2);
+                    if (k + 1 == plan.k_blocks) trace(3);
                 }
             }
         }
@@ -237,6 +253,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                         break;
                     }
                     tc_fence_after_sync();
+                    if (k == 0) trace(4);
+                    if (k + 1 == plan.k_blocks) trace(5);
                     const uint64_t a0_desc = operand_descriptor(
                         a_ring + (s * kHalves) * kATileBytes, kKMajorLeadingBytes);
                     const uint64_t a1_desc = operand_descriptor(
@@ -281,6 +299,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 if (!live) break;
                 mma_commit<2>(acc_full);
                 mma_commit<2>(mapa(acc_full, 1));
+                trace(6);
                 ++count;
             }
         }
@@ -302,6 +321,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             }
             ++count;
             tc_fence_after_sync();
+            if (warp == 2) trace(7);
             const bool mine = half < item.halves;
             // Read this warp's [32, 256] band out as bf16 pairs, then release the accumulator:
             // the stores below overlap the next item's main loop.
@@ -355,10 +375,40 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(mapa(acc_empty, 0));
+            if (warp == 2) trace(8);
             if (!mine) continue;
 
             const int c_row =
                 static_cast<int>(item.row + 2 * kBlockM * half + kBlockM * rank + 32 * quadrant);
+            if (index + cluster_count_x() >= plan.items) {
+                // This CTA's last item: no load is outstanding or to come and every MMA that read
+                // the operand ring has retired (acc_full), so the ring is free shared memory. Each
+                // warp stages all its passes there at once, kPasses tiles of its own, and the
+                // stores go out back to back instead of waiting for one staging tile in turn.
+                const uint32_t spare = a_ring + (warp - 2) * kPasses * kBandBytes;
+#pragma unroll
+                for (uint32_t pass = 0; pass < kPasses; ++pass)
+#pragma unroll
+                    for (uint32_t chunk = 0; chunk < 8; ++chunk)
+                        st_shared_v4(spare + pass * kBandBytes + swizzled_chunk_offset(lane, chunk, 0),
+                                     held[pass][4 * chunk], held[pass][4 * chunk + 1],
+                                     held[pass][4 * chunk + 2], held[pass][4 * chunk + 3]);
+                fence_proxy_async_shared();
+                __syncwarp();
+                if (lane == 0) {
+#pragma unroll
+                    for (uint32_t pass = 0; pass < kPasses; ++pass) {
+                        if (plan.accumulate)
+                            tma_reduce_add_2d(&c_map, spare + pass * kBandBytes,
+                                              static_cast<int>(item.column + pass * kStageColumns), c_row);
+                        else
+                            tma_store_2d(&c_map, spare + pass * kBandBytes,
+                                         static_cast<int>(item.column + pass * kStageColumns), c_row);
+                    }
+                    tma_store_commit();
+                }
+                continue;
+            }
 #pragma unroll
             for (uint32_t pass = 0; pass < kPasses; ++pass) {
                 // The store that last read this warp's staging tile must be done reading it.
@@ -383,7 +433,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 }
             }
         }
-        if (lane == 0) tma_store_wait_all();
+        if (warp == 2) trace(9);
+        if (lane == 0) tma_store_wait_before_exit();
+        if (warp == 2) trace(10);
     }
 
     // ---------------------------------------------------- teardown
@@ -395,6 +447,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     tc_fence_before_sync();
     __syncthreads();
     cluster_sync();
+    if (warp == 0) trace(11);
     if (warp == 1) tmem_dealloc<2>(tmem, kTmemColumns);
 }
 

@@ -159,7 +159,7 @@ __global__ void __launch_bounds__(kThreads, 1) rows_kernel(const Arguments args,
                     bulk_load(ring + s * kTileBytes, args.source + tile * kTileBytes, kTileBytes, full + 8 * s);
                 }
             }
-            tma_store_wait_all();
+            tma_store_wait_before_exit();
         }
     } else {
         // ------------------------------------------------ arithmetic
