@@ -103,8 +103,11 @@ def test_shape_guards_reject_before_launch(device):
         gemm.run(a.cpu(), b.cpu())
 
 
-def test_host_buffer_entry_point(device):
-    m, n, k = 512, 256, 256
+@pytest.mark.parametrize("shape", [(512, 256, 256), (4352, 512, 128)])
+def test_host_buffer_entry_point(device, shape):
+    """Host buffers in and out; the second shape is 17 row tiles, which the entry's pipeline cuts into
+    eight blocks of two tiles and a last block of one."""
+    m, n, k = shape
     a = oracle.gemm_stage("a", m, k)
     b = oracle.gemm_stage("b", n, k)
     c = np.zeros((m, n), dtype=np.uint16)
