@@ -228,6 +228,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         }
     } else if (warp == 1) {
         // ------------------------------------------------ MMA issue (leader only)
+        // The issuing thread: lane 0, or the one elect.sync picks (1). The attention kernels gain
+        // from the latter; here an M256 N256 MMA occupies the pipe for 128 cycles and the thread's
+        // own cost per MMA does not show (1436 vs 1439 TFLOP/s), so the plain form stays.
 #ifndef FK_GEMM_ISSUE_ELECT
 #define FK_GEMM_ISSUE_ELECT 0
 #endif
@@ -263,19 +266,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                         operand_descriptor(b_ring + s * kBTileBytes, kKMajorLeadingBytes);
                     const uint32_t accumulate = k != 0;
                     if (item.halves == 2) {
-#ifdef FK_GEMM_GROUPED_ISSUE
-#pragma unroll
-                        for (uint32_t chunk = 0; chunk < kBlockK / 16; ++chunk) {
-                            const uint64_t step = (chunk * kKMajorChunkBytes) >> 4;
-                            mma_ss<2>(tmem, a0_desc + step, b_desc + step, idesc, accumulate | chunk);
-                        }
-#pragma unroll
-                        for (uint32_t chunk = 0; chunk < kBlockK / 16; ++chunk) {
-                            const uint64_t step = (chunk * kKMajorChunkBytes) >> 4;
-                            mma_ss<2>(tmem + kBlockN, a1_desc + step, b_desc + step, idesc,
-                                      accumulate | chunk);
-                        }
-#else
 #pragma unroll
                         for (uint32_t chunk = 0; chunk < kBlockK / 16; ++chunk) {
                             // Advancing the 14-bit address field by 32 B per K=16 chunk.
@@ -284,7 +274,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                             mma_ss<2>(tmem + kBlockN, a1_desc + step, b_desc + step, idesc,
                                       accumulate | chunk);
                         }
-#endif
                     } else {
 #pragma unroll
                         for (uint32_t chunk = 0; chunk < kBlockK / 16; ++chunk) {
