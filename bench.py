@@ -31,6 +31,7 @@ sys.path.insert(0, ROOT)
 M = N = K = 16384
 GEMM_SEED = 1
 FLASH = dict(batch=16, heads=16, seq=4096, head_dim=128, seed=3, causal=False)
+FLASH_CAUSAL = dict(batch=4, heads=32, seq=16384, head_dim=128, seed=4, causal=True)
 WORKLOAD = "gemm_bf16_16384x16384x16384_normal_over_sqrtK_seed1"
 METRIC = "bf16_gemm_tflops_16384"
 #: 4 Mi rows x 128 bf16 = 1 GiB in and 1 GiB out per launch, far larger than the L2.
@@ -318,6 +319,33 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     bwd_value = 2.5 * flash_flops * args.steps / bwd_seconds / 1e12
     del qkv, out, lse, d_out, grads, workspace, leaves
 
+    # ---- the causal long-sequence forward (the sharded attention configuration), planes split across ranks
+    causal_planes = FLASH_CAUSAL["batch"] * FLASH_CAUSAL["heads"]
+    c0, c1 = shard.planes(causal_planes, world, rank)
+    generator = torch.Generator(device=device).manual_seed(FLASH_CAUSAL["seed"])
+    qkv = [torch.randn((causal_planes, FLASH_CAUSAL["seq"], 128), generator=generator, device=device)
+           .to(torch.bfloat16)[c0:c1].contiguous() for _ in range(3)]
+    out = torch.empty_like(qkv[0])
+    lse = torch.empty((c1 - c0, FLASH_CAUSAL["seq"]), dtype=torch.float32, device=device)
+
+    def causal_step():
+        check(library().fk_flash_fwd(qkv[0].data_ptr(), qkv[1].data_ptr(), qkv[2].data_ptr(), out.data_ptr(),
+                                     None, lse.data_ptr(), c1 - c0, FLASH_CAUSAL["seq"], 128 ** -0.5, 1, stream,
+                                     flash_status.data_ptr()))
+
+    causal_step()
+    gemm.check_status(flash_status)
+    reference = torch.nn.functional.scaled_dot_product_attention(
+        qkv[0][:1].unsqueeze(0), qkv[1][:1].unsqueeze(0), qkv[2][:1].unsqueeze(0), is_causal=True)[0]
+    causal_error = (out[:1].float() - reference.float()).abs().max().item()
+    if not causal_error <= 2e-2:
+        raise RuntimeError(f"causal flash forward disagrees with torch SDPA: max |diff| {causal_error}")
+    causal_seconds = max_over_ranks(time_steps(causal_step, args.steps, args.warmup, barrier))
+    # useful flops: key blocks above the diagonal are neither computed nor counted
+    causal_flops = 4.0 * causal_planes * 128 * FLASH_CAUSAL["seq"] * (FLASH_CAUSAL["seq"] + 1) / 2
+    causal_value = causal_flops * args.steps / causal_seconds / 1e12
+    del qkv, out, lse, reference
+
     # ---- the row kernels either side of the two contractions: rows split across ranks, HBM roofline
     from ferro_kittens_b200 import rows as row_kernels
 
@@ -412,6 +440,11 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                           "frac_of_measured_peak": flash_value / world / peaks["burst"],
                           "frac_of_nominal_2250": flash_value / world / 2250.0,
                           "max_abs_diff_vs_sdpa": flash_error},
+            "flash_fwd_causal": {"config": {k: v for k, v in FLASH_CAUSAL.items()}, "value": causal_value,
+                                 "unit": "TFLOP/s", "flops_counted": "4 * planes * 128 * seq * (seq + 1) / 2",
+                                 "ms_per_step": causal_seconds / args.steps * 1e3,
+                                 "frac_of_measured_peak": causal_value / world / peaks["burst"],
+                                 "max_abs_diff_vs_sdpa": causal_error},
             "flash_bwd": {"config": {k: v for k, v in FLASH.items()}, "value": bwd_value, "unit": "TFLOP/s",
                           "flops_counted": "10 * planes * seq^2 * 128 (five tile products; seven are executed)",
                           "ms_per_step": bwd_seconds / args.steps * 1e3,
