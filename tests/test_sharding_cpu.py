@@ -28,6 +28,25 @@ def test_gemm_columns_tile_the_matrix_in_whole_tiles():
         shard.gemm_columns(1024, 2, 2)
 
 
+@pytest.mark.parametrize("world", [1, 2, 3, 4, 6, 8])
+def test_gemm_blocks_tile_c_and_upload_least(world):
+    """Host-resident operands: the grid of C blocks covers C once, in whole tiles, and no other
+    whole-tile grid uploads fewer operand rows per rank."""
+    m = n = 16384
+    rows, columns = shard.gemm_grid(m, n, world)
+    assert rows * columns == world
+    covered = np.zeros((m // 256, n // 256), dtype=np.int32)
+    for rank in range(world):
+        r0, r1, c0, c1 = shard.gemm_block(m, n, world, rank)
+        assert r0 % 256 == 0 and r1 % 256 == 0 and c0 % 256 == 0 and c1 % 256 == 0
+        covered[r0 // 256:r1 // 256, c0 // 256:c1 // 256] += 1
+    assert (covered == 1).all()
+    for other in range(1, world + 1):
+        if world % other == 0 and m % (256 * other) == 0 and n % (256 * (world // other)) == 0:
+            assert m / rows + n / columns <= m / other + n / (world // other)
+    assert shard.gemm_grid(m, n, 8) == (2, 4) and shard.gemm_grid(m, n, 2) == (1, 2)
+
+
 def test_planes_tile_the_batch():
     for total, world in [(256, 8), (128, 8), (6, 4), (1, 2)]:
         blocks = [shard.planes(total, world, rank) for rank in range(world)]
