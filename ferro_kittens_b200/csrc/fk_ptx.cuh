@@ -114,6 +114,8 @@ struct StallSite {
     uint32_t peer_stop;      // shared::cluster address of the peer's flag, 0 if none
     long long budget = kWaitBudgetCycles;
     bool spin = false;       // poll with test_wait instead of suspending in try_wait
+    uint32_t nap = 0;        // when polling: nanoseconds to sleep between probes (0 = none), so that
+                             // the probes do not take issue slots from the warps being waited for
 };
 
 /// The non-suspending probe. A thread suspended in try_wait takes a few hundred cycles to come back
@@ -142,8 +144,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const S
     const long long start = clock64();
     for (;;) {
 #pragma unroll 1
-        for (int i = 0; i < 16; ++i)
+        for (int i = 0; i < 16; ++i) {
+            if (site.spin && site.nap) __nanosleep(site.nap);
             if (site.spin ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
+        }
         if (*site.stop) return false;
         if (clock64() - start > site.budget) {
             *site.stop = 1;

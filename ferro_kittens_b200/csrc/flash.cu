@@ -184,7 +184,19 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t tmem = *slot_ptr;
 
     // Every role here sits on the tile's dependency chain: poll, do not suspend.
-    const StallSite site{status, stop_flag, 0, kWaitBudgetCycles, true};
+#ifndef FK_FLASH_LOADER_SPIN
+#define FK_FLASH_LOADER_SPIN 1
+#endif
+#ifndef FK_FLASH_NAP_NS
+#define FK_FLASH_NAP_NS 0
+#endif
+#ifndef FK_FLASH_MMA_NAP_NS
+#define FK_FLASH_MMA_NAP_NS FK_FLASH_NAP_NS
+#endif
+    const StallSite site{status, stop_flag, 0, kWaitBudgetCycles, true, FK_FLASH_NAP_NS};
+    // The loader runs slots ahead of its consumers: it can afford to suspend.
+    const StallSite calm{status, stop_flag, 0, kWaitBudgetCycles, FK_FLASH_LOADER_SPIN != 0, 0};
+    const StallSite issue{status, stop_flag, 0, kWaitBudgetCycles, true, FK_FLASH_MMA_NAP_NS};
 #ifdef FK_FLASH_TRACE
     // Development build: clock stamps of the first blocks of CTA (0, 0), after the status words.
     auto trace = [&](uint32_t role, uint32_t block, uint32_t point) {
@@ -212,7 +224,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (uint32_t fill = 0; fill < 2 * keys.most; ++fill) {
                 const uint32_t s = fill % kSlots;
                 const uint32_t parity = (fill / kSlots) & 1u;
-                if (!mbar_wait(kv_empty + 8 * s, parity ^ 1u, site, kStallLoader, fill)) break;
+                if (!mbar_wait(kv_empty + 8 * s, parity ^ 1u, calm, kStallLoader, fill)) break;
                 mbar_arrive_expect_tx(kv_full + 8 * s, kBlockBytes);
                 const CUtensorMap* map = (fill & 1u) ? &v_map : &k_map;
                 const int row = static_cast<int>(kBlockKeys * (fill >> 1));
@@ -260,10 +272,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                 mma_commit<1>(o_done + 8 * t);
             };
 
-            bool live = mbar_wait(q_full, 0, site, kStallMmaQ, 0);
+            bool live = mbar_wait(q_full, 0, issue, kStallMmaQ, 0);
             if (live) {
                 tc_fence_after_sync();
-                live = mbar_wait(kv_full + 0, 0, site, kStallMmaKv, 0);
+                live = mbar_wait(kv_full + 0, 0, issue, kStallMmaKv, 0);
             }
             if (live) {
                 tc_fence_after_sync();
@@ -275,12 +287,12 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const uint32_t v_use = 2 * j + 1, k_use = 2 * j + 2;
                 const uint32_t v_slot = v_use % kSlots, k_slot = k_use % kSlots;
                 const bool more = j + 1 < keys.most;
-                if (!mbar_wait(kv_full + 8 * v_slot, (v_use / kSlots) & 1u, site, kStallMmaKv, v_use))
+                if (!mbar_wait(kv_full + 8 * v_slot, (v_use / kSlots) & 1u, issue, kStallMmaKv, v_use))
                     break;
                 bool next_loaded = false;
                 for (uint32_t t = 0; live && t < kTiles; ++t) {
                     if (j < keys.blocks[t]) {
-                        if (!mbar_wait(p_ready + 8 * t, j & 1u, site, kStallMmaP, j)) {
+                        if (!mbar_wait(p_ready + 8 * t, j & 1u, issue, kStallMmaP, j)) {
                             live = false;
                             break;
                         }
