@@ -537,8 +537,15 @@ def run_only(args, local_rank: int) -> None:
         name = f"flash_fwd_planes{planes}_seq{seq}_{'causal' if args.causal else 'full'}"
     seconds = time_steps(fn, args.steps, args.warmup, lambda: None)
     gemm.check_status(status)
-    print(json.dumps({"only": name, "steps": args.steps, "ms_per_step": seconds / args.steps * 1e3,
-                      "tflops": flops * args.steps / seconds / 1e12}), flush=True)
+    line = {"only": name, "steps": args.steps, "ms_per_step": seconds / args.steps * 1e3,
+            "tflops": flops * args.steps / seconds / 1e12}
+    if args.only == "gemm" and args.beside_library:
+        # The library's kernel for the same product, launched the same number of times, so that a
+        # launch list of this command holds both.
+        out = torch.empty((args.m, args.n), dtype=torch.bfloat16, device=device)
+        library_seconds = time_steps(lambda: torch.matmul(a, b.T, out=out), args.steps, args.warmup, lambda: None)
+        line["library_ms_per_step"] = library_seconds / args.steps * 1e3
+    print(json.dumps(line), flush=True)
 
 
 def main() -> None:
@@ -546,6 +553,8 @@ def main() -> None:
     parser.add_argument("--only", choices=["gemm", "flash", "flash_bwd", "softmax", "layernorm", "groupnorm"],
                         help="run one kernel alone (for profiling)")
     parser.add_argument("--rows", type=int, default=1 << 20, help="rows of 128 columns for the row kernels")
+    parser.add_argument("--beside-library", action="store_true",
+                        help="with --only gemm: also launch torch.matmul (cuBLAS) on the same operands")
     parser.add_argument("--m", type=int, default=8192)
     parser.add_argument("--n", type=int, default=8192)
     parser.add_argument("--k", type=int, default=8192)
