@@ -116,6 +116,7 @@ struct StallSite {
     bool spin = false;       // poll with test_wait instead of suspending in try_wait
     uint32_t nap = 0;        // when polling: nanoseconds to sleep between probes (0 = none), so that
                              // the probes do not take issue slots from the warps being waited for
+    uint32_t gap = 0;        // when polling: cycles to idle on the clock register between probes
 };
 
 /// The non-suspending probe. A thread suspended in try_wait takes a few hundred cycles to come back
@@ -146,6 +147,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const S
 #pragma unroll 1
         for (int i = 0; i < 16; ++i) {
             if (site.spin && site.nap) __nanosleep(site.nap);
+            if (site.spin && site.gap) {
+                const long long from = clock64();
+                while (clock64() - from < site.gap) {
+                }
+            }
             if (site.spin ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
         }
         if (*site.stop) return false;

@@ -190,13 +190,19 @@ __global__ void __launch_bounds__(kThreads, 1)
 #ifndef FK_FLASH_NAP_NS
 #define FK_FLASH_NAP_NS 0
 #endif
+#ifndef FK_FLASH_GAP
+#define FK_FLASH_GAP 0
+#endif
+#ifndef FK_FLASH_MMA_GAP
+#define FK_FLASH_MMA_GAP FK_FLASH_GAP
+#endif
 #ifndef FK_FLASH_MMA_NAP_NS
 #define FK_FLASH_MMA_NAP_NS FK_FLASH_NAP_NS
 #endif
-    const StallSite site{status, stop_flag, 0, kWaitBudgetCycles, true, FK_FLASH_NAP_NS};
+    const StallSite site{status, stop_flag, 0, kWaitBudgetCycles, true, FK_FLASH_NAP_NS, FK_FLASH_GAP};
     // The loader runs slots ahead of its consumers: it can afford to suspend.
     const StallSite calm{status, stop_flag, 0, kWaitBudgetCycles, FK_FLASH_LOADER_SPIN != 0, 0};
-    const StallSite issue{status, stop_flag, 0, kWaitBudgetCycles, true, FK_FLASH_MMA_NAP_NS};
+    const StallSite issue{status, stop_flag, 0, kWaitBudgetCycles, true, FK_FLASH_MMA_NAP_NS, FK_FLASH_MMA_GAP};
 #ifdef FK_FLASH_TRACE
     // Development build: clock stamps of the first blocks of CTA (0, 0), after the status words.
     auto trace = [&](uint32_t role, uint32_t block, uint32_t point) {
