@@ -60,7 +60,7 @@ constexpr float kRescaleThreshold = 8.0f;
 constexpr uint32_t kPolyMask = FK_FLASH_POLY_MASK;
 
 struct Plan {
-    SharedPlan q, kv, swap, q_full, kv_full, kv_empty, s_full, p_ready, o_done, pair, tmem_slot, stop,
+    SharedPlan q, kv, swap, q_full, kv_full, kv_empty, s_full, p_ready, p_soon, o_done, pair, tmem_slot, stop,
         end;
     constexpr Plan()
         : q(SharedPlan{}.tile_ring(kTileRows, kHead, 2, kTiles)),
@@ -71,7 +71,8 @@ struct Plan {
           kv_empty(kv_full.semaphores(kSlots)),
           s_full(kv_empty.semaphores(kTiles)),
           p_ready(s_full.semaphores(kTiles)),
-          o_done(p_ready.semaphores(kTiles)),
+          p_soon(p_ready.semaphores(kTiles)),
+          o_done(p_soon.semaphores(kTiles)),
           pair(o_done.semaphores(4)),
           tmem_slot(pair.tmem_slot()),
           stop(tmem_slot.word()),
@@ -140,6 +141,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t kv_empty = base + kPlan.kv_empty.at;
     const uint32_t s_full = base + kPlan.s_full.at;
     const uint32_t p_ready = base + kPlan.p_ready.at;
+    const uint32_t p_soon = base + kPlan.p_soon.at;
     const uint32_t o_done = base + kPlan.o_done.at;
     const uint32_t slot = base + kPlan.tmem_slot.at;
     volatile uint32_t* stop_flag =
@@ -163,6 +165,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (uint32_t t = 0; t < kTiles; ++t) {
             mbar_init(s_full + 8 * t, 1);
             mbar_init(p_ready + 8 * t, kSoftmaxWarps);
+            mbar_init(p_soon + 8 * t, kSoftmaxWarps);
             mbar_init(o_done + 8 * t, 1);
         }
         for (uint32_t quadrant = 0; quadrant < 4; ++quadrant)
@@ -184,6 +187,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t tmem = *slot_ptr;
 
     // Every role here sits on the tile's dependency chain: poll, do not suspend.
+// 0: the MMA thread polls `p_ready` from the moment it has nothing else to issue. 1 / 2: the softmax
+// warps also arrive on `p_soon` before their exponentials / after the first half of them, and the MMA
+// thread suspends on that barrier first, so that it polls for a short while only.
+#ifndef FK_FLASH_EARLY
+#define FK_FLASH_EARLY 0
+#endif
 #ifndef FK_FLASH_LOADER_SPIN
 #define FK_FLASH_LOADER_SPIN 1
 #endif
@@ -202,6 +211,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const StallSite site{status, stop_flag, 0, kWaitBudgetCycles, true, FK_FLASH_NAP_NS, FK_FLASH_GAP};
     // The loader runs slots ahead of its consumers: it can afford to suspend.
     const StallSite calm{status, stop_flag, 0, kWaitBudgetCycles, FK_FLASH_LOADER_SPIN != 0, 0};
+    const StallSite doze{status, stop_flag, 0, kWaitBudgetCycles, false, 0};  // suspends in try_wait
     const StallSite issue{status, stop_flag, 0, kWaitBudgetCycles, true, FK_FLASH_MMA_NAP_NS, FK_FLASH_MMA_GAP};
 #ifdef FK_FLASH_TRACE
     // Development build: clock stamps of the first blocks of CTA (0, 0), after the status words.
@@ -298,6 +308,13 @@ __global__ void __launch_bounds__(kThreads, 1)
                 bool next_loaded = false;
                 for (uint32_t t = 0; live && t < kTiles; ++t) {
                     if (j < keys.blocks[t]) {
+#if FK_FLASH_EARLY
+                        // Sleep until the softmax warps are part-way through this block, then poll.
+                        if (!mbar_wait(p_soon + 8 * t, j & 1u, doze, kStallMmaP, j)) {
+                            live = false;
+                            break;
+                        }
+#endif
                         if (!mbar_wait(p_ready + 8 * t, j & 1u, issue, kStallMmaP, j)) {
                             live = false;
                             break;
@@ -425,6 +442,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
                 if (warp == 0) trace(t, j, 2);
 
+#if FK_FLASH_EARLY == 1
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_soon + 8 * t);
+#endif
                 const float shift = row_max[t] * scale_log2;
                 const float2 scale2 = make_float2(scale_log2, scale_log2);
                 const float2 shift2 = make_float2(-shift, -shift);
@@ -461,6 +482,12 @@ __global__ void __launch_bounds__(kThreads, 1)
                         packed[i] = pack_bf16x2(p.x, p.y);
                     }
                     tmem_st_32x16(s_tmem + 32 * half + 16 * c, packed);
+#if FK_FLASH_EARLY == 2
+                    if (c == 0) {
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(p_soon + 8 * t);
+                    }
+#endif
                 }
                 row_sum[t] += ((sum_a.x + sum_b.x) + (sum_c.x + sum_d.x)) + ((sum_a.y + sum_b.y) + (sum_c.y + sum_d.y));
                 if (warp == 0) trace(t, j, 3);
