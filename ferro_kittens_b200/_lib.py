@@ -109,6 +109,9 @@ SIGNATURES = {
     "fk_groupnorm_tile": (c_int, [c_void_p, c_void_p, c_uint32, c_float, c_void_p, c_void_p]),
     "fk_wait_stream": (c_int, [c_void_p, c_uint32]),
     "fk_wait_event": (c_int, [c_void_p, c_uint32]),
+    "fk_launch_budget_ms": (c_uint32, []),
+    "fk_selftest_deadline": (c_int, [c_uint32, c_uint32]),
+    "fk_selftest_call_guard": (c_int, [c_int, c_uint32, POINTER(c_uint64), POINTER(c_uint64)]),
     "fk_status_check": (c_int, [c_void_p, c_void_p]),
     "fk_selftest_stall": (c_int, [c_void_p, c_void_p, c_uint32]),
 }
@@ -120,8 +123,7 @@ def library() -> ctypes.CDLL:
     """The loaded library; raises if it cannot be built or loaded."""
     global _library
     if _library is None:
-        if not LIBRARY.exists():
-            build_library()
+        build_library()  # returns at once when the library is newer than every source
         handle = ctypes.CDLL(str(LIBRARY))
         for name, (restype, argtypes) in SIGNATURES.items():
             function = getattr(handle, name)  # AttributeError if the symbol is missing

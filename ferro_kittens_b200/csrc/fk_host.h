@@ -4,6 +4,7 @@
 
 #include <cstdarg>
 #include <cstdint>
+#include <mutex>
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -28,6 +29,14 @@ int scratch(int slot, size_t bytes, void** out);
 
 /// 8 status words per device for the host-buffer entry points.
 int scratch_status(uint32_t** out);
+
+/// Everything queued on `stream` has completed, or FK_ERR_TIMEOUT past the launch budget
+/// (`fk_launch_budget_ms`): the library's replacement for cudaStreamSynchronize.
+int wait_stream(cudaStream_t stream);
+
+/// One lock per device, held for the whole of a host-buffer entry point: those calls share
+/// the device's staging buffers, streams, events and status words.
+std::mutex& device_call_guard(int device);
 
 /// What a launch needs to know about the current device, asked of the runtime once per device:
 /// a launch of a few microseconds must not pay several attribute queries each time.

@@ -114,9 +114,6 @@ struct StallSite {
     uint32_t peer_stop;      // shared::cluster address of the peer's flag, 0 if none
     long long budget = kWaitBudgetCycles;
     bool spin = false;       // poll with test_wait instead of suspending in try_wait
-    uint32_t nap = 0;        // when polling: nanoseconds to sleep between probes (0 = none), so that
-                             // the probes do not take issue slots from the warps being waited for
-    uint32_t gap = 0;        // when polling: cycles to idle on the clock register between probes
 };
 
 /// The non-suspending probe. A thread suspended in try_wait takes a few hundred cycles to come back
@@ -146,12 +143,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const S
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 16; ++i) {
-            if (site.spin && site.nap) __nanosleep(site.nap);
-            if (site.spin && site.gap) {
-                const long long from = clock64();
-                while (clock64() - from < site.gap) {
-                }
-            }
             if (site.spin ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
         }
         if (*site.stop) return false;
@@ -374,58 +365,14 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
 /// 1 in exactly one lane of a converged warp, 0 in the others. Use it as a BRANCH around the
 /// whole issuing role (`if (elect_one()) { waits, MMAs, commits }`): the compiler then knows the
 /// region runs in a single thread and emits the tight issue sequence -- 23 cycles of the thread's
-/// own instructions per tcgen05.mma, measured, against 71 under `if (lane == 0)` or under a
-/// lane-0 predicate, which it cannot tell from arbitrary divergence. Do not use the flag as a
-/// predicate next to other warp-level operations (shuffles, lane-0 waits): that form stalled a
-/// microbenchmark's bounded wait and faulted once in a kernel.
+/// own instructions per tcgen05.mma, measured, against 71 under `if (lane == 0)`, which it cannot
+/// tell from arbitrary divergence. The waits, the MMAs and their commits must all sit inside the
+/// one branch: tcgen05.commit tracks the MMAs issued by the thread that executes it, so a commit
+/// executed by any other lane arrives at once, before the MMAs it was meant to cover have retired.
 __device__ __forceinline__ uint32_t elect_one() {
     uint32_t flag;
     asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(flag));
     return flag;
-}
-
-// Predicated forms: every lane executes the instruction stream and the lane whose `leader` is
-// non-zero issues (inside an elected single-thread region `leader` is simply 1).
-template <int CTA_GROUP>
-__device__ __forceinline__ void mma_ss_if(uint32_t leader, uint32_t d_tmem, uint64_t a_desc,
-                                          uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    if constexpr (CTA_GROUP == 2)
-        asm volatile(
-            "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
-            "@q tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader)
-            : "memory");
-    else
-        asm volatile(
-            "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
-            "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader)
-            : "memory");
-}
-__device__ __forceinline__ void mma_ts_if(uint32_t leader, uint32_t d_tmem, uint32_t a_tmem,
-                                          uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
-        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader)
-        : "memory");
-}
-template <int CTA_GROUP>
-__device__ __forceinline__ void mma_commit_if(uint32_t leader, uint32_t cluster_bar) {
-    if constexpr (CTA_GROUP == 2)
-        asm volatile(
-            "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
-            "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(
-                cluster_bar),
-            "r"(leader)
-            : "memory");
-    else
-        asm volatile(
-            "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
-            "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(
-                cluster_bar),
-            "r"(leader)
-            : "memory");
 }
 
 /// Arrive on `cluster_bar` once every MMA this thread issued so far has retired.

@@ -11,12 +11,14 @@
 // 128-row query tiles and ping-pongs them, so the tensor core works on one
 // tile while the CUDA cores run the other's softmax.
 //
-//   warps 0-7   softmax, all eight on one query tile at a time, alternating tiles: warps w and
-//               w + 4 own the same 32 rows (tcgen05.ld 32x32b, one thread per row) and 64 key
-//               columns each, swap half-row maxima through shared memory, keep running max and
-//               sum in registers, write P back to tensor memory as bf16 over S, rescale the
-//               output accumulator in tensor memory only when the max moved by more than 2^8;
-//               final normalise, bf16 staging and TMA store.
+//   warps 0-7   softmax, one team of four warps per query tile (warps 0-3 tile 0, warps 4-7
+//               tile 1), one thread per row: tcgen05.ld 32x32b of the row's 128 scores, running
+//               max and sum in registers with no exchange between threads, P written back to
+//               tensor memory as bf16 over S and published in two halves so that P.V starts under
+//               the second half's exponentials; the output accumulator is rescaled in tensor
+//               memory only when the max moved by more than 2^8; final normalise, bf16 staging
+//               and TMA store. The two teams run independently, so one tile's exponentials
+//               overlap the other's waits, loads and maxima on every scheduler.
 //   warp 8      loader: Q once, then K(j), V(j) 128-key blocks through a ring of kSlots slots.
 //   warp 9      MMA issue: S_t = Q_t K(j)^T (8 x M128 N128 K16) and O_t += P_t V(j)
 //               (8 x M128 N128 K16, A from tensor memory), interleaved across the two tiles.
@@ -24,6 +26,8 @@
 // Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each; P_t
 // aliases the first 64 columns of S_t. Causal launches skip key blocks above
 // the diagonal and mask only the diagonal block. Every wait is bounded.
+
+#include <mutex>
 
 #include "fk_host.h"
 #include "fk_layout.h"
@@ -37,10 +41,23 @@ constexpr uint32_t kTiles = 2;        // query tiles per CTA
 constexpr uint32_t kBlockKeys = 128;  // keys per K/V block
 constexpr uint32_t kHead = 128;
 constexpr uint32_t kSlots = 5;        // K/V ring depth, one [128, 128] bf16 block per slot
-constexpr uint32_t kSoftmaxWarps = 4 * kTiles;
+constexpr uint32_t kTeamWarps = 4;    // softmax warps per query tile: 32 rows each, one thread per row
+constexpr uint32_t kSoftmaxWarps = kTeamWarps * kTiles;
 constexpr uint32_t kLoaderWarp = kSoftmaxWarps;
 constexpr uint32_t kMmaWarp = kSoftmaxWarps + 1;
-constexpr uint32_t kThreads = (kSoftmaxWarps + 2) * 32;
+// Three warpgroups: the two softmax teams, and one that holds the loader and the MMA warp (its
+// other two warps idle). Registers are allocated per warpgroup, so the launch gives every thread
+// kLaunchRegisters and the roles rebalance at once: a softmax thread holds its row's 128 scores
+// and takes kSoftmaxRegisters, the third warpgroup keeps kServiceRegisters.
+constexpr uint32_t kThreads = 3 * 128;
+constexpr uint32_t kLaunchRegisters = 168;
+constexpr uint32_t kSoftmaxRegisters = 208;
+constexpr uint32_t kServiceRegisters = 88;
+// setmaxnreg.inc waits until the pool holds the registers it asks for: the demands must fit what
+// the launch allocated, or the wait never ends.
+static_assert(kSoftmaxWarps * 32 * kSoftmaxRegisters + 128 * kServiceRegisters <= kThreads * kLaunchRegisters,
+              "the warpgroups ask for more registers than the launch allocates");
+static_assert(kThreads * kLaunchRegisters <= 65536, "the CTA's registers exceed the SM's register file");
 constexpr uint32_t kSubtileBytes = 128 * 64 * 2;      // one [128, 64] bf16 SWIZZLE_128B subtile
 constexpr uint32_t kBlockBytes = 2 * kSubtileBytes;   // one [128, 128] bf16 tile
 constexpr uint32_t kTmemColumns = 512;
@@ -50,31 +67,31 @@ constexpr uint32_t kOutputColumn = 256;  // O_t at kOutputColumn + 128 t
 constexpr float kRescaleThreshold = 8.0f;
 // Of the 16 pairs of scores in a 32-column chunk, the pairs whose bit is set here take their
 // 2^x from a polynomial on the FMA pipe instead of the ex2 unit: at D = 128 a score tile costs
-// as many ex2-unit cycles as tensor cycles. Measured on B200 in back-to-back launches (the
-// power-capped regime) the best share is four pairs of sixteen: +5 % over none, causal and not
-// (1048 vs 996, 1061 vs 1007 TFLOP/s); eight of sixteen gives the gain back to the issue slots.
-// Before the MMA role moved to an elected thread and the waits to polling the best share was two.
+// as many ex2-unit cycles as tensor cycles.
 #ifndef FK_FLASH_POLY_MASK
 #define FK_FLASH_POLY_MASK 0x1111u
 #endif
 constexpr uint32_t kPolyMask = FK_FLASH_POLY_MASK;
+// P is published in two halves of 64 keys: the first four P.V MMAs of a block are issued while
+// the team is still exponentiating the second half.
+#ifndef FK_FLASH_SPLIT
+#define FK_FLASH_SPLIT 1
+#endif
+constexpr bool kSplitPublish = FK_FLASH_SPLIT != 0;
 
 struct Plan {
-    SharedPlan q, kv, swap, q_full, kv_full, kv_empty, s_full, p_ready, p_soon, o_done, pair, tmem_slot, stop,
-        end;
+    SharedPlan q, kv, q_full, kv_full, kv_empty, s_full, p_half, p_ready, o_done, tmem_slot, stop, end;
     constexpr Plan()
         : q(SharedPlan{}.tile_ring(kTileRows, kHead, 2, kTiles)),
           kv(q.tile_ring(kBlockKeys, kHead, 2, kSlots)),
-          swap(kv.reserve(2 * 2 * kTileRows * 4, 16)),  // half-row maxima / sums, two buffers
-          q_full(swap.semaphore()),
+          q_full(kv.semaphore()),
           kv_full(q_full.semaphores(kSlots)),
           kv_empty(kv_full.semaphores(kSlots)),
           s_full(kv_empty.semaphores(kTiles)),
-          p_ready(s_full.semaphores(kTiles)),
-          p_soon(p_ready.semaphores(kTiles)),
-          o_done(p_soon.semaphores(kTiles)),
-          pair(o_done.semaphores(4)),
-          tmem_slot(pair.tmem_slot()),
+          p_half(s_full.semaphores(kTiles)),
+          p_ready(p_half.semaphores(kTiles)),
+          o_done(p_ready.semaphores(kTiles)),
+          tmem_slot(o_done.tmem_slot()),
           stop(tmem_slot.word()),
           end(stop) {}
 };
@@ -92,7 +109,6 @@ enum StallCode : uint32_t {
     kStallMmaP = 0x204,
     kStallSoftmaxS = 0x205,
     kStallSoftmaxO = 0x206,
-    kStallSibling = 0x20a,
     kMisaligned = 0x2ff,
 };
 
@@ -127,9 +143,8 @@ __global__ void __launch_bounds__(kThreads, 1)
                          float* __restrict__ lse, uint32_t seq, float scale, uint32_t causal,
                          uint32_t* status) {
     extern __shared__ __align__(1024) uint8_t dynamic_shared[];
-    const uint32_t raw = smem_u32(dynamic_shared);
-    const uint32_t base = raw;
-    if (raw & (kBaseAlign - 1)) {
+    const uint32_t base = smem_u32(dynamic_shared);
+    if (base & (kBaseAlign - 1)) {
         if (threadIdx.x == 0 && status) atomicCAS(status, 0u, static_cast<uint32_t>(kMisaligned));
         return;
     }
@@ -140,13 +155,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t kv_full = base + kPlan.kv_full.at;
     const uint32_t kv_empty = base + kPlan.kv_empty.at;
     const uint32_t s_full = base + kPlan.s_full.at;
+    const uint32_t p_half = base + kPlan.p_half.at;
     const uint32_t p_ready = base + kPlan.p_ready.at;
-    const uint32_t p_soon = base + kPlan.p_soon.at;
     const uint32_t o_done = base + kPlan.o_done.at;
     const uint32_t slot = base + kPlan.tmem_slot.at;
-    volatile uint32_t* stop_flag =
-        reinterpret_cast<volatile uint32_t*>(dynamic_shared + (base + kPlan.stop.at - raw));
-    volatile uint32_t* slot_ptr = reinterpret_cast<volatile uint32_t*>(dynamic_shared + (slot - raw));
+    volatile uint32_t* stop_flag = reinterpret_cast<volatile uint32_t*>(dynamic_shared + kPlan.stop.at);
+    volatile uint32_t* slot_ptr = reinterpret_cast<volatile uint32_t*>(dynamic_shared + kPlan.tmem_slot.at);
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
@@ -164,12 +178,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         for (uint32_t t = 0; t < kTiles; ++t) {
             mbar_init(s_full + 8 * t, 1);
-            mbar_init(p_ready + 8 * t, kSoftmaxWarps);
-            mbar_init(p_soon + 8 * t, kSoftmaxWarps);
+            mbar_init(p_half + 8 * t, kTeamWarps);
+            mbar_init(p_ready + 8 * t, kTeamWarps);
             mbar_init(o_done + 8 * t, 1);
         }
-        for (uint32_t quadrant = 0; quadrant < 4; ++quadrant)
-            mbar_init(base + kPlan.pair.at + 8 * quadrant, 2);
         *stop_flag = 0;
         fence_mbarrier_init();
         prefetch_tensormap(&q_map);
@@ -186,44 +198,16 @@ __global__ void __launch_bounds__(kThreads, 1)
     tc_fence_after_sync();
     const uint32_t tmem = *slot_ptr;
 
-    // Every role here sits on the tile's dependency chain: poll, do not suspend.
-// 0: the MMA thread polls `p_ready` from the moment it has nothing else to issue. 1 / 2: the softmax
-// warps also arrive on `p_soon` before their exponentials / after the first half of them, and the MMA
-// thread suspends on that barrier first, so that it polls for a short while only.
-#ifndef FK_FLASH_EARLY
-#define FK_FLASH_EARLY 0
-#endif
-#ifndef FK_FLASH_LOADER_SPIN
-#define FK_FLASH_LOADER_SPIN 1
-#endif
-#ifndef FK_FLASH_NAP_NS
-#define FK_FLASH_NAP_NS 0
-#endif
-#ifndef FK_FLASH_GAP
-#define FK_FLASH_GAP 0
-#endif
-#ifndef FK_FLASH_MMA_GAP
-#define FK_FLASH_MMA_GAP FK_FLASH_GAP
-#endif
-#ifndef FK_FLASH_MMA_NAP_NS
-#define FK_FLASH_MMA_NAP_NS FK_FLASH_NAP_NS
-#endif
-    const StallSite site{status, stop_flag, 0, kWaitBudgetCycles, true, FK_FLASH_NAP_NS, FK_FLASH_GAP};
-    // The loader runs slots ahead of its consumers: it can afford to suspend.
-    const StallSite calm{status, stop_flag, 0, kWaitBudgetCycles, FK_FLASH_LOADER_SPIN != 0, 0};
-    const StallSite doze{status, stop_flag, 0, kWaitBudgetCycles, false, 0};  // suspends in try_wait
-    const StallSite issue{status, stop_flag, 0, kWaitBudgetCycles, true, FK_FLASH_MMA_NAP_NS, FK_FLASH_MMA_GAP};
-#ifdef FK_FLASH_TRACE
-    // Development build: clock stamps of the first blocks of CTA (0, 0), after the status words.
-    auto trace = [&](uint32_t role, uint32_t block, uint32_t point) {
-        if (blockIdx.x == 0 && blockIdx.y == 0 && block < 24 && lane == 0)
-            reinterpret_cast<long long*>(status + 4)[(role * 24 + block) * 6 + point] = clock64();
-    };
-#else
-    auto trace = [](uint32_t, uint32_t, uint32_t) {};
-#endif
+    // Every role here sits on a tile's dependency chain S -> softmax -> P -> P.V -> Q.K^T -> S:
+    // a thread suspended in try_wait comes back a few hundred cycles after the phase completes,
+    // so the roles poll instead (measured: +2.5 to +3.8 %).
+    const StallSite site{status, stop_flag, 0, kWaitBudgetCycles, true};
 
-    if (warp == kLoaderWarp) {
+    // The rebalancing sits inside the role branches: ptxas budgets every instruction reachable
+    // from a setmaxnreg by its count, so the two regions must not share code before the teardown.
+    if (warp >= kSoftmaxWarps) {
+      setmaxnreg_dec<kServiceRegisters>();
+      if (warp == kLoaderWarp) {
         // ------------------------------------------------ loader
         if (lane == 0) {
             uint32_t q_bytes = 0;
@@ -240,7 +224,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (uint32_t fill = 0; fill < 2 * keys.most; ++fill) {
                 const uint32_t s = fill % kSlots;
                 const uint32_t parity = (fill / kSlots) & 1u;
-                if (!mbar_wait(kv_empty + 8 * s, parity ^ 1u, calm, kStallLoader, fill)) break;
+                if (!mbar_wait(kv_empty + 8 * s, parity ^ 1u, site, kStallLoader, fill)) break;
                 mbar_arrive_expect_tx(kv_full + 8 * s, kBlockBytes);
                 const CUtensorMap* map = (fill & 1u) ? &v_map : &k_map;
                 const int row = static_cast<int>(kBlockKeys * (fill >> 1));
@@ -250,14 +234,11 @@ __global__ void __launch_bounds__(kThreads, 1)
                                 kv_full + 8 * s);
             }
         }
-    } else if (warp == kMmaWarp) {
+      } else if (warp == kMmaWarp) {
         // ------------------------------------------------ MMA issue
-#ifndef FK_FLASH_ISSUE_ELECT
-#define FK_FLASH_ISSUE_ELECT 1
-#endif
-        // One thread issues. Chosen by elect.sync the compiler knows the region runs in a single
-        // thread (see the note at elect_one); chosen as lane 0 it does not.
-        if (FK_FLASH_ISSUE_ELECT ? elect_one() != 0 : lane == 0) {
+        // One thread issues, chosen by elect.sync: the compiler then knows the region runs in a
+        // single thread (see the note at elect_one); chosen as lane 0 it does not.
+        if (elect_one() != 0) {
             constexpr uint32_t idesc_qk = instruction_descriptor(kTileRows, kBlockKeys, false, false);
             constexpr uint32_t idesc_pv = instruction_descriptor(kTileRows, kHead, false, true);
 
@@ -275,23 +256,24 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
                 mma_commit<1>(s_full + 8 * t);
             };
-            // O_t (+)= P_t . V over 128 keys: P from tensor memory (8 columns per K=16 chunk),
-            // V MN-major: 16 key rows per chunk, the second 64 head columns one subtile on.
-            auto output = [&](uint32_t t, uint32_t v_slot, bool accumulate) {
+            // O_t (+)= P_t . V over keys [16 first, 16 last) of the block: P from tensor memory
+            // (8 columns per K=16 chunk), V MN-major: 16 key rows per chunk, the second 64 head
+            // columns one subtile on.
+            auto output = [&](uint32_t t, uint32_t v_slot, bool accumulate, uint32_t first, uint32_t last) {
                 const uint32_t v_base = kv_ring + v_slot * kBlockBytes;
 #pragma unroll
-                for (uint32_t chunk = 0; chunk < kBlockKeys / 16; ++chunk)
+                for (uint32_t chunk = first; chunk < last; ++chunk)
                     mma_ts(tmem + kOutputColumn + kHead * t,
                            tmem + kScoreColumn + kBlockKeys * t + 8 * chunk,
                            operand_descriptor(v_base + chunk * kMnMajorChunkBytes, kSubtileBytes),
                            idesc_pv, accumulate || chunk != 0);
-                mma_commit<1>(o_done + 8 * t);
             };
+            constexpr uint32_t kChunks = kBlockKeys / 16;
 
-            bool live = mbar_wait(q_full, 0, issue, kStallMmaQ, 0);
+            bool live = mbar_wait(q_full, 0, site, kStallMmaQ, 0);
             if (live) {
                 tc_fence_after_sync();
-                live = mbar_wait(kv_full + 0, 0, issue, kStallMmaKv, 0);
+                live = mbar_wait(kv_full + 0, 0, site, kStallMmaKv, 0);
             }
             if (live) {
                 tc_fence_after_sync();
@@ -303,25 +285,26 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const uint32_t v_use = 2 * j + 1, k_use = 2 * j + 2;
                 const uint32_t v_slot = v_use % kSlots, k_slot = k_use % kSlots;
                 const bool more = j + 1 < keys.most;
-                if (!mbar_wait(kv_full + 8 * v_slot, (v_use / kSlots) & 1u, issue, kStallMmaKv, v_use))
+                if (!mbar_wait(kv_full + 8 * v_slot, (v_use / kSlots) & 1u, site, kStallMmaKv, v_use))
                     break;
                 bool next_loaded = false;
                 for (uint32_t t = 0; live && t < kTiles; ++t) {
                     if (j < keys.blocks[t]) {
-#if FK_FLASH_EARLY
-                        // Sleep until the softmax warps are part-way through this block, then poll.
-                        if (!mbar_wait(p_soon + 8 * t, j & 1u, doze, kStallMmaP, j)) {
-                            live = false;
-                            break;
+                        if (kSplitPublish) {
+                            if (!mbar_wait(p_half + 8 * t, j & 1u, site, kStallMmaP, j)) {
+                                live = false;
+                                break;
+                            }
+                            tc_fence_after_sync();
+                            output(t, v_slot, j != 0, 0, kChunks / 2);
                         }
-#endif
-                        if (!mbar_wait(p_ready + 8 * t, j & 1u, issue, kStallMmaP, j)) {
+                        if (!mbar_wait(p_ready + 8 * t, j & 1u, site, kStallMmaP, j)) {
                             live = false;
                             break;
                         }
                         tc_fence_after_sync();
-                        trace(2, j, 2 * t);
-                        output(t, v_slot, j != 0);
+                        output(t, v_slot, j != 0, kSplitPublish ? kChunks / 2 : 0, kChunks);
+                        mma_commit<1>(o_done + 8 * t);
                     }
                     if (j + 1 < keys.blocks[t]) {
                         if (!next_loaded) {
@@ -333,206 +316,160 @@ __global__ void __launch_bounds__(kThreads, 1)
                             tc_fence_after_sync();
                             next_loaded = true;
                         }
-                        trace(2, j, 4 + t);
                         scores(t, k_slot);
                     }
-                    trace(2, j, 2 * t + 1);
                 }
                 if (!live) break;
                 mma_commit<1>(kv_empty + 8 * v_slot);
                 if (more) mma_commit<1>(kv_empty + 8 * k_slot);
             }
         }
+      }
     } else {
+        setmaxnreg_inc<kSoftmaxRegisters>();
         // ------------------------------------------------ softmax, correction, epilogue
-        // All eight warps work on one query tile at a time, alternating tiles: warps 0-3 own
-        // key columns 0-63 of a score block and warps 4-7 columns 64-127, so the two warps
-        // that share a scheduler (and its ex2 unit) overlap one's exponentials with the
-        // other's FMA-pipe work. Two sibling warps own the same 32 rows and swap half-row
-        // maxima through shared memory under a two-arrival mbarrier (a bounded wait).
-        const uint32_t half = warp >> 2;         // which 64 key columns / 64 head columns
-        const uint32_t quadrant = warp & 3u;     // tensor-memory lanes this warp may touch
+        // One team of four warps per query tile, one thread per row: no value ever crosses
+        // threads. The two teams share the four schedulers (warps w and w + 4 sit on the same
+        // one) and are in different phases of their tiles, so one team's exponentials run while
+        // the other waits for its next S, loads it and finds its maxima.
+        const uint32_t t = warp / kTeamWarps;       // query tile of this team
+        const uint32_t quadrant = warp & 3u;        // tensor-memory lanes this warp may touch
         const uint32_t row = 32 * quadrant + lane;  // row of the tile this thread owns
+        const uint32_t blocks = keys.blocks[t];
         const uint32_t lane_base = (32 * quadrant) << 16;
+        const uint32_t s_tmem = tmem + lane_base + kScoreColumn + kBlockKeys * t;
+        const uint32_t o_tmem = tmem + lane_base + kOutputColumn + kHead * t;
         const float scale_log2 = scale * 1.4426950408889634f;
-        float* const swap = reinterpret_cast<float*>(dynamic_shared + (base + kPlan.swap.at - raw));
-        const uint32_t pair_bar = base + kPlan.pair.at + 8 * quadrant;
+        const float2 scale2 = make_float2(scale_log2, scale_log2);
 
-        float row_max[kTiles] = {-INFINITY, -INFINITY};  // raw score units, same in both siblings
-        float row_sum[kTiles] = {0.0f, 0.0f};            // this thread's half of the row only
-        uint32_t step = 0;
-        bool live = true;
-        // Rendezvous of the two warps that own the same rows, called after `step` was advanced:
-        // a two-arrival mbarrier, so that this wait is bounded like every other one.
-        const auto sibling_sync = [&]() {
-            __syncwarp();
-            if (lane == 0) mbar_arrive(pair_bar);
-            if (!mbar_wait(pair_bar, (step - 1) & 1u, site, kStallSibling, step)) live = false;
-        };
+        float row_max = -INFINITY;  // raw score units
+        float row_sum = 0.0f;
+        bool live = blocks != 0;
 
-        for (uint32_t j = 0; live && j < keys.most; ++j) {
-#pragma unroll
-            for (uint32_t t = 0; t < kTiles; ++t) {
-                if (!live || j >= keys.blocks[t]) continue;
-                const uint32_t s_tmem = tmem + lane_base + kScoreColumn + kBlockKeys * t;
-                const uint32_t o_tmem = tmem + lane_base + kOutputColumn + kHead * t + 64 * half;
-                if (!mbar_wait(s_full + 8 * t, j & 1u, site, kStallSoftmaxS, j)) {
-                    live = false;
-                    continue;
-                }
-                tc_fence_after_sync();
-                if (warp == 0) trace(t, j, 0);
-                uint32_t raw_s[2][32];
-                tmem_ld_32x32(s_tmem + 64 * half, raw_s[0]);
-                tmem_ld_32x32(s_tmem + 64 * half + 32, raw_s[1]);
-                tmem_wait_ld();
-                if (warp == 0) trace(t, j, 1);
-
-                if (causal && j + 1 == keys.blocks[t]) {
-                    // Diagonal block: key (128 j + c) is visible to query (tile start + row) iff c <= row.
-#pragma unroll
-                    for (uint32_t c = 0; c < 2; ++c)
-#pragma unroll
-                        for (uint32_t i = 0; i < 32; ++i)
-                            if (64 * half + 32 * c + i > row) raw_s[c][i] = 0xff800000u;  // -inf
-                }
-
-                float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
-#pragma unroll
-                for (uint32_t i = 0; i < 8; ++i) {
-                    m0 = max3(m0, __uint_as_float(raw_s[0][4 * i]), __uint_as_float(raw_s[0][4 * i + 1]));
-                    m1 = max3(m1, __uint_as_float(raw_s[0][4 * i + 2]), __uint_as_float(raw_s[0][4 * i + 3]));
-                    m2 = max3(m2, __uint_as_float(raw_s[1][4 * i]), __uint_as_float(raw_s[1][4 * i + 1]));
-                    m3 = max3(m3, __uint_as_float(raw_s[1][4 * i + 2]), __uint_as_float(raw_s[1][4 * i + 3]));
-                }
-                // Swap half-row maxima with the sibling warp. Two buffers by step parity: a warp
-                // cannot be two steps ahead of its sibling, which every step's barrier holds.
-                float* const mine = swap + ((step & 1u) * 2 + half) * kTileRows + row;
-                float* const theirs = swap + ((step & 1u) * 2 + (half ^ 1u)) * kTileRows + row;
-                ++step;
-                *mine = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-                sibling_sync();
-                const float block_max = fmaxf(*mine, *theirs);
-                const float new_max = fmaxf(row_max[t], block_max);
-                const bool moved = (new_max - row_max[t]) * scale_log2 > kRescaleThreshold;
-                if (__any_sync(0xffffffffu, moved)) {
-                    // Refresh this warp's maxima; rows whose max did not move scale by 1. Both
-                    // siblings hold the same rows and the same maxima, so both take this branch.
-                    const float factor = ex2_approx((row_max[t] - new_max) * scale_log2);
-                    if (j > 0) {
-                        if (!mbar_wait(o_done + 8 * t, (j - 1) & 1u, site, kStallSoftmaxO, j)) {
-                            live = false;
-                            continue;
-                        }
-                        tc_fence_after_sync();
-#pragma unroll 1
-                        for (uint32_t c = 0; c < 2; ++c) {
-                            uint32_t o[32];
-                            tmem_ld_32x32(o_tmem + 32 * c, o);
-                            tmem_wait_ld();
-#pragma unroll
-                            for (uint32_t i = 0; i < 32; ++i)
-                                o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
-                            tmem_st_32x32(o_tmem + 32 * c, o);
-                        }
-                        tmem_wait_st();
-                    }
-                    row_sum[t] *= factor;
-                    row_max[t] = new_max;
-                }
-                if (warp == 0) trace(t, j, 2);
-
-#if FK_FLASH_EARLY == 1
-                __syncwarp();
-                if (lane == 0) mbar_arrive(p_soon + 8 * t);
-#endif
-                const float shift = row_max[t] * scale_log2;
-                const float2 scale2 = make_float2(scale_log2, scale_log2);
-                const float2 shift2 = make_float2(-shift, -shift);
-                // Four independent sum chains: with two, the compiler recycles the registers the
-                // exponentials land in so tightly that every ex2 waits out the one before it and
-                // the loop runs at half the unit's rate (measured in isolation: 1219 cycles per 64
-                // columns for two warps on a scheduler against 1080 with four chains, bound 1024).
-                float2 sum_a = make_float2(0.0f, 0.0f), sum_b = make_float2(0.0f, 0.0f);
-                float2 sum_c = make_float2(0.0f, 0.0f), sum_d = make_float2(0.0f, 0.0f);
-#pragma unroll
-                for (uint32_t c = 0; c < 2; ++c) {
-                    // 32 keys -> 16 packed bf16 pairs, written over S columns both siblings have read.
-                    uint32_t packed[16];
-#pragma unroll
-                    for (uint32_t i = 0; i < 16; ++i) {
-                        const float2 x = __ffma2_rn(make_float2(__uint_as_float(raw_s[c][2 * i]),
-                                                                __uint_as_float(raw_s[c][2 * i + 1])),
-                                                    scale2, shift2);
-                        float2 p;
-                        if ((kPolyMask >> i) & 1u) {
-                            p = exp2_pair_fma(x);
-                        } else {
-                            p.x = ex2_approx(x.x);
-                            p.y = ex2_approx(x.y);
-                        }
-                        if ((i & 3u) == 0)
-                            sum_a = __fadd2_rn(sum_a, p);
-                        else if ((i & 3u) == 1)
-                            sum_b = __fadd2_rn(sum_b, p);
-                        else if ((i & 3u) == 2)
-                            sum_c = __fadd2_rn(sum_c, p);
-                        else
-                            sum_d = __fadd2_rn(sum_d, p);
-                        packed[i] = pack_bf16x2(p.x, p.y);
-                    }
-                    tmem_st_32x16(s_tmem + 32 * half + 16 * c, packed);
-#if FK_FLASH_EARLY == 2
-                    if (c == 0) {
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(p_soon + 8 * t);
-                    }
-#endif
-                }
-                row_sum[t] += ((sum_a.x + sum_b.x) + (sum_c.x + sum_d.x)) + ((sum_a.y + sum_b.y) + (sum_c.y + sum_d.y));
-                if (warp == 0) trace(t, j, 3);
-                tmem_wait_st();
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(p_ready + 8 * t);
-                if (warp == 0) trace(t, j, 4);
-                trace(3 + warp, j, t);  // every softmax warp's arrival, per tile
-            }
-        }
-
-#pragma unroll
-        for (uint32_t t = 0; t < kTiles; ++t) {
-            const uint32_t blocks = keys.blocks[t];
-            if (!live || blocks == 0) continue;
-            const uint32_t o_tmem = tmem + lane_base + kOutputColumn + kHead * t + 64 * half;
-            if (!mbar_wait(o_done + 8 * t, (blocks - 1) & 1u, site, kStallSoftmaxO, blocks)) {
+        for (uint32_t j = 0; live && j < blocks; ++j) {
+            if (!mbar_wait(s_full + 8 * t, j & 1u, site, kStallSoftmaxS, j)) {
                 live = false;
-                continue;
+                break;
             }
             tc_fence_after_sync();
-            // The row sum is the two siblings' halves together.
-            float* const mine = swap + ((step & 1u) * 2 + half) * kTileRows + row;
-            float* const theirs = swap + ((step & 1u) * 2 + (half ^ 1u)) * kTileRows + row;
-            ++step;
-            *mine = row_sum[t];
-            sibling_sync();
-            const float total = *mine + *theirs;
-            const float inverse = 1.0f / total;
-            const uint32_t q_index = q_row0 + kTileRows * t + row;
-            if (lse && half == 0)
-                lse[static_cast<size_t>(plane) * seq + q_index] =
-                    (row_max[t] * scale_log2 + lg2_approx(total)) * 0.6931471805599453f;
-            // Q_t's shared tile is dead once the last MMA retired: it stages the output. This
-            // warp owns rows [32 q, 32 q + 32) of the [128, 64] subtile of head columns 64 half...
-            const uint32_t subtile = q_tiles + t * kBlockBytes + half * kSubtileBytes;
+            uint32_t raw_s[4][32];
+#pragma unroll
+            for (uint32_t c = 0; c < 4; ++c) tmem_ld_32x32(s_tmem + 32 * c, raw_s[c]);
+            tmem_wait_ld();
+
+            if (causal && j + 1 == blocks) {
+                // Diagonal block: key (128 j + c) is visible to query (tile start + row) iff c <= row.
+#pragma unroll
+                for (uint32_t c = 0; c < 4; ++c)
+#pragma unroll
+                    for (uint32_t i = 0; i < 32; ++i)
+                        if (32 * c + i > row) raw_s[c][i] = 0xff800000u;  // -inf
+            }
+
+            float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+            for (uint32_t i = 0; i < 16; ++i) {
+                m0 = max3(m0, __uint_as_float(raw_s[0][2 * i]), __uint_as_float(raw_s[0][2 * i + 1]));
+                m1 = max3(m1, __uint_as_float(raw_s[1][2 * i]), __uint_as_float(raw_s[1][2 * i + 1]));
+                m2 = max3(m2, __uint_as_float(raw_s[2][2 * i]), __uint_as_float(raw_s[2][2 * i + 1]));
+                m3 = max3(m3, __uint_as_float(raw_s[3][2 * i]), __uint_as_float(raw_s[3][2 * i + 1]));
+            }
+            const float new_max = max3(row_max, fmaxf(m0, m1), fmaxf(m2, m3));
+            const bool moved = (new_max - row_max) * scale_log2 > kRescaleThreshold;
+            if (__any_sync(0xffffffffu, moved)) {
+                // Refresh this warp's maxima; rows whose max did not move scale by 1. A stale
+                // max is used consistently for P, the row sum and the log-sum-exp, so the result
+                // does not depend on when the refresh happens.
+                const float factor = ex2_approx((row_max - new_max) * scale_log2);
+                if (j > 0) {
+                    if (!mbar_wait(o_done + 8 * t, (j - 1) & 1u, site, kStallSoftmaxO, j)) {
+                        live = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
 #pragma unroll 1
-            for (uint32_t c = 0; c < 2; ++c) {
+                    for (uint32_t c = 0; c < 4; ++c) {
+                        uint32_t o[32];
+                        tmem_ld_32x32(o_tmem + 32 * c, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (uint32_t i = 0; i < 32; ++i)
+                            o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+                        tmem_st_32x32(o_tmem + 32 * c, o);
+                    }
+                    tmem_wait_st();
+                }
+                row_sum *= factor;
+                row_max = new_max;
+            }
+
+            const float shift = row_max * scale_log2;
+            const float2 shift2 = make_float2(-shift, -shift);
+            // Four independent sum chains: with two, the compiler recycles the registers the
+            // exponentials land in so tightly that every ex2 waits out the one before it and
+            // the loop runs at half the unit's rate.
+            float2 sum_a = make_float2(0.0f, 0.0f), sum_b = make_float2(0.0f, 0.0f);
+            float2 sum_c = make_float2(0.0f, 0.0f), sum_d = make_float2(0.0f, 0.0f);
+#pragma unroll
+            for (uint32_t c = 0; c < 4; ++c) {
+                // 32 keys -> 16 packed bf16 pairs, written over S columns this thread has read.
+                uint32_t packed[16];
+#pragma unroll
+                for (uint32_t i = 0; i < 16; ++i) {
+                    const float2 x = __ffma2_rn(make_float2(__uint_as_float(raw_s[c][2 * i]),
+                                                            __uint_as_float(raw_s[c][2 * i + 1])),
+                                                scale2, shift2);
+                    float2 p;
+                    if ((kPolyMask >> i) & 1u) {
+                        p = exp2_pair_fma(x);
+                    } else {
+                        p.x = ex2_approx(x.x);
+                        p.y = ex2_approx(x.y);
+                    }
+                    if ((i & 3u) == 0)
+                        sum_a = __fadd2_rn(sum_a, p);
+                    else if ((i & 3u) == 1)
+                        sum_b = __fadd2_rn(sum_b, p);
+                    else if ((i & 3u) == 2)
+                        sum_c = __fadd2_rn(sum_c, p);
+                    else
+                        sum_d = __fadd2_rn(sum_d, p);
+                    packed[i] = pack_bf16x2(p.x, p.y);
+                }
+                tmem_st_32x16(s_tmem + 16 * c, packed);
+                if (kSplitPublish && c == 1) {
+                    tmem_wait_st();
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(p_half + 8 * t);
+                }
+            }
+            row_sum += ((sum_a.x + sum_b.x) + (sum_c.x + sum_d.x)) + ((sum_a.y + sum_b.y) + (sum_c.y + sum_d.y));
+            tmem_wait_st();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_ready + 8 * t);
+        }
+
+        if (live) live = mbar_wait(o_done + 8 * t, (blocks - 1) & 1u, site, kStallSoftmaxO, blocks);
+        if (live) {
+            tc_fence_after_sync();
+            const float inverse = 1.0f / row_sum;
+            const uint32_t q_index = q_row0 + kTileRows * t + row;
+            if (lse)
+                lse[static_cast<size_t>(plane) * seq + q_index] =
+                    (row_max * scale_log2 + lg2_approx(row_sum)) * 0.6931471805599453f;
+            // Q_t's shared tile is dead once the last MMA retired: it stages the output. This
+            // warp owns rows [32 q, 32 q + 32) of both [128, 64] subtiles.
+            const uint32_t stage = q_tiles + t * kBlockBytes;
+#pragma unroll 1
+            for (uint32_t c = 0; c < 4; ++c) {
                 uint32_t o[32];
                 tmem_ld_32x32(o_tmem + 32 * c, o);
                 tmem_wait_ld();
                 if (o_f32) {
                     float4* out = reinterpret_cast<float4*>(
-                        o_f32 + (static_cast<size_t>(plane) * seq + q_index) * kHead + 64 * half + 32 * c);
+                        o_f32 + (static_cast<size_t>(plane) * seq + q_index) * kHead + 32 * c);
 #pragma unroll
                     for (uint32_t i = 0; i < 8; ++i)
                         out[i] = make_float4(__uint_as_float(o[4 * i]) * inverse,
@@ -540,10 +477,11 @@ __global__ void __launch_bounds__(kThreads, 1)
                                              __uint_as_float(o[4 * i + 2]) * inverse,
                                              __uint_as_float(o[4 * i + 3]) * inverse);
                 } else {
+                    const uint32_t subtile = stage + (c / 2) * kSubtileBytes;
 #pragma unroll
                     for (uint32_t i = 0; i < 4; ++i) {
                         const uint32_t* v = o + 8 * i;
-                        st_shared_v4(subtile + swizzled_chunk_offset(row, 4 * c + i, 0),
+                        st_shared_v4(subtile + swizzled_chunk_offset(row, 4 * (c % 2) + i, 0),
                                      pack_bf16x2(__uint_as_float(v[0]) * inverse,
                                                  __uint_as_float(v[1]) * inverse),
                                      pack_bf16x2(__uint_as_float(v[2]) * inverse,
@@ -559,9 +497,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                 fence_proxy_async_shared();
                 __syncwarp();
                 if (lane == 0) {
-                    tma_store_3d(&o_map, subtile + 32 * quadrant * 128, static_cast<int>(64 * half),
-                                 static_cast<int>(q_row0 + kTileRows * t + 32 * quadrant),
-                                 static_cast<int>(plane));
+                    const int out_row = static_cast<int>(q_row0 + kTileRows * t + 32 * quadrant);
+                    for (uint32_t half = 0; half < 2; ++half)
+                        tma_store_3d(&o_map, stage + half * kSubtileBytes + 32 * quadrant * 128,
+                                     static_cast<int>(64 * half), out_row, static_cast<int>(plane));
                     tma_store_commit();
                 }
             }
@@ -571,6 +510,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     // ---------------------------------------------------- teardown
     if (*stop_flag) {
+        // A role gave up: let copies and MMAs already in flight land before shared and tensor
+        // memory are handed back.
         for (int i = 0; i < 256; ++i) __nanosleep(1000);
     }
     tc_fence_before_sync();
@@ -642,11 +583,20 @@ extern "C" int fk_flash_fwd(const void* q, const void* k, const void* v, void* o
                                device_status);
 }
 
+// One call at a time per device, like fk_gemm_bf16_host: the staging buffers and status words are
+// the device's, so the call holds the device's guard until nothing of it is in flight.
 extern "C" int fk_flash_fwd_host(const uint16_t* q_host, const uint16_t* k_host,
                                  const uint16_t* v_host, uint16_t* o_host, float* lse_host,
                                  uint32_t planes, uint32_t seq, float scale, int causal) {
     if (!q_host || !k_host || !v_host || !o_host)
         return fk_fail(FK_ERR_INVALID, "an operand pointer is null");
+    if (seq == 0 || seq % flash::kTileRows || planes == 0)
+        return fk_fail(FK_ERR_SHAPE,
+                       "%u queries x %u heads does not divide the %u queries a tile owns", seq,
+                       planes, flash::kTileRows);
+    int device = 0;
+    FK_CUDA(cudaGetDevice(&device));
+    std::lock_guard<std::mutex> call(device_call_guard(device));
     const size_t bytes = size_t(planes) * seq * flash::kHead * 2;
     const size_t lse_bytes = size_t(planes) * seq * 4;
     void *q = nullptr, *k = nullptr, *v = nullptr, *o = nullptr, *lse = nullptr;
@@ -659,14 +609,22 @@ extern "C" int fk_flash_fwd_host(const uint16_t* q_host, const uint16_t* k_host,
     if (status == FK_OK) status = scratch_status(&status_words);
     if (status != FK_OK) return status;
     cudaStream_t stream = nullptr;
-    FK_CUDA(cudaMemsetAsync(status_words, 0, 16, stream));
-    FK_CUDA(cudaMemcpyAsync(q, q_host, bytes, cudaMemcpyHostToDevice, stream));
-    FK_CUDA(cudaMemcpyAsync(k, k_host, bytes, cudaMemcpyHostToDevice, stream));
-    FK_CUDA(cudaMemcpyAsync(v, v_host, bytes, cudaMemcpyHostToDevice, stream));
-    status = fk_flash_fwd(q, k, v, o, nullptr, static_cast<float*>(lse), planes, seq, scale, causal,
-                          stream, status_words);
-    if (status != FK_OK) return status;
-    FK_CUDA(cudaMemcpyAsync(o_host, o, bytes, cudaMemcpyDeviceToHost, stream));
-    if (lse_host) FK_CUDA(cudaMemcpyAsync(lse_host, lse, lse_bytes, cudaMemcpyDeviceToHost, stream));
+    const auto enqueue = [&]() -> int {
+        FK_CUDA(cudaMemsetAsync(status_words, 0, 16, stream));
+        FK_CUDA(cudaMemcpyAsync(q, q_host, bytes, cudaMemcpyHostToDevice, stream));
+        FK_CUDA(cudaMemcpyAsync(k, k_host, bytes, cudaMemcpyHostToDevice, stream));
+        FK_CUDA(cudaMemcpyAsync(v, v_host, bytes, cudaMemcpyHostToDevice, stream));
+        const int launched = fk_flash_fwd(q, k, v, o, nullptr, static_cast<float*>(lse), planes, seq, scale,
+                                          causal, stream, status_words);
+        if (launched != FK_OK) return launched;
+        FK_CUDA(cudaMemcpyAsync(o_host, o, bytes, cudaMemcpyDeviceToHost, stream));
+        if (lse_host) FK_CUDA(cudaMemcpyAsync(lse_host, lse, lse_bytes, cudaMemcpyDeviceToHost, stream));
+        return FK_OK;
+    };
+    status = enqueue();
+    if (status != FK_OK) {
+        wait_stream(stream);  // no copy of this call may still be reading the caller's buffers
+        return status;
+    }
     return fk_status_check(status_words, stream);
 }

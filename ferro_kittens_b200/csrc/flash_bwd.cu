@@ -35,10 +35,6 @@
 #include "fk_layout.h"
 #include "fk_ptx.cuh"
 
-#ifndef FK_BWD_SPIN
-#define FK_BWD_SPIN 0
-#endif
-
 namespace fk {
 namespace flash_bwd {
 
@@ -217,18 +213,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *slot_ptr;
-    // Polling instead of suspending measured no better here (it pays in the forward).
-    const StallSite site{status, stop_flag, 0, kWaitBudgetCycles, FK_BWD_SPIN != 0};
-#ifdef FK_BWD_TRACE
-    // Development build: clock stamps of the first blocks of CTA (0, 0), after the status words
-    // (FK_BWD_TRACE=2: the key-block owners; 1: the query-block owners, whose launch comes second).
-    auto trace = [&](uint32_t role, uint32_t block, uint32_t point) {
-        if ((FK_BWD_TRACE == 2) == KV && blockIdx.x == 0 && blockIdx.y == 0 && block < 24 && lane == 0)
-            reinterpret_cast<long long*>(status + 8)[(role * 24 + block) * 4 + point] = clock64();
-    };
-#else
-    auto trace = [](uint32_t, uint32_t, uint32_t) {};
-#endif
+    // The waits suspend in try_wait: polling measured no better here (it pays in the forward).
+    const StallSite site{status, stop_flag, 0, kWaitBudgetCycles, false};
 
     if (warp == kLoaderWarp) {
         // ------------------------------------------------ loader: resident tiles, the x0 ring, the statistics
@@ -276,26 +262,15 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
     } else if (warp == kMmaWarp) {
         // ------------------------------------------------ MMA issue
-#ifndef FK_BWD_ISSUE_STYLE
-#define FK_BWD_ISSUE_STYLE 1
-#endif
-        // Style 0: the whole warp runs the code and lane 0 issues through predicated instructions.
-        // Style 1: one elected thread runs all of it, branches and waits included.
-        constexpr bool kElected = FK_BWD_ISSUE_STYLE == 1;
-        const uint32_t leader = kElected ? 1u : (lane == 0 ? 1u : 0u);
+        // One elected thread runs the whole role, waits, MMAs and commits: the compiler then knows the
+        // region is single-threaded and emits the tight issue sequence (see the note at elect_one).
         constexpr uint32_t idesc_ss = instruction_descriptor(kRows, kRows, false, false);
         constexpr uint32_t idesc_ts = instruction_descriptor(kRows, kHead, false, true);
-        if (!kElected || elect_one()) {
+        if (elect_one()) {
         auto wait = [&](uint32_t bar, uint32_t parity, uint32_t code, uint32_t detail) {
-            uint32_t ok = 1;
-            if (kElected) {
-                ok = mbar_wait(bar, parity, site, code, detail) ? 1u : 0u;
-            } else {
-                if (lane == 0) ok = mbar_wait(bar, parity, site, code, detail) ? 1u : 0u;
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-            }
+            const bool ok = mbar_wait(bar, parity, site, code, detail);
             if (ok) tc_fence_after_sync();
-            return ok != 0;
+            return ok;
         };
         // T = A . B^T over d = 128, both tiles K-major: two stacked [128, 64] subtiles, four K=16 chunks each.
         auto transposed_product = [&](uint32_t t_column, uint32_t a_tile, uint32_t b_tile) {
@@ -304,7 +279,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
             for (uint32_t chunk = 0; chunk < kHead / 16; ++chunk) {
                 const uint64_t step = ((chunk / 4) * kSubtileBytes + (chunk % 4) * kKMajorChunkBytes) >> 4;
-                mma_ss_if<1>(leader, tmem + t_column, a_desc + step, b_desc + step, idesc_ss, chunk != 0);
+                mma_ss<1>(tmem + t_column, a_desc + step, b_desc + step, idesc_ss, chunk != 0);
             }
         };
         // ACC (+)= A . B over the tile's 128 rows: A is the bf16 the element-wise warps left over T
@@ -314,7 +289,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             const uint64_t b_desc = operand_descriptor(b_tile, kSubtileBytes);
 #pragma unroll
             for (uint32_t chunk = 0; chunk < kRows / 16; ++chunk)
-                mma_ts_if(leader, tmem + acc_column,
+                mma_ts(tmem + acc_column,
                           tmem + t_column + kThreadColumns * (16 * chunk / kThreadColumns) + (16 * chunk % kThreadColumns) / 2,
                           b_desc + ((chunk * kMnMajorChunkBytes) >> 4), idesc_ts, (keep || chunk != 0) ? 1u : 0u);
         };
@@ -330,41 +305,37 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (live && count != 0) live = wait(full0, 0, kStallMmaStream, 0);
         if (live && count != 0) {
             transposed_product(kT1, resident, x0_of(0));  // S^T = K Q^T   |  S = Q K^T
-            mma_commit_if<1>(leader, t1_full);
+            mma_commit<1>(t1_full);
             live = wait(full1, 0, kStallMmaStream, 0);
         }
         if (live && count != 0) {
             transposed_product(kT2, resident + kTileBytes, x1_of(0));  // dP^T = V dO^T | dP = dO V^T
-            mma_commit_if<1>(leader, t2_full);
-            if (!KV) mma_commit_if<1>(leader, empty1);
+            mma_commit<1>(t2_full);
+            if (!KV) mma_commit<1>(empty1);
         }
         for (uint32_t n = 0; live && n < count; ++n) {
             const bool more = n + 1 < count;
             if (!wait(p_ready, n & 1u, kStallMmaP, n)) break;
-            trace(1, n, 0);
             if (KV) {
                 accumulate(kAcc0, kT1, x1_of(n), n != 0);  // dV += P^T dO
-                mma_commit_if<1>(leader, empty1 + 8 * (n % kSlots1));
+                mma_commit<1>(empty1 + 8 * (n % kSlots1));
             }
             if (more) {
                 if (!wait(full0 + 8 * ((n + 1) % kSlots0), ((n + 1) / kSlots0) & 1u, kStallMmaStream, n + 1)) break;
                 transposed_product(kT1, resident, x0_of(n + 1));
-                mma_commit_if<1>(leader, t1_full);
+                mma_commit<1>(t1_full);
             }
-            trace(1, n, 1);
             if (!wait(ds_ready, n & 1u, kStallMmaDs, n)) break;
-            trace(1, n, 2);
             accumulate(kAcc1, kT2, x0_of(n), n != 0);  // dK += dS^T Q  |  dQ += dS K
-            mma_commit_if<1>(leader, empty0 + 8 * (n % kSlots0));
+            mma_commit<1>(empty0 + 8 * (n % kSlots0));
             if (more) {
                 if (!wait(full1 + 8 * ((n + 1) % kSlots1), ((n + 1) / kSlots1) & 1u, kStallMmaStream, n + 1)) break;
                 transposed_product(kT2, resident + kTileBytes, x1_of(n + 1));
-                mma_commit_if<1>(leader, t2_full);
-                if (!KV) mma_commit_if<1>(leader, empty1 + 8 * ((n + 1) % kSlots1));
+                mma_commit<1>(t2_full);
+                if (!KV) mma_commit<1>(empty1 + 8 * ((n + 1) % kSlots1));
             }
-            trace(1, n, 3);
         }
-        mma_commit_if<1>(leader, acc_done);
+        mma_commit<1>(acc_done);
         }
         __syncwarp();
     } else if (warp < kElementWarps) {
@@ -392,7 +363,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                 break;
             }
             tc_fence_after_sync();
-            if (warp == 0) trace(0, n, 0);
             if (KV && !mbar_wait(stats_full + 8 * s, (n / kSlotsStats) & 1u, site, kStallElementT, n)) {
                 live = false;
                 break;
@@ -445,7 +415,6 @@ __global__ void __launch_bounds__(kThreads, 1)
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_ready);  // P is in place (KV), and S has been consumed
-            if (warp == 0) trace(0, n, 1);
 
             // ---- second half: dS from dP and the P still in registers, while the pipe runs dV and S(n+1)
             if (!mbar_wait(t2_full, n & 1u, site, kStallElementT2, n)) {
@@ -453,7 +422,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                 break;
             }
             tc_fence_after_sync();
-            if (warp == 0) trace(0, n, 2);
 #pragma unroll
             for (uint32_t c = 0; c < kChunks; ++c) {
                 uint32_t slope[32];
@@ -489,7 +457,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                 mbar_arrive(ds_ready);
                 if (KV) mbar_arrive(stats_empty + 8 * s);  // the block's statistics have been read
             }
-            if (warp == 0) trace(0, n, 3);
         }
 
         if (live && !mbar_wait(acc_done, 0, site, kStallElementAcc, count)) live = false;

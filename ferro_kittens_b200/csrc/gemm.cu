@@ -156,16 +156,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const uint32_t peer = rank ^ 1u;
-#ifdef FK_GEMM_TRACE
-    // Development build: clock stamps of the leader CTA of cluster 0, after the status words.
-    auto trace = [&](uint32_t point) {
-        if (blockIdx.x == 0 && lane == 0) reinterpret_cast<long long*>(status + 4)[point] = clock64();
-    };
-#else
-    auto trace = [](uint32_t) {};
-#endif
-    if (warp == 0) trace(0);
-
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
             mbar_init(full + 8 * s, 1);
@@ -186,7 +176,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     tc_fence_after_sync();
     if (warp == 1) tmem_relinquish<2>();
     const uint32_t tmem = *slot_ptr;
-    if (warp == 0) trace(1);
 
     const StallSite site{status, stop_flag, mapa(stop_addr, peer)};
 
@@ -206,12 +195,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 for (uint32_t k = 0; k < plan.k_blocks; ++k, ++fill) {
                     const uint32_t s = fill % kStages;
                     const uint32_t parity = (fill / kStages) & 1u;
-                    if (fill == 0) trace(12);
                     if (!mbar_wait(empty + 8 * s, parity ^ 1u, site, kStallProducer, fill)) {
                         live = false;
                         break;
                     }
-                    if (fill == 0) trace(13);
                     const uint32_t arrive_at = mapa(full + 8 * s, 0);
                     if (rank == 0) mbar_arrive_expect_tx(full + 8 * s, pair_bytes);
                     const int column = static_cast<int>(kBlockK * k);
@@ -221,20 +208,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                     if (item.halves == 2)
                         tma_load_2d_pair(a_ring + (s * kHalves + 1) * kATileBytes, &a_map, column,
                                          a_row + static_cast<int>(2 * kBlockM), arrive_at);
-                    if (k == 0) trace(2);
-                    if (k + 1 == plan.k_blocks) trace(3);
                 }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------ MMA issue (leader only)
-        // The issuing thread: lane 0, or the one elect.sync picks (1). The attention kernels gain
-        // from the latter; here an M256 N256 MMA occupies the pipe for 128 cycles and the thread's
-        // own cost per MMA does not show (1436 vs 1439 TFLOP/s), so the plain form stays.
-#ifndef FK_GEMM_ISSUE_ELECT
-#define FK_GEMM_ISSUE_ELECT 0
-#endif
-        if (rank == 0 && (FK_GEMM_ISSUE_ELECT ? elect_one() != 0 : lane == 0)) {
+        // One thread issues. An M256 N256 MMA occupies the pipe for 128 cycles, so the thread's
+        // own cost per MMA does not show here (lane 0 or an elected lane: 1436 vs 1439 TFLOP/s).
+        if (rank == 0 && lane == 0) {
             const uint32_t idesc = plan.idesc;
             uint32_t drain = 0, count = 0;
             bool live = true;
@@ -256,8 +237,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                         break;
                     }
                     tc_fence_after_sync();
-                    if (k == 0) trace(4);
-                    if (k + 1 == plan.k_blocks) trace(5);
                     const uint64_t a0_desc = operand_descriptor(
                         a_ring + (s * kHalves) * kATileBytes, kKMajorLeadingBytes);
                     const uint64_t a1_desc = operand_descriptor(
@@ -288,7 +267,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 if (!live) break;
                 mma_commit<2>(acc_full);
                 mma_commit<2>(mapa(acc_full, 1));
-                trace(6);
                 ++count;
             }
         }
@@ -310,7 +288,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             }
             ++count;
             tc_fence_after_sync();
-            if (warp == 2) trace(7);
             const bool mine = half < item.halves;
             // Read this warp's [32, 256] band out as bf16 pairs, then release the accumulator:
             // the stores below overlap the next item's main loop.
@@ -364,7 +341,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(mapa(acc_empty, 0));
-            if (warp == 2) trace(8);
             if (!mine) continue;
 
             const int c_row =
@@ -422,9 +398,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 }
             }
         }
-        if (warp == 2) trace(9);
         if (lane == 0) tma_store_wait_before_exit();
-        if (warp == 2) trace(10);
     }
 
     // ---------------------------------------------------- teardown
@@ -436,7 +410,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     tc_fence_before_sync();
     __syncthreads();
     cluster_sync();
-    if (warp == 0) trace(11);
     if (warp == 1) tmem_dealloc<2>(tmem, kTmemColumns);
 }
 
@@ -454,7 +427,9 @@ static Schedule schedule(uint32_t m, uint32_t n, uint32_t k, uint32_t group, uin
     plan.m = m;
     plan.tiles_m = (m + kHalves * 2 * kBlockM - 1) / (kHalves * 2 * kBlockM);
     plan.tiles_n = n / kBlockN;
-    plan.group = group;
+    // A width at or past the tile rows is already the column-major walk; clamping keeps
+    // `group * columns` inside 32 bits whatever the caller passes.
+    plan.group = group < plan.tiles_m ? group : plan.tiles_m;
     plan.k_blocks = k / kBlockK;
     const uint32_t tiles = plan.tiles_m * plan.tiles_n;
     const uint32_t tail = tiles % clusters;
@@ -605,23 +580,36 @@ int host_pipeline(HostPipeline** out) {
 }
 }  // namespace
 
+static int host_shape_check(const void* a, const void* b, const void* c, uint32_t m, uint32_t n, uint32_t k,
+                            uint32_t group) {
+    if (!a || !b || !c) return fk_fail(FK_ERR_INVALID, "an operand pointer is null");
+    if (m == 0 || n == 0 || k == 0 || m % (2 * gemm::kBlockM) || n % gemm::kBlockN || k % gemm::kBlockK)
+        return fk_fail(FK_ERR_SHAPE, "%ux%ux%u does not divide the %ux%ux%u tiling", m, n, k,
+                       2 * gemm::kBlockM, gemm::kBlockN, gemm::kBlockK);
+    if (group == 0) return fk_fail(FK_ERR_SHAPE, "a traversal group width of 0 has no tiles in it");
+    return FK_OK;
+}
+
 // Upload, compute and read-back overlap: B goes up first, then A in blocks of rows; the GEMM of a
 // block starts when its rows of A have landed, and its rows of C go back while later blocks upload and
 // compute. Row blocks keep every copy contiguous on both sides. PCIe is full duplex, so the whole call
 // costs about the upload alone plus the last block's GEMM and read-back; done in sequence it cost
 // upload + compute + read-back. The copies overlap only from page-locked host memory; from pageable
-// memory the call is still correct.
+// memory the call is still correct. One call at a time per device: the staging buffers, streams,
+// events and status words are the device's, so the call holds the device's guard from its first
+// enqueue to its last wait, and a second thread's call on the same device waits its turn.
 extern "C" int fk_gemm_bf16_host(const uint16_t* a_host, const uint16_t* b_host, uint16_t* c_host,
                                  uint32_t m, uint32_t n, uint32_t k, uint32_t group) {
-    if (!a_host || !b_host || !c_host) return fk_fail(FK_ERR_INVALID, "an operand pointer is null");
-    if (m == 0 || n == 0 || k == 0 || m % (2 * gemm::kBlockM) || n % gemm::kBlockN || k % gemm::kBlockK)
-        return fk_fail(FK_ERR_SHAPE, "%ux%ux%u does not divide the %ux%ux%u tiling", m, n, k,
-                       2 * gemm::kBlockM, gemm::kBlockN, gemm::kBlockK);
+    int status = host_shape_check(a_host, b_host, c_host, m, n, k, group);
+    if (status != FK_OK) return status;
+    int device = 0;
+    FK_CUDA(cudaGetDevice(&device));
+    std::lock_guard<std::mutex> call(device_call_guard(device));
     const size_t a_bytes = size_t(m) * k * 2, b_bytes = size_t(n) * k * 2, c_bytes = size_t(m) * n * 2;
     void *a = nullptr, *b = nullptr, *c = nullptr;
     uint32_t* status_words = nullptr;
     HostPipeline* pipe = nullptr;
-    int status = scratch(0, a_bytes, &a);
+    status = scratch(0, a_bytes, &a);
     if (status == FK_OK) status = scratch(1, b_bytes, &b);
     if (status == FK_OK) status = scratch(2, c_bytes, &c);
     if (status == FK_OK) status = scratch_status(&status_words);
@@ -634,38 +622,46 @@ extern "C" int fk_gemm_bf16_host(const uint16_t* a_host, const uint16_t* b_host,
     const uint32_t chunk = ((tiles + kHostChunks - 1) / kHostChunks) * tile_rows;
     const uint32_t chunks = (m + chunk - 1) / chunk;
 
-    // The staging buffers are shared with earlier calls on the default stream: start after them.
-    FK_CUDA(cudaEventRecord(pipe->idle, nullptr));
-    FK_CUDA(cudaStreamWaitEvent(pipe->upload, pipe->idle, 0));
-    FK_CUDA(cudaStreamWaitEvent(pipe->compute, pipe->idle, 0));
-    FK_CUDA(cudaStreamWaitEvent(pipe->download, pipe->idle, 0));
-    FK_CUDA(cudaMemsetAsync(status_words, 0, 32, pipe->compute));
-    FK_CUDA(cudaMemcpyAsync(b, b_host, b_bytes, cudaMemcpyHostToDevice, pipe->upload));
-    FK_CUDA(cudaEventRecord(pipe->b_ready, pipe->upload));
-    FK_CUDA(cudaStreamWaitEvent(pipe->compute, pipe->b_ready, 0));
-    for (uint32_t i = 0; i < chunks; ++i) {
-        const uint32_t row0 = i * chunk, rows = (m - row0 < chunk) ? m - row0 : chunk;
-        uint8_t* a_chunk = static_cast<uint8_t*>(a) + size_t(row0) * k * 2;
-        uint8_t* c_chunk = static_cast<uint8_t*>(c) + size_t(row0) * n * 2;
-        FK_CUDA(cudaMemcpyAsync(a_chunk, a_host + size_t(row0) * k, size_t(rows) * k * 2, cudaMemcpyHostToDevice,
-                                pipe->upload));
-        FK_CUDA(cudaEventRecord(pipe->a_ready[i], pipe->upload));
-        FK_CUDA(cudaStreamWaitEvent(pipe->compute, pipe->a_ready[i], 0));
-        status = fk_gemm_bf16(a_chunk, b, c_chunk, rows, n, k, n, group, pipe->compute, status_words);
-        if (status != FK_OK) break;
-        FK_CUDA(cudaEventRecord(pipe->c_ready[i], pipe->compute));
-        FK_CUDA(cudaStreamWaitEvent(pipe->download, pipe->c_ready[i], 0));
-        FK_CUDA(cudaMemcpyAsync(c_host + size_t(row0) * n, c_chunk, size_t(rows) * n * 2, cudaMemcpyDeviceToHost,
-                                pipe->download));
-    }
-    // Whatever happened, leave no work of this call in flight behind the return.
-    const cudaError_t up = cudaStreamSynchronize(pipe->upload);
-    const cudaError_t run = cudaStreamSynchronize(pipe->compute);
-    const cudaError_t down = cudaStreamSynchronize(pipe->download);
+    // Everything is enqueued inside this lambda so that, whatever fails part-way, the three
+    // streams are drained below before the call returns: the caller may free or reuse its host
+    // buffers the moment it has the return code.
+    const auto enqueue = [&]() -> int {
+        // The staging buffers are shared with earlier work on the default stream: start after it.
+        FK_CUDA(cudaEventRecord(pipe->idle, nullptr));
+        FK_CUDA(cudaStreamWaitEvent(pipe->upload, pipe->idle, 0));
+        FK_CUDA(cudaStreamWaitEvent(pipe->compute, pipe->idle, 0));
+        FK_CUDA(cudaStreamWaitEvent(pipe->download, pipe->idle, 0));
+        FK_CUDA(cudaMemsetAsync(status_words, 0, 32, pipe->compute));
+        FK_CUDA(cudaMemcpyAsync(b, b_host, b_bytes, cudaMemcpyHostToDevice, pipe->upload));
+        FK_CUDA(cudaEventRecord(pipe->b_ready, pipe->upload));
+        FK_CUDA(cudaStreamWaitEvent(pipe->compute, pipe->b_ready, 0));
+        for (uint32_t i = 0; i < chunks; ++i) {
+            const uint32_t row0 = i * chunk, rows = (m - row0 < chunk) ? m - row0 : chunk;
+            uint8_t* a_chunk = static_cast<uint8_t*>(a) + size_t(row0) * k * 2;
+            uint8_t* c_chunk = static_cast<uint8_t*>(c) + size_t(row0) * n * 2;
+            FK_CUDA(cudaMemcpyAsync(a_chunk, a_host + size_t(row0) * k, size_t(rows) * k * 2,
+                                    cudaMemcpyHostToDevice, pipe->upload));
+            FK_CUDA(cudaEventRecord(pipe->a_ready[i], pipe->upload));
+            FK_CUDA(cudaStreamWaitEvent(pipe->compute, pipe->a_ready[i], 0));
+            const int launched = fk_gemm_bf16(a_chunk, b, c_chunk, rows, n, k, n, group, pipe->compute, status_words);
+            if (launched != FK_OK) return launched;
+            FK_CUDA(cudaEventRecord(pipe->c_ready[i], pipe->compute));
+            FK_CUDA(cudaStreamWaitEvent(pipe->download, pipe->c_ready[i], 0));
+            FK_CUDA(cudaMemcpyAsync(c_host + size_t(row0) * n, c_chunk, size_t(rows) * n * 2,
+                                    cudaMemcpyDeviceToHost, pipe->download));
+        }
+        return FK_OK;
+    };
+    status = enqueue();
+    // Whatever happened, leave no work of this call in flight behind the return. Each wait carries
+    // the launch deadline (src/watchdog.rs:300-332): a wedged device yields FK_ERR_TIMEOUT, not a hang.
+    const int up = wait_stream(pipe->upload);
+    const int run = wait_stream(pipe->compute);
+    const int down = wait_stream(pipe->download);
     if (status != FK_OK) return status;
-    FK_CUDA(up);
-    FK_CUDA(run);
-    FK_CUDA(down);
+    if (up != FK_OK) return up;
+    if (run != FK_OK) return run;
+    if (down != FK_OK) return down;
     return fk_status_check(status_words, pipe->compute);
 }
 
@@ -707,28 +703,41 @@ int static_scratch(uint8_t** out) {
 extern "C" int fk_gemm_bf16_host_noalloc(const uint16_t* a_host, const uint16_t* b_host,
                                          uint16_t* c_host, uint32_t m, uint32_t n, uint32_t k,
                                          uint32_t group) {
-    if (!a_host || !b_host || !c_host) return fk_fail(FK_ERR_INVALID, "an operand pointer is null");
+    // Every refusal comes before the first enqueue: a refused call has touched nothing.
+    int status = host_shape_check(a_host, b_host, c_host, m, n, k, group);
+    if (status != FK_OK) return status;
     const size_t a_bytes = size_t(m) * k * 2, b_bytes = size_t(n) * k * 2, c_bytes = size_t(m) * n * 2;
     if (a_bytes > kStaticOperandBytes || b_bytes > kStaticOperandBytes || c_bytes > kStaticOperandBytes)
         return fk_fail(FK_ERR_TOO_LARGE,
                        "%ux%ux%u needs %zu / %zu / %zu bytes for A / B / C; the built-in staging holds "
                        "%zu bytes each (use fk_gemm_bf16_host for larger shapes)",
                        m, n, k, a_bytes, b_bytes, c_bytes, kStaticOperandBytes);
+    int device = 0;
+    FK_CUDA(cudaGetDevice(&device));
+    std::lock_guard<std::mutex> call(device_call_guard(device));
     uint8_t* scratch_base = nullptr;
-    int status = static_scratch(&scratch_base);
+    status = static_scratch(&scratch_base);
     if (status != FK_OK) return status;
     void* a = scratch_base;
     void* b = scratch_base + kStaticOperandBytes;
     void* c = scratch_base + 2 * kStaticOperandBytes;
     uint32_t* status_words = reinterpret_cast<uint32_t*>(scratch_base + 3 * kStaticOperandBytes);
     cudaStream_t stream = nullptr;
-    // The array keeps the previous call's contents: the status words must start at zero. A, B
-    // and C are overwritten in full by this call before anything reads them.
-    FK_CUDA(cudaMemsetAsync(status_words, 0, 32, stream));
-    FK_CUDA(cudaMemcpyAsync(a, a_host, a_bytes, cudaMemcpyHostToDevice, stream));
-    FK_CUDA(cudaMemcpyAsync(b, b_host, b_bytes, cudaMemcpyHostToDevice, stream));
-    status = fk_gemm_bf16(a, b, c, m, n, k, n, group, stream, status_words);
-    if (status != FK_OK) return status;
-    FK_CUDA(cudaMemcpyAsync(c_host, c, c_bytes, cudaMemcpyDeviceToHost, stream));
+    const auto enqueue = [&]() -> int {
+        // The array keeps the previous call's contents: the status words must start at zero. A, B
+        // and C are overwritten in full by this call before anything reads them.
+        FK_CUDA(cudaMemsetAsync(status_words, 0, 32, stream));
+        FK_CUDA(cudaMemcpyAsync(a, a_host, a_bytes, cudaMemcpyHostToDevice, stream));
+        FK_CUDA(cudaMemcpyAsync(b, b_host, b_bytes, cudaMemcpyHostToDevice, stream));
+        const int launched = fk_gemm_bf16(a, b, c, m, n, k, n, group, stream, status_words);
+        if (launched != FK_OK) return launched;
+        FK_CUDA(cudaMemcpyAsync(c_host, c, c_bytes, cudaMemcpyDeviceToHost, stream));
+        return FK_OK;
+    };
+    status = enqueue();
+    if (status != FK_OK) {
+        wait_stream(stream);  // no copy of this call may still be reading the caller's buffers
+        return status;
+    }
     return fk_status_check(status_words, stream);
 }

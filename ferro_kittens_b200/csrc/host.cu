@@ -6,6 +6,7 @@
 
 #include <chrono>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <thread>
@@ -13,6 +14,10 @@
 #include "fk_host.h"
 #include "fk_layout.h"
 #include "fk_ptx.cuh"
+
+namespace fk {
+constexpr int kMaxDevices = 64;
+}
 
 // ------------------------------------------------------------------ errors
 
@@ -327,17 +332,24 @@ extern "C" uint32_t fk_tmem_address(uint32_t base, uint32_t row, uint32_t column
 
 // ------------------------------------------------------------------ waits and status
 
+// Spin for the first 50 ms (a launch's own length: be prompt), then sleep 1 ms between polls so
+// that a wedged launch does not burn a core for the rest of its budget -- the reference's SPIN and
+// POLL (src/watchdog.rs:117-121). Past the budget the reference ends the process; on a shared
+// GPU this returns FK_ERR_TIMEOUT instead and leaves the decision to the caller.
 template <typename Query>
 static int poll_until(Query query, uint32_t budget_ms, const char* what) {
-    const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(budget_ms);
+    const auto start = std::chrono::steady_clock::now();
+    const auto budget = std::chrono::milliseconds(budget_ms);
     for (;;) {
         const cudaError_t status = query();
         if (status == cudaSuccess) return FK_OK;
         if (status != cudaErrorNotReady)
             return fk_fail(FK_ERR_DRIVER, "%s failed: %s", what, cudaGetErrorString(status));
-        if (std::chrono::steady_clock::now() >= deadline)
-            return fk_fail(FK_ERR_TIMEOUT, "%s still pending after %u ms", what, budget_ms);
-        std::this_thread::sleep_for(std::chrono::microseconds(50));
+        const auto waited = std::chrono::steady_clock::now() - start;
+        if (waited >= budget)
+            return fk_fail(FK_ERR_TIMEOUT, "%s still pending after %u ms (the launch deadline; %s overrides it)",
+                           what, budget_ms, "KITTENS_LAUNCH_BUDGET_MS");
+        if (waited >= std::chrono::milliseconds(50)) std::this_thread::sleep_for(std::chrono::milliseconds(1));
     }
 }
 
@@ -349,6 +361,61 @@ extern "C" int fk_wait_event(void* event, uint32_t budget_ms) {
     return poll_until([&] { return cudaEventQuery(static_cast<cudaEvent_t>(event)); }, budget_ms,
                       "cudaEventQuery");
 }
+
+// The budget every wait inside the library carries: the reference's 30 s default
+// (src/watchdog.rs:102) unless its environment variable (:106) says otherwise. Read once, at the
+// first wait, so that every wait of a run carries the same budget.
+extern "C" uint32_t fk_launch_budget_ms(void) {
+    static const uint32_t budget = [] {
+        const char* text = getenv("KITTENS_LAUNCH_BUDGET_MS");
+        if (text && *text) {
+            char* end = nullptr;
+            const unsigned long long value = strtoull(text, &end, 10);
+            if (end && *end == '\0' && value > 0 && value <= 0xffffffffull) return static_cast<uint32_t>(value);
+        }
+        return 30000u;
+    }();
+    return budget;
+}
+
+// The deadline path without a device: a query that reports "not ready" `ready_after_polls` times
+// (for ever when that is 0xffffffff) and then success, run through the same poll loop.
+extern "C" int fk_selftest_deadline(uint32_t budget_ms, uint32_t ready_after_polls) {
+    uint32_t polls = 0;
+    return poll_until(
+        [&] {
+            if (ready_after_polls != 0xffffffffu && polls >= ready_after_polls) return cudaSuccess;
+            ++polls;
+            return cudaErrorNotReady;
+        },
+        budget_ms, "the self-test query");
+}
+
+extern "C" int fk_selftest_call_guard(int device, uint32_t hold_ms, uint64_t* entered_ns, uint64_t* left_ns) {
+    if (device < 0 || device >= fk::kMaxDevices || !entered_ns || !left_ns)
+        return fk_fail(FK_ERR_INVALID, "device index %d out of range or a null pointer", device);
+    const auto now = [] {
+        return static_cast<uint64_t>(std::chrono::duration_cast<std::chrono::nanoseconds>(
+                                         std::chrono::steady_clock::now().time_since_epoch())
+                                         .count());
+    };
+    std::lock_guard<std::mutex> call(fk::device_call_guard(device));
+    *entered_ns = now();
+    std::this_thread::sleep_for(std::chrono::milliseconds(hold_ms));
+    *left_ns = now();
+    return FK_OK;
+}
+
+namespace fk {
+
+int wait_stream(cudaStream_t stream) { return fk_wait_stream(stream, fk_launch_budget_ms()); }
+
+std::mutex& device_call_guard(int device) {
+    static std::mutex guards[kMaxDevices];
+    return guards[(device >= 0 && device < kMaxDevices) ? device : 0];
+}
+
+}  // namespace fk
 
 static const char* stall_role(uint32_t code) {
     switch (code) {
@@ -390,7 +457,8 @@ extern "C" int fk_status_check(const uint32_t* device_status, void* stream) {
     uint32_t words[4] = {0, 0, 0, 0};
     FK_CUDA(cudaMemcpyAsync(words, device_status, sizeof words, cudaMemcpyDeviceToHost,
                             static_cast<cudaStream_t>(stream)));
-    FK_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    const int waited = fk::wait_stream(static_cast<cudaStream_t>(stream));
+    if (waited != FK_OK) return waited;
     if (words[0] == 0) return FK_OK;
     return fk_fail(FK_ERR_DEVICE_STALL, "device stall: %s (code %#x) in block %u, step %u, parity %u",
                    stall_role(words[0]), words[0], words[1], words[2], words[3]);
@@ -428,7 +496,6 @@ extern "C" int fk_selftest_stall(void* stream, uint32_t* device_status, uint32_t
 
 namespace fk {
 
-constexpr int kMaxDevices = 64;
 constexpr int kSlots = 8;
 static std::mutex scratch_guard;
 static void* scratch_base[kMaxDevices][kSlots];
@@ -441,6 +508,8 @@ int scratch(int slot, size_t bytes, void** out) {
     if (device >= kMaxDevices || slot >= kSlots) return fk_fail(FK_ERR_INVALID, "scratch slot out of range");
     std::lock_guard<std::mutex> lock(scratch_guard);
     if (scratch_size[device][slot] < bytes) {
+        // Callers hold the device's call guard and leave nothing in flight behind their return, so
+        // no kernel or copy can still be using the buffer that is replaced here.
         if (scratch_base[device][slot]) FK_CUDA(cudaFree(scratch_base[device][slot]));
         scratch_base[device][slot] = nullptr;
         scratch_size[device][slot] = 0;

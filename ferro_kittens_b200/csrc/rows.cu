@@ -30,22 +30,11 @@ constexpr uint32_t kTileRows = 128;
 constexpr uint32_t kColumns = 128;
 constexpr uint32_t kRowBytes = kColumns * 2;
 constexpr uint32_t kTileBytes = kTileRows * kRowBytes;  // 32 KiB
-#ifndef FK_ROWS_STAGES
-#define FK_ROWS_STAGES 4
-#endif
-constexpr uint32_t kStages = FK_ROWS_STAGES;
+constexpr uint32_t kStages = 4;
 constexpr uint32_t kComputeWarps = 16;
 constexpr uint32_t kWarpRows = kTileRows / kComputeWarps;  // 8
 constexpr uint32_t kSteps = kWarpRows / 2;                 // two rows per warp-wide access
 constexpr uint32_t kThreads = (kComputeWarps + 1) * 32;
-
-// Of a lane's four pairs per row, the pairs whose bit is set take 2^x from the FMA-pipe polynomial
-// instead of the ex2 unit. Off by default: one pair of four measured +3 % at a power-capped clock and
-// nothing otherwise, and the polynomial's 7.5e-5 on top of the bf16 rounding crosses the 2^-8 gate.
-#ifndef FK_ROWS_POLY_MASK
-#define FK_ROWS_POLY_MASK 0x0u
-#endif
-constexpr uint32_t kPolyMask = FK_ROWS_POLY_MASK;
 
 enum Operation : int { kSoftmax = 0, kLayerNorm = 1, kGroupNorm = 2 };
 
@@ -234,8 +223,7 @@ __global__ void __launch_bounds__(kThreads, 1) rows_kernel(const Arguments args,
 #pragma unroll
                     for (uint32_t i = 0; i < 4; ++i) {
                         const float2 d = __fadd2_rn(x[step][i], shift);
-                        x[step][i] = ((kPolyMask >> i) & 1u) ? exp2_pair_fma(d)
-                                                             : make_float2(ex2_approx(d.x), ex2_approx(d.y));
+                        x[step][i] = make_float2(ex2_approx(d.x), ex2_approx(d.y));
                     }
                     const float scale = __frcp_rn(row_sum(lane_sum(x[step])));
                     const float2 scale2 = make_float2(scale, scale);

@@ -187,7 +187,12 @@ int fk_gemm(const void* a, const void* b, void* c, uint32_t m, uint32_t n, uint3
 
 /* The whole of `gemm::run` from HOST buffers (:503-537): stage A and B, launch,
  * read C back; blocks until C is on the host. Device buffers are cached per
- * device and grown on demand. */
+ * device and grown on demand. One call at a time per device: the staging buffers, the three
+ * streams and the status words belong to the device, so the call holds a per-device lock from
+ * its first enqueue to its last wait and a second thread calling on the same device waits its
+ * turn (fk_flash_fwd_host and fk_gemm_bf16_host_noalloc take the same lock). Every wait inside
+ * carries the launch deadline (fk_launch_budget_ms) and the call leaves none of its copies in
+ * flight behind any return, error returns included. */
 int fk_gemm_bf16_host(const uint16_t* a_host, const uint16_t* b_host, uint16_t* c_host, uint32_t m,
                       uint32_t n, uint32_t k, uint32_t group);
 
@@ -275,13 +280,28 @@ int fk_groupnorm_tile(const void* source, void* destination, uint32_t rows, floa
 /* ---------------------------------------------------------------- waits and status
  *
  * `watchdog::wait` / `wait_event` (src/watchdog.rs:300-332): poll with a
- * deadline instead of blocking in a synchronize. Unlike the reference these
- * return FK_ERR_TIMEOUT rather than aborting the process. */
+ * deadline instead of blocking in a synchronize: spin for the first 50 ms, then one poll per
+ * millisecond (`SPIN`, `POLL`, :117-121). Unlike the reference these return FK_ERR_TIMEOUT
+ * rather than aborting the process. */
 int fk_wait_stream(void* stream, uint32_t budget_ms);
 int fk_wait_event(void* event, uint32_t budget_ms);
 
-/* Read a kernel's 4 status words back (blocking on `stream`) and, when the
- * first is non-zero, return FK_ERR_DEVICE_STALL with the role, block, stage and
+/* `watchdog::budget` (src/watchdog.rs:102-106): the deadline of every wait the library makes on
+ * its own (fk_status_check and the host-buffer entry points): 30 000 ms unless the
+ * environment variable KITTENS_LAUNCH_BUDGET_MS holds another value. Read once per process. */
+uint32_t fk_launch_budget_ms(void);
+
+/* Self-tests of the host-side waiting, no device needed. fk_selftest_deadline runs the poll loop
+ * of fk_wait_stream against a query that answers "not ready" `ready_after_polls` times
+ * (0xffffffff: for ever) and then "done": FK_OK, or FK_ERR_TIMEOUT after `budget_ms`.
+ * fk_selftest_call_guard takes the per-device lock of the host-buffer entry points, holds it
+ * for `hold_ms` and reports when it got and gave up the lock (steady-clock nanoseconds): two
+ * threads calling it for one device must not overlap. */
+int fk_selftest_deadline(uint32_t budget_ms, uint32_t ready_after_polls);
+int fk_selftest_call_guard(int device, uint32_t hold_ms, uint64_t* entered_ns, uint64_t* left_ns);
+
+/* Read a kernel's 4 status words back (waiting on `stream` under the launch
+ * deadline) and, when the first is non-zero, return FK_ERR_DEVICE_STALL with the role, block, stage and
  * parity in fk_last_error(). */
 int fk_status_check(const uint32_t* device_status, void* stream);
 
