@@ -6,26 +6,36 @@
 // (examples/src/flash_forward.rs:150-310, 457-568), widened to a batch of planes,
 // a non-causal mode, bf16 output and LSE. Same panel layout ([planes, seq, 128]
 // bf16), same two contractions (Q K^T with both operands K-major; P V with V
-// MN-major), same online softmax. The structure is new: where the reference
-// alternates MMA and softmax behind block-wide barriers, one CTA here owns two
-// 128-row query tiles and ping-pongs them, so the tensor core works on one
-// tile while the CUDA cores run the other's softmax.
+// MN-major), same online softmax, output rows written by plain global stores like
+// the reference's `store_rows` (src/global.rs:238-252). The structure is new: where
+// the reference launches one CTA per query block and alternates MMA and softmax
+// behind block-wide barriers, here one persistent CTA per SM walks a list of work
+// items, each two 128-row query tiles that it ping-pongs, so the tensor core works
+// on one tile while the CUDA cores run the other's softmax, and the next item's
+// Q, first K block and first Q K^T overlap the current item's last softmax and
+// read-out.
 //
 //   warps 0-7   softmax, one team of four warps per query tile (warps 0-3 tile 0, warps 4-7
 //               tile 1), one thread per row: tcgen05.ld 32x32b of the row's 128 scores, running
 //               max and sum in registers with no exchange between threads, P written back to
 //               tensor memory as bf16 over S and published in two halves so that P.V starts under
 //               the second half's exponentials; the output accumulator is rescaled in tensor
-//               memory only when the max moved by more than 2^8; final normalise, bf16 staging
-//               and TMA store. The two teams run independently, so one tile's exponentials
-//               overlap the other's waits, loads and maxima on every scheduler.
-//   warp 8      loader: Q once, then K(j), V(j) 128-key blocks through a ring of kSlots slots.
+//               memory only when the max moved by more than 2^8; at the end of an item the team
+//               reads its accumulator out, hands it back (`o_free`) and stores the normalised rows.
+//               The two teams run independently, so one tile's exponentials overlap the other's
+//               waits, loads and maxima on every scheduler.
+//   warp 8      loader: per item Q_t as soon as the previous item's last Q K^T has read its
+//               buffer, then K(j), V(j) 128-key blocks through a ring of kSlots slots that runs
+//               on across items.
 //   warp 9      MMA issue: S_t = Q_t K(j)^T (8 x M128 N128 K16) and O_t += P_t V(j)
-//               (8 x M128 N128 K16, A from tensor memory), interleaved across the two tiles.
+//               (8 x M128 N128 K16, A from tensor memory), interleaved across the two tiles; the
+//               next item's first S_t is issued right behind the current item's last P V.
 //
 // Tensor memory (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each; P_t
 // aliases the first 64 columns of S_t. Causal launches skip key blocks above
-// the diagonal and mask only the diagonal block. Every wait is bounded.
+// the diagonal, mask only the diagonal block, and pair a heavy query block with
+// a light one of the same plane in every work item so that the items weigh the
+// same. Barrier phases are carried across items. Every wait is bounded.
 
 #include <mutex>
 
@@ -51,8 +61,8 @@ constexpr uint32_t kMmaWarp = kSoftmaxWarps + 1;
 // and takes kSoftmaxRegisters, the third warpgroup keeps kServiceRegisters.
 constexpr uint32_t kThreads = 3 * 128;
 constexpr uint32_t kLaunchRegisters = 168;
-constexpr uint32_t kSoftmaxRegisters = 208;
-constexpr uint32_t kServiceRegisters = 88;
+constexpr uint32_t kSoftmaxRegisters = 200;
+constexpr uint32_t kServiceRegisters = 104;
 // setmaxnreg.inc waits until the pool holds the registers it asks for: the demands must fit what
 // the launch allocated, or the wait never ends.
 static_assert(kSoftmaxWarps * 32 * kSoftmaxRegisters + 128 * kServiceRegisters <= kThreads * kLaunchRegisters,
@@ -68,30 +78,46 @@ constexpr float kRescaleThreshold = 8.0f;
 // Of the 16 pairs of scores in a 32-column chunk, the pairs whose bit is set here take their
 // 2^x from a polynomial on the FMA pipe instead of the ex2 unit: at D = 128 a score tile costs
 // as many ex2-unit cycles as tensor cycles.
-#ifndef FK_FLASH_POLY_MASK
-#define FK_FLASH_POLY_MASK 0x1111u
-#endif
-constexpr uint32_t kPolyMask = FK_FLASH_POLY_MASK;
-// P is published in two halves of 64 keys: the first four P.V MMAs of a block are issued while
-// the team is still exponentiating the second half.
-#ifndef FK_FLASH_SPLIT
-#define FK_FLASH_SPLIT 1
-#endif
-constexpr bool kSplitPublish = FK_FLASH_SPLIT != 0;
+// Measured best share: four pairs of sixteen (three quarters of the exponentials stay on the unit).
+constexpr uint32_t kPolyMask = 0x1111u;
+// P is published in runs of 32-key chunks, each run on a barrier of its own: the P.V MMAs of a
+// run are issued while the team is still exponentiating the runs after it. Bit c of the mask
+// ends a run after chunk c (bit 3, the last chunk, always does).
+// Two halves measured best (three quarters + one, and four quarters, lose 1-4 %: every run costs
+// the team a tcgen05.wait::st).
+constexpr uint32_t kPublishMask = 0xau;
+static_assert((kPublishMask & 8u) && kPublishMask < 16u, "the last chunk ends the last run");
+constexpr uint32_t kParts = ((kPublishMask >> 0) & 1u) + ((kPublishMask >> 1) & 1u) + ((kPublishMask >> 2) & 1u) + 1u;
+// Run `part` covers chunks [run_first(part), run_first(part + 1)).
+__host__ __device__ constexpr uint32_t run_first(uint32_t part) {
+    uint32_t seen = 0;
+    for (uint32_t c = 0; c < 4; ++c) {
+        if (seen == part) return c;
+        if ((kPublishMask >> c) & 1u) ++seen;
+    }
+    return 4;
+}
+__host__ __device__ constexpr uint32_t run_of(uint32_t chunk) {
+    uint32_t part = 0;
+    for (uint32_t c = 0; c < chunk; ++c)
+        if ((kPublishMask >> c) & 1u) ++part;
+    return part;
+}
 
 struct Plan {
-    SharedPlan q, kv, q_full, kv_full, kv_empty, s_full, p_half, p_ready, o_done, tmem_slot, stop, end;
+    SharedPlan q, kv, q_full, q_empty, kv_full, kv_empty, s_full, p_ready, o_done, o_free, tmem_slot, stop, end;
     constexpr Plan()
         : q(SharedPlan{}.tile_ring(kTileRows, kHead, 2, kTiles)),
           kv(q.tile_ring(kBlockKeys, kHead, 2, kSlots)),
-          q_full(kv.semaphore()),
-          kv_full(q_full.semaphores(kSlots)),
+          q_full(kv.semaphores(kTiles)),
+          q_empty(q_full.semaphores(kTiles)),
+          kv_full(q_empty.semaphores(kSlots)),
           kv_empty(kv_full.semaphores(kSlots)),
           s_full(kv_empty.semaphores(kTiles)),
-          p_half(s_full.semaphores(kTiles)),
-          p_ready(p_half.semaphores(kTiles)),
+          p_ready(s_full.semaphores(kTiles * kParts)),
           o_done(p_ready.semaphores(kTiles)),
-          tmem_slot(o_done.tmem_slot()),
+          o_free(o_done.semaphores(kTiles)),
+          tmem_slot(o_free.tmem_slot()),
           stop(tmem_slot.word()),
           end(stop) {}
 };
@@ -109,39 +135,85 @@ enum StallCode : uint32_t {
     kStallMmaP = 0x204,
     kStallSoftmaxS = 0x205,
     kStallSoftmaxO = 0x206,
+    kStallMmaOutput = 0x207,
+    kStallLoaderQ = 0x208,
     kMisaligned = 0x2ff,
 };
 
-struct Extent {
+// What a launch hands every role so that each walks the same list of work items.
+struct Problem {
+    uint32_t seq;
+    uint32_t planes;
+    uint32_t pairs;   // query blocks of kTiles * kTileRows rows per plane: ceil(seq / 256)
+    uint32_t causal;
+    uint32_t items;   // work items of the launch
+};
+
+// One visit of a CTA: a query block of one plane, or nothing (`most` == 0).
+struct Work {
+    uint32_t plane;
+    uint32_t q_row0;
     uint32_t blocks[kTiles];  // key blocks each query tile attends
     uint32_t most;
 };
 
-// Key blocks per tile: all of them, or up to and including the diagonal block.
-__device__ __forceinline__ Extent extent(uint32_t q_row0, uint32_t seq, bool causal) {
-    Extent e;
-    e.most = 0;
-    for (uint32_t t = 0; t < kTiles; ++t) {
-        const uint32_t first = q_row0 + kTileRows * t;
-        e.blocks[t] = first >= seq ? 0u : (causal ? first / kBlockKeys + 1u : seq / kBlockKeys);
-        e.most = e.blocks[t] > e.most ? e.blocks[t] : e.most;
+// Items of a launch, host and device: without a mask one query block each, plane-major, so that
+// the CTAs running together share a plane's K and V through the L2. Under a causal mask a query
+// block's work grows with its position, so an item is the pair {last - h, h} of one plane, heavy
+// first: every item then weighs the same and a static round-robin over the CTAs is balanced.
+__host__ __device__ __forceinline__ uint32_t item_count(uint32_t pairs, uint32_t planes, bool causal) {
+    return (causal ? (pairs + 1) / 2 : pairs) * planes;
+}
+
+// The `visit`-th stop of CTA `cta` of `ctas`; false past the end of its list.
+__device__ __forceinline__ bool work_at(const Problem& problem, uint32_t cta, uint32_t ctas, uint32_t visit,
+                                        Work& work) {
+    uint32_t q_block;
+    bool present = true;
+    if (problem.causal) {
+        const uint32_t per_plane = (problem.pairs + 1) / 2;
+        const uint32_t item = cta + (visit >> 1) * ctas;
+        if (item >= problem.items) return false;
+        const uint32_t h = item % per_plane;
+        work.plane = item / per_plane;
+        q_block = (visit & 1u) ? h : problem.pairs - 1 - h;
+        present = !((visit & 1u) && h == problem.pairs - 1 - h);  // the middle block of an odd count, once
+    } else {
+        const uint32_t item = cta + visit * ctas;
+        if (item >= problem.items) return false;
+        work.plane = item / problem.pairs;
+        q_block = item % problem.pairs;
     }
-    return e;
+    work.q_row0 = q_block * kTiles * kTileRows;
+    work.most = 0;
+    for (uint32_t t = 0; t < kTiles; ++t) {
+        const uint32_t first = work.q_row0 + kTileRows * t;
+        work.blocks[t] = (!present || first >= problem.seq) ? 0u
+                         : problem.causal                   ? first / kBlockKeys + 1u
+                                                            : problem.seq / kBlockKeys;
+        work.most = work.blocks[t] > work.most ? work.blocks[t] : work.most;
+    }
+    return true;
 }
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
-    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    // volatile: a fold must stay behind the tcgen05.wait::ld that makes its operands valid.
+    asm volatile("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
+}
+
+__device__ __forceinline__ void st_global_v4(void* address, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(address), "r"(a), "r"(b), "r"(c), "r"(d)
+                 : "memory");
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
     flash_forward_kernel(const __grid_constant__ CUtensorMap q_map,
                          const __grid_constant__ CUtensorMap k_map,
-                         const __grid_constant__ CUtensorMap v_map,
-                         const __grid_constant__ CUtensorMap o_map, float* __restrict__ o_f32,
-                         float* __restrict__ lse, uint32_t seq, float scale, uint32_t causal,
-                         uint32_t* status) {
+                         const __grid_constant__ CUtensorMap v_map, uint16_t* __restrict__ o_bf16,
+                         float* __restrict__ o_f32, float* __restrict__ lse, const Problem problem,
+                         float scale, uint32_t* status) {
     extern __shared__ __align__(1024) uint8_t dynamic_shared[];
     const uint32_t base = smem_u32(dynamic_shared);
     if (base & (kBaseAlign - 1)) {
@@ -152,42 +224,42 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t q_tiles = base + kPlan.q.at;
     const uint32_t kv_ring = base + kPlan.kv.at;
     const uint32_t q_full = base + kPlan.q_full.at;
+    const uint32_t q_empty = base + kPlan.q_empty.at;
     const uint32_t kv_full = base + kPlan.kv_full.at;
     const uint32_t kv_empty = base + kPlan.kv_empty.at;
     const uint32_t s_full = base + kPlan.s_full.at;
-    const uint32_t p_half = base + kPlan.p_half.at;
     const uint32_t p_ready = base + kPlan.p_ready.at;
     const uint32_t o_done = base + kPlan.o_done.at;
+    const uint32_t o_free = base + kPlan.o_free.at;
     const uint32_t slot = base + kPlan.tmem_slot.at;
     volatile uint32_t* stop_flag = reinterpret_cast<volatile uint32_t*>(dynamic_shared + kPlan.stop.at);
     volatile uint32_t* slot_ptr = reinterpret_cast<volatile uint32_t*>(dynamic_shared + kPlan.tmem_slot.at);
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
-    const uint32_t plane = blockIdx.y;
-    // Causal work grows with the query block: launch the heaviest CTAs first.
-    const uint32_t q_block = causal ? gridDim.x - 1 - blockIdx.x : blockIdx.x;
-    const uint32_t q_row0 = q_block * kTiles * kTileRows;
-    const Extent keys = extent(q_row0, seq, causal != 0);
+    const uint32_t cta = blockIdx.x, ctas = gridDim.x;
+    const uint32_t seq = problem.seq;
+    const bool causal = problem.causal != 0;
 
     if (threadIdx.x == 0) {
-        mbar_init(q_full, 1);
         for (uint32_t s = 0; s < kSlots; ++s) {
             mbar_init(kv_full + 8 * s, 1);
             mbar_init(kv_empty + 8 * s, 1);
         }
         for (uint32_t t = 0; t < kTiles; ++t) {
+            mbar_init(q_full + 8 * t, 1);
+            mbar_init(q_empty + 8 * t, 1);
             mbar_init(s_full + 8 * t, 1);
-            mbar_init(p_half + 8 * t, kTeamWarps);
-            mbar_init(p_ready + 8 * t, kTeamWarps);
+            for (uint32_t part = 0; part < kParts; ++part)
+                mbar_init(p_ready + 8 * (kParts * t + part), kTeamWarps);
             mbar_init(o_done + 8 * t, 1);
+            mbar_init(o_free + 8 * t, kTeamWarps);
         }
         *stop_flag = 0;
         fence_mbarrier_init();
         prefetch_tensormap(&q_map);
         prefetch_tensormap(&k_map);
         prefetch_tensormap(&v_map);
-        prefetch_tensormap(&o_map);
     }
     if (warp == kMmaWarp) {
         tmem_alloc<1>(slot, kTmemColumns);
@@ -198,10 +270,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     tc_fence_after_sync();
     const uint32_t tmem = *slot_ptr;
 
-    // Every role here sits on a tile's dependency chain S -> softmax -> P -> P.V -> Q.K^T -> S:
-    // a thread suspended in try_wait comes back a few hundred cycles after the phase completes,
-    // so the roles poll instead (measured: +2.5 to +3.8 %).
-    const StallSite site{status, stop_flag, 0, kWaitBudgetCycles, true};
+    // The MMA thread sits on both tiles' dependency chains S -> softmax -> P -> P.V -> Q.K^T -> S
+    // and polls: a thread suspended in try_wait comes back a few hundred cycles after the phase
+    // completes. The softmax warps and the loader suspend: their probes would take issue slots
+    // from the other team's warps on the same scheduler, and the kernel runs at the board's power
+    // limit, where idle spinning is paid for in clock (measured: +2 % over everyone polling).
+    const StallSite site_mma{status, stop_flag, 0, kWaitBudgetCycles, true};
+    const StallSite site_softmax{status, stop_flag, 0, kWaitBudgetCycles, false};
+    const StallSite site_loader{status, stop_flag, 0, kWaitBudgetCycles, false};
 
     // The rebalancing sits inside the role branches: ptxas budgets every instruction reachable
     // from a setmaxnreg by its count, so the two regions must not share code before the teardown.
@@ -210,28 +286,42 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (warp == kLoaderWarp) {
         // ------------------------------------------------ loader
         if (lane == 0) {
-            uint32_t q_bytes = 0;
-            for (uint32_t t = 0; t < kTiles; ++t) q_bytes += keys.blocks[t] ? kBlockBytes : 0u;
-            mbar_arrive_expect_tx(q_full, q_bytes);
-            for (uint32_t t = 0; t < kTiles; ++t) {
-                if (!keys.blocks[t]) continue;
-                const int row = static_cast<int>(q_row0 + kTileRows * t);
-                for (uint32_t half = 0; half < 2; ++half)
-                    tma_load_3d(q_tiles + t * kBlockBytes + half * kSubtileBytes, &q_map,
-                                static_cast<int>(64 * half), row, static_cast<int>(plane), q_full);
-            }
-            // Ring order: K(0), V(0), K(1), V(1), ...
-            for (uint32_t fill = 0; fill < 2 * keys.most; ++fill) {
-                const uint32_t s = fill % kSlots;
-                const uint32_t parity = (fill / kSlots) & 1u;
-                if (!mbar_wait(kv_empty + 8 * s, parity ^ 1u, site, kStallLoader, fill)) break;
-                mbar_arrive_expect_tx(kv_full + 8 * s, kBlockBytes);
-                const CUtensorMap* map = (fill & 1u) ? &v_map : &k_map;
-                const int row = static_cast<int>(kBlockKeys * (fill >> 1));
-                for (uint32_t half = 0; half < 2; ++half)
-                    tma_load_3d(kv_ring + s * kBlockBytes + half * kSubtileBytes, map,
-                                static_cast<int>(64 * half), row, static_cast<int>(plane),
-                                kv_full + 8 * s);
+            uint32_t fill = 0;               // K/V blocks put into the ring so far, all items
+            uint32_t loaded[kTiles] = {0, 0};  // Q tiles loaded so far, per tile
+            bool live = true;
+            Work work;
+            for (uint32_t visit = 0; live && work_at(problem, cta, ctas, visit, work); ++visit) {
+                if (work.most == 0) continue;
+                for (uint32_t t = 0; live && t < kTiles; ++t) {
+                    if (!work.blocks[t]) continue;
+                    // The previous item's last Q.K^T of this tile has read the buffer.
+                    if (!mbar_wait(q_empty + 8 * t, (loaded[t] & 1u) ^ 1u, site_loader, kStallLoaderQ, loaded[t])) {
+                        live = false;
+                        break;
+                    }
+                    ++loaded[t];
+                    mbar_arrive_expect_tx(q_full + 8 * t, kBlockBytes);
+                    const int row = static_cast<int>(work.q_row0 + kTileRows * t);
+                    for (uint32_t half = 0; half < 2; ++half)
+                        tma_load_3d(q_tiles + t * kBlockBytes + half * kSubtileBytes, &q_map,
+                                    static_cast<int>(64 * half), row, static_cast<int>(work.plane), q_full + 8 * t);
+                }
+                // Ring order: K(0), V(0), K(1), V(1), ...
+                for (uint32_t i = 0; live && i < 2 * work.most; ++i, ++fill) {
+                    const uint32_t s = fill % kSlots;
+                    const uint32_t parity = (fill / kSlots) & 1u;
+                    if (!mbar_wait(kv_empty + 8 * s, parity ^ 1u, site_loader, kStallLoader, fill)) {
+                        live = false;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(kv_full + 8 * s, kBlockBytes);
+                    const CUtensorMap* map = (i & 1u) ? &v_map : &k_map;
+                    const int row = static_cast<int>(kBlockKeys * (i >> 1));
+                    for (uint32_t half = 0; half < 2; ++half)
+                        tma_load_3d(kv_ring + s * kBlockBytes + half * kSubtileBytes, map,
+                                    static_cast<int>(64 * half), row, static_cast<int>(work.plane),
+                                    kv_full + 8 * s);
+                }
             }
         }
       } else if (warp == kMmaWarp) {
@@ -241,9 +331,20 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (elect_one() != 0) {
             constexpr uint32_t idesc_qk = instruction_descriptor(kTileRows, kBlockKeys, false, false);
             constexpr uint32_t idesc_pv = instruction_descriptor(kTileRows, kHead, false, true);
+            bool live = true;
+            uint32_t started[kTiles] = {0, 0};  // items whose first Q.K^T was issued, per tile
+            uint32_t blocks_done[kTiles] = {0, 0};  // P.V blocks issued so far, per tile, all items
 
+            const auto wait_kv = [&](uint32_t fill) {
+                if (!mbar_wait(kv_full + 8 * (fill % kSlots), (fill / kSlots) & 1u, site_mma, kStallMmaKv, fill)) {
+                    live = false;
+                    return false;
+                }
+                tc_fence_after_sync();
+                return true;
+            };
             // S_t = Q_t . K^T over d = 128: two stacked [128, 64] subtiles, four K=16 chunks each.
-            auto scores = [&](uint32_t t, uint32_t k_slot) {
+            const auto scores = [&](uint32_t t, uint32_t k_slot) {
                 const uint32_t q_base = q_tiles + t * kBlockBytes;
                 const uint32_t k_base = kv_ring + k_slot * kBlockBytes;
 #pragma unroll
@@ -256,10 +357,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
                 mma_commit<1>(s_full + 8 * t);
             };
-            // O_t (+)= P_t . V over keys [16 first, 16 last) of the block: P from tensor memory
-            // (8 columns per K=16 chunk), V MN-major: 16 key rows per chunk, the second 64 head
+            // O_t (+)= P_t . V over K=16 chunks [first, last) of the block: P from tensor memory
+            // (8 columns per chunk), V MN-major: 16 key rows per chunk, the second 64 head
             // columns one subtile on.
-            auto output = [&](uint32_t t, uint32_t v_slot, bool accumulate, uint32_t first, uint32_t last) {
+            const auto output = [&](uint32_t t, uint32_t v_slot, bool accumulate, uint32_t first, uint32_t last) {
                 const uint32_t v_base = kv_ring + v_slot * kBlockBytes;
 #pragma unroll
                 for (uint32_t chunk = first; chunk < last; ++chunk)
@@ -268,66 +369,107 @@ __global__ void __launch_bounds__(kThreads, 1)
                            operand_descriptor(v_base + chunk * kMnMajorChunkBytes, kSubtileBytes),
                            idesc_pv, accumulate || chunk != 0);
             };
-            constexpr uint32_t kChunks = kBlockKeys / 16;
+            // The first S_t of an item: its Q_t must have landed, its K(0) sits at ring position
+            // `fill`. A tile with a single key block has read its Q for the last time here.
+            const auto first_scores = [&](const Work& item, uint32_t t, uint32_t fill) {
+                if (!mbar_wait(q_full + 8 * t, started[t] & 1u, site_mma, kStallMmaQ, started[t])) {
+                    live = false;
+                    return;
+                }
+                tc_fence_after_sync();
+                ++started[t];
+                scores(t, fill % kSlots);
+                if (item.blocks[t] == 1) mma_commit<1>(q_empty + 8 * t);
+            };
 
-            bool live = mbar_wait(q_full, 0, site, kStallMmaQ, 0);
-            if (live) {
-                tc_fence_after_sync();
-                live = mbar_wait(kv_full + 0, 0, site, kStallMmaKv, 0);
-            }
-            if (live) {
-                tc_fence_after_sync();
-                for (uint32_t t = 0; t < kTiles; ++t)
-                    if (keys.blocks[t]) scores(t, 0);
-                mma_commit<1>(kv_empty + 0);
-            }
-            for (uint32_t j = 0; live && j < keys.most; ++j) {
-                const uint32_t v_use = 2 * j + 1, k_use = 2 * j + 2;
-                const uint32_t v_slot = v_use % kSlots, k_slot = k_use % kSlots;
-                const bool more = j + 1 < keys.most;
-                if (!mbar_wait(kv_full + 8 * v_slot, (v_use / kSlots) & 1u, site, kStallMmaKv, v_use))
+            Work work, next;
+            uint32_t visit = 0;
+            bool have = false;
+            // The first item with work in it.
+            while (work_at(problem, cta, ctas, visit, work)) {
+                ++visit;
+                if (work.most) {
+                    have = true;
                     break;
-                bool next_loaded = false;
-                for (uint32_t t = 0; live && t < kTiles; ++t) {
-                    if (j < keys.blocks[t]) {
-                        if (kSplitPublish) {
-                            if (!mbar_wait(p_half + 8 * t, j & 1u, site, kStallMmaP, j)) {
-                                live = false;
-                                break;
-                            }
-                            tc_fence_after_sync();
-                            output(t, v_slot, j != 0, 0, kChunks / 2);
-                        }
-                        if (!mbar_wait(p_ready + 8 * t, j & 1u, site, kStallMmaP, j)) {
-                            live = false;
-                            break;
-                        }
-                        tc_fence_after_sync();
-                        output(t, v_slot, j != 0, kSplitPublish ? kChunks / 2 : 0, kChunks);
-                        mma_commit<1>(o_done + 8 * t);
-                    }
-                    if (j + 1 < keys.blocks[t]) {
-                        if (!next_loaded) {
-                            if (!mbar_wait(kv_full + 8 * k_slot, (k_use / kSlots) & 1u, site,
-                                           kStallMmaKv, k_use)) {
-                                live = false;
-                                break;
-                            }
-                            tc_fence_after_sync();
-                            next_loaded = true;
-                        }
-                        scores(t, k_slot);
+                }
+            }
+            uint32_t fill = 0;  // ring position of K(0) of the current item
+            if (have && wait_kv(fill)) {
+                for (uint32_t t = 0; live && t < kTiles; ++t)
+                    if (work.blocks[t]) first_scores(work, t, fill);
+                if (live) mma_commit<1>(kv_empty + 8 * (fill % kSlots));
+            }
+            while (have && live) {
+                bool have_next = false;
+                while (work_at(problem, cta, ctas, visit, next)) {
+                    ++visit;
+                    if (next.most) {
+                        have_next = true;
+                        break;
                     }
                 }
-                if (!live) break;
-                mma_commit<1>(kv_empty + 8 * v_slot);
-                if (more) mma_commit<1>(kv_empty + 8 * k_slot);
+                const uint32_t next_fill = fill + 2 * work.most;
+                for (uint32_t j = 0; live && j < work.most; ++j) {
+                    const uint32_t v_use = fill + 2 * j + 1, k_use = fill + 2 * j + 2;
+                    const uint32_t v_slot = v_use % kSlots, k_slot = k_use % kSlots;
+                    const bool last = j + 1 == work.most;
+                    if (!wait_kv(v_use)) break;
+                    bool k_loaded = false;
+                    for (uint32_t t = 0; live && t < kTiles; ++t) {
+                        if (j < work.blocks[t]) {
+                            if (j == 0) {
+                                // The team has read the previous item's accumulator out.
+                                if (!mbar_wait(o_free + 8 * t, (started[t] & 1u), site_mma, kStallMmaOutput, started[t])) {
+                                    live = false;
+                                    break;
+                                }
+                                tc_fence_after_sync();
+                            }
+#pragma unroll
+                            for (uint32_t part = 0; part < kParts; ++part) {
+                                if (!mbar_wait(p_ready + 8 * (kParts * t + part), blocks_done[t] & 1u, site_mma, kStallMmaP,
+                                               blocks_done[t])) {
+                                    live = false;
+                                    break;
+                                }
+                                tc_fence_after_sync();
+                                output(t, v_slot, j != 0, 2 * run_first(part), 2 * run_first(part + 1));
+                            }
+                            if (!live) break;
+                            mma_commit<1>(o_done + 8 * t);
+                            ++blocks_done[t];
+                        }
+                        if (j + 1 < work.blocks[t]) {
+                            if (!k_loaded) {
+                                if (!wait_kv(k_use)) break;
+                                k_loaded = true;
+                            }
+                            scores(t, k_slot);
+                            if (j + 2 == work.blocks[t]) mma_commit<1>(q_empty + 8 * t);  // Q_t's last reader
+                        }
+                        // Right behind this item's last P.V of the tile: the next item's first S_t.
+                        if (last && have_next && next.blocks[t]) {
+                            if (!k_loaded) {
+                                if (!wait_kv(next_fill)) break;
+                                k_loaded = true;
+                            }
+                            first_scores(next, t, next_fill);
+                        }
+                    }
+                    if (!live) break;
+                    mma_commit<1>(kv_empty + 8 * v_slot);
+                    if (!last) mma_commit<1>(kv_empty + 8 * k_slot);
+                    if (last && have_next) mma_commit<1>(kv_empty + 8 * (next_fill % kSlots));
+                }
+                fill = next_fill;
+                work = next;
+                have = have_next;
             }
         }
       }
     } else {
         setmaxnreg_inc<kSoftmaxRegisters>();
-        // ------------------------------------------------ softmax, correction, epilogue
+        // ------------------------------------------------ softmax, correction, read-out
         // One team of four warps per query tile, one thread per row: no value ever crosses
         // threads. The two teams share the four schedulers (warps w and w + 4 sit on the same
         // one) and are in different phases of their tiles, so one team's exponentials run while
@@ -335,141 +477,147 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t t = warp / kTeamWarps;       // query tile of this team
         const uint32_t quadrant = warp & 3u;        // tensor-memory lanes this warp may touch
         const uint32_t row = 32 * quadrant + lane;  // row of the tile this thread owns
-        const uint32_t blocks = keys.blocks[t];
         const uint32_t lane_base = (32 * quadrant) << 16;
         const uint32_t s_tmem = tmem + lane_base + kScoreColumn + kBlockKeys * t;
         const uint32_t o_tmem = tmem + lane_base + kOutputColumn + kHead * t;
         const float scale_log2 = scale * 1.4426950408889634f;
         const float2 scale2 = make_float2(scale_log2, scale_log2);
 
-        float row_max = -INFINITY;  // raw score units
-        float row_sum = 0.0f;
-        bool live = blocks != 0;
+        uint32_t g = 0;  // key blocks this team has seen, all items: the parity of its barriers
+        bool live = true;
+        Work work;
+        for (uint32_t visit = 0; live && work_at(problem, cta, ctas, visit, work); ++visit) {
+            const uint32_t blocks = work.blocks[t];
+            if (blocks == 0) continue;
+            float row_max = -INFINITY;  // raw score units
+            float row_sum = 0.0f;
 
-        for (uint32_t j = 0; live && j < blocks; ++j) {
-            if (!mbar_wait(s_full + 8 * t, j & 1u, site, kStallSoftmaxS, j)) {
+            for (uint32_t j = 0; live && j < blocks; ++j, ++g) {
+                if (!mbar_wait(s_full + 8 * t, g & 1u, site_softmax, kStallSoftmaxS, g)) {
+                    live = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                uint32_t raw_s[4][32];
+#pragma unroll
+                for (uint32_t c = 0; c < 4; ++c) tmem_ld_32x32(s_tmem + 32 * c, raw_s[c]);
+                tmem_wait_ld();
+
+                if (causal && j + 1 == blocks) {
+                    // Diagonal block: key (128 j + c) is visible to query (tile start + row) iff c <= row.
+#pragma unroll
+                    for (uint32_t c = 0; c < 4; ++c)
+#pragma unroll
+                        for (uint32_t i = 0; i < 32; ++i)
+                            if (32 * c + i > row) raw_s[c][i] = 0xff800000u;  // -inf
+                }
+
+                float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+                for (uint32_t i = 0; i < 16; ++i) {
+                    m0 = max3(m0, __uint_as_float(raw_s[0][2 * i]), __uint_as_float(raw_s[0][2 * i + 1]));
+                    m1 = max3(m1, __uint_as_float(raw_s[1][2 * i]), __uint_as_float(raw_s[1][2 * i + 1]));
+                    m2 = max3(m2, __uint_as_float(raw_s[2][2 * i]), __uint_as_float(raw_s[2][2 * i + 1]));
+                    m3 = max3(m3, __uint_as_float(raw_s[3][2 * i]), __uint_as_float(raw_s[3][2 * i + 1]));
+                }
+                const float new_max = max3(row_max, fmaxf(m0, m1), fmaxf(m2, m3));
+                const bool moved = (new_max - row_max) * scale_log2 > kRescaleThreshold;
+                if (__any_sync(0xffffffffu, moved)) {
+                    // Refresh this warp's maxima; rows whose max did not move scale by 1. A stale
+                    // max is used consistently for P, the row sum and the log-sum-exp, so the
+                    // result does not depend on when the refresh happens.
+                    const float factor = ex2_approx((row_max - new_max) * scale_log2);
+                    if (j > 0) {
+                        if (!mbar_wait(o_done + 8 * t, (g - 1) & 1u, site_softmax, kStallSoftmaxO, g)) {
+                            live = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+#pragma unroll 1
+                        for (uint32_t c = 0; c < 4; ++c) {
+                            uint32_t o[32];
+                            tmem_ld_32x32(o_tmem + 32 * c, o);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (uint32_t i = 0; i < 32; ++i)
+                                o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+                            tmem_st_32x32(o_tmem + 32 * c, o);
+                        }
+                        tmem_wait_st();
+                    }
+                    row_sum *= factor;
+                    row_max = new_max;
+                }
+
+                const float shift = row_max * scale_log2;
+                const float2 shift2 = make_float2(-shift, -shift);
+                // Four independent sum chains: with two, the compiler recycles the registers the
+                // exponentials land in so tightly that every ex2 waits out the one before it and
+                // the loop runs at half the unit's rate.
+                float2 sum_a = make_float2(0.0f, 0.0f), sum_b = make_float2(0.0f, 0.0f);
+                float2 sum_c = make_float2(0.0f, 0.0f), sum_d = make_float2(0.0f, 0.0f);
+#pragma unroll
+                for (uint32_t c = 0; c < 4; ++c) {
+                    // 32 keys -> 16 packed bf16 pairs, written over S columns this thread has read.
+                    uint32_t packed[16];
+#pragma unroll
+                    for (uint32_t i = 0; i < 16; ++i) {
+                        const float2 x = __ffma2_rn(make_float2(__uint_as_float(raw_s[c][2 * i]),
+                                                                __uint_as_float(raw_s[c][2 * i + 1])),
+                                                    scale2, shift2);
+                        float2 p;
+                        if ((kPolyMask >> i) & 1u) {
+                            p = exp2_pair_fma(x);
+                        } else {
+                            p.x = ex2_approx(x.x);
+                            p.y = ex2_approx(x.y);
+                        }
+                        if ((i & 3u) == 0)
+                            sum_a = __fadd2_rn(sum_a, p);
+                        else if ((i & 3u) == 1)
+                            sum_b = __fadd2_rn(sum_b, p);
+                        else if ((i & 3u) == 2)
+                            sum_c = __fadd2_rn(sum_c, p);
+                        else
+                            sum_d = __fadd2_rn(sum_d, p);
+                        packed[i] = pack_bf16x2(p.x, p.y);
+                    }
+                    tmem_st_32x16(s_tmem + 16 * c, packed);
+                    if ((kPublishMask >> c) & 1u) {
+                        if (c == 3)
+                            row_sum += ((sum_a.x + sum_b.x) + (sum_c.x + sum_d.x)) +
+                                       ((sum_a.y + sum_b.y) + (sum_c.y + sum_d.y));
+                        tmem_wait_st();
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(p_ready + 8 * (kParts * t + run_of(c)));
+                    }
+                }
+            }
+            if (!live) break;
+
+            // The item's last P.V has retired: read the accumulator out and store the rows.
+            if (!mbar_wait(o_done + 8 * t, (g - 1) & 1u, site_softmax, kStallSoftmaxO, g)) {
                 live = false;
                 break;
             }
             tc_fence_after_sync();
-            uint32_t raw_s[4][32];
-#pragma unroll
-            for (uint32_t c = 0; c < 4; ++c) tmem_ld_32x32(s_tmem + 32 * c, raw_s[c]);
-            tmem_wait_ld();
-
-            if (causal && j + 1 == blocks) {
-                // Diagonal block: key (128 j + c) is visible to query (tile start + row) iff c <= row.
-#pragma unroll
-                for (uint32_t c = 0; c < 4; ++c)
-#pragma unroll
-                    for (uint32_t i = 0; i < 32; ++i)
-                        if (32 * c + i > row) raw_s[c][i] = 0xff800000u;  // -inf
-            }
-
-            float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
-#pragma unroll
-            for (uint32_t i = 0; i < 16; ++i) {
-                m0 = max3(m0, __uint_as_float(raw_s[0][2 * i]), __uint_as_float(raw_s[0][2 * i + 1]));
-                m1 = max3(m1, __uint_as_float(raw_s[1][2 * i]), __uint_as_float(raw_s[1][2 * i + 1]));
-                m2 = max3(m2, __uint_as_float(raw_s[2][2 * i]), __uint_as_float(raw_s[2][2 * i + 1]));
-                m3 = max3(m3, __uint_as_float(raw_s[3][2 * i]), __uint_as_float(raw_s[3][2 * i + 1]));
-            }
-            const float new_max = max3(row_max, fmaxf(m0, m1), fmaxf(m2, m3));
-            const bool moved = (new_max - row_max) * scale_log2 > kRescaleThreshold;
-            if (__any_sync(0xffffffffu, moved)) {
-                // Refresh this warp's maxima; rows whose max did not move scale by 1. A stale
-                // max is used consistently for P, the row sum and the log-sum-exp, so the result
-                // does not depend on when the refresh happens.
-                const float factor = ex2_approx((row_max - new_max) * scale_log2);
-                if (j > 0) {
-                    if (!mbar_wait(o_done + 8 * t, (j - 1) & 1u, site, kStallSoftmaxO, j)) {
-                        live = false;
-                        break;
-                    }
-                    tc_fence_after_sync();
-#pragma unroll 1
-                    for (uint32_t c = 0; c < 4; ++c) {
-                        uint32_t o[32];
-                        tmem_ld_32x32(o_tmem + 32 * c, o);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (uint32_t i = 0; i < 32; ++i)
-                            o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
-                        tmem_st_32x32(o_tmem + 32 * c, o);
-                    }
-                    tmem_wait_st();
-                }
-                row_sum *= factor;
-                row_max = new_max;
-            }
-
-            const float shift = row_max * scale_log2;
-            const float2 shift2 = make_float2(-shift, -shift);
-            // Four independent sum chains: with two, the compiler recycles the registers the
-            // exponentials land in so tightly that every ex2 waits out the one before it and
-            // the loop runs at half the unit's rate.
-            float2 sum_a = make_float2(0.0f, 0.0f), sum_b = make_float2(0.0f, 0.0f);
-            float2 sum_c = make_float2(0.0f, 0.0f), sum_d = make_float2(0.0f, 0.0f);
-#pragma unroll
-            for (uint32_t c = 0; c < 4; ++c) {
-                // 32 keys -> 16 packed bf16 pairs, written over S columns this thread has read.
-                uint32_t packed[16];
-#pragma unroll
-                for (uint32_t i = 0; i < 16; ++i) {
-                    const float2 x = __ffma2_rn(make_float2(__uint_as_float(raw_s[c][2 * i]),
-                                                            __uint_as_float(raw_s[c][2 * i + 1])),
-                                                scale2, shift2);
-                    float2 p;
-                    if ((kPolyMask >> i) & 1u) {
-                        p = exp2_pair_fma(x);
-                    } else {
-                        p.x = ex2_approx(x.x);
-                        p.y = ex2_approx(x.y);
-                    }
-                    if ((i & 3u) == 0)
-                        sum_a = __fadd2_rn(sum_a, p);
-                    else if ((i & 3u) == 1)
-                        sum_b = __fadd2_rn(sum_b, p);
-                    else if ((i & 3u) == 2)
-                        sum_c = __fadd2_rn(sum_c, p);
-                    else
-                        sum_d = __fadd2_rn(sum_d, p);
-                    packed[i] = pack_bf16x2(p.x, p.y);
-                }
-                tmem_st_32x16(s_tmem + 16 * c, packed);
-                if (kSplitPublish && c == 1) {
-                    tmem_wait_st();
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(p_half + 8 * t);
-                }
-            }
-            row_sum += ((sum_a.x + sum_b.x) + (sum_c.x + sum_d.x)) + ((sum_a.y + sum_b.y) + (sum_c.y + sum_d.y));
-            tmem_wait_st();
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(p_ready + 8 * t);
-        }
-
-        if (live) live = mbar_wait(o_done + 8 * t, (blocks - 1) & 1u, site, kStallSoftmaxO, blocks);
-        if (live) {
-            tc_fence_after_sync();
             const float inverse = 1.0f / row_sum;
-            const uint32_t q_index = q_row0 + kTileRows * t + row;
-            if (lse)
-                lse[static_cast<size_t>(plane) * seq + q_index] =
-                    (row_max * scale_log2 + lg2_approx(row_sum)) * 0.6931471805599453f;
-            // Q_t's shared tile is dead once the last MMA retired: it stages the output. This
-            // warp owns rows [32 q, 32 q + 32) of both [128, 64] subtiles.
-            const uint32_t stage = q_tiles + t * kBlockBytes;
-#pragma unroll 1
+            const size_t q_index = static_cast<size_t>(work.plane) * seq + work.q_row0 + kTileRows * t + row;
+            if (lse) lse[q_index] = (row_max * scale_log2 + lg2_approx(row_sum)) * 0.6931471805599453f;
+#pragma unroll
             for (uint32_t c = 0; c < 4; ++c) {
                 uint32_t o[32];
                 tmem_ld_32x32(o_tmem + 32 * c, o);
                 tmem_wait_ld();
+                if (c == 3) {
+                    // Everything is in registers: the MMA thread may overwrite the accumulator.
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(o_free + 8 * t);
+                }
                 if (o_f32) {
-                    float4* out = reinterpret_cast<float4*>(
-                        o_f32 + (static_cast<size_t>(plane) * seq + q_index) * kHead + 32 * c);
+                    float4* out = reinterpret_cast<float4*>(o_f32 + q_index * kHead + 32 * c);
 #pragma unroll
                     for (uint32_t i = 0; i < 8; ++i)
                         out[i] = make_float4(__uint_as_float(o[4 * i]) * inverse,
@@ -477,35 +625,21 @@ __global__ void __launch_bounds__(kThreads, 1)
                                              __uint_as_float(o[4 * i + 2]) * inverse,
                                              __uint_as_float(o[4 * i + 3]) * inverse);
                 } else {
-                    const uint32_t subtile = stage + (c / 2) * kSubtileBytes;
+                    // A thread's row is 256 contiguous bytes of the output: 16-byte stores, every
+                    // 32-byte sector written whole by two consecutive ones.
+                    uint16_t* out = o_bf16 + q_index * kHead + 32 * c;
 #pragma unroll
                     for (uint32_t i = 0; i < 4; ++i) {
                         const uint32_t* v = o + 8 * i;
-                        st_shared_v4(subtile + swizzled_chunk_offset(row, 4 * (c % 2) + i, 0),
-                                     pack_bf16x2(__uint_as_float(v[0]) * inverse,
-                                                 __uint_as_float(v[1]) * inverse),
-                                     pack_bf16x2(__uint_as_float(v[2]) * inverse,
-                                                 __uint_as_float(v[3]) * inverse),
-                                     pack_bf16x2(__uint_as_float(v[4]) * inverse,
-                                                 __uint_as_float(v[5]) * inverse),
-                                     pack_bf16x2(__uint_as_float(v[6]) * inverse,
-                                                 __uint_as_float(v[7]) * inverse));
+                        st_global_v4(out + 8 * i,
+                                     pack_bf16x2(__uint_as_float(v[0]) * inverse, __uint_as_float(v[1]) * inverse),
+                                     pack_bf16x2(__uint_as_float(v[2]) * inverse, __uint_as_float(v[3]) * inverse),
+                                     pack_bf16x2(__uint_as_float(v[4]) * inverse, __uint_as_float(v[5]) * inverse),
+                                     pack_bf16x2(__uint_as_float(v[6]) * inverse, __uint_as_float(v[7]) * inverse));
                     }
                 }
             }
-            if (!o_f32) {
-                fence_proxy_async_shared();
-                __syncwarp();
-                if (lane == 0) {
-                    const int out_row = static_cast<int>(q_row0 + kTileRows * t + 32 * quadrant);
-                    for (uint32_t half = 0; half < 2; ++half)
-                        tma_store_3d(&o_map, stage + half * kSubtileBytes + 32 * quadrant * 128,
-                                     static_cast<int>(64 * half), out_row, static_cast<int>(plane));
-                    tma_store_commit();
-                }
-            }
         }
-        if (lane == 0) tma_store_wait_before_exit();
     }
 
     // ---------------------------------------------------- teardown
@@ -530,28 +664,42 @@ extern "C" uint32_t fk_flash_shared_bytes(void) { return flash::kSharedBytes; }
 extern "C" uint32_t fk_flash_threads(void) { return flash::kThreads; }
 
 extern "C" int fk_flash_fwd_launch(const void* q_map, const void* k_map, const void* v_map,
-                                   const void* o_map, float* o_f32, float* lse, uint32_t planes,
+                                   void* o_bf16, float* o_f32, float* lse, uint32_t planes,
                                    uint32_t seq, float scale, int causal, void* stream,
                                    uint32_t* device_status) {
-    if (!q_map || !k_map || !v_map || (!o_map && !o_f32))
-        return fk_fail(FK_ERR_INVALID, "a tensor map pointer is null");
+    if (!q_map || !k_map || !v_map) return fk_fail(FK_ERR_INVALID, "a tensor map pointer is null");
+    if (!o_bf16 && !o_f32) return fk_fail(FK_ERR_INVALID, "an operand pointer is null");
     if (seq == 0 || seq % flash::kTileRows || planes == 0)
         return fk_fail(FK_ERR_SHAPE,
                        "%u queries x %u heads does not divide the %u queries a tile owns", seq,
                        planes, flash::kTileRows);
-    if (planes > 65535) return fk_fail(FK_ERR_SHAPE, "%u planes is past the 65535 a launch takes", planes);
+    if (reinterpret_cast<uintptr_t>(o_bf16) & 15u || reinterpret_cast<uintptr_t>(o_f32) & 15u)
+        return fk_fail(FK_ERR_ALIGNMENT, "the output wants 16-byte alignment");
+    const uint32_t rows_per_item = flash::kTiles * flash::kTileRows;
+    flash::Problem problem;
+    problem.seq = seq;
+    problem.planes = planes;
+    problem.pairs = (seq + rows_per_item - 1) / rows_per_item;
+    problem.causal = causal ? 1u : 0u;
+    if (static_cast<uint64_t>(causal ? (problem.pairs + 1) / 2 : problem.pairs) * planes > 0x7fffffffull)
+        return fk_fail(FK_ERR_SHAPE, "%u planes x %u queries is more work items than a launch walks", planes, seq);
+    problem.items = flash::item_count(problem.pairs, planes, causal != 0);
+
+    DeviceFacts facts;
+    const int known = device_facts(&facts);
+    if (known != FK_OK) return known;
     uint32_t limit = 0;
     const int admitted = fk_admit_shared_plan(
         reinterpret_cast<const void*>(flash::flash_forward_kernel), flash::kSharedBytes, &limit);
     if (admitted != FK_OK) return admitted;
-    const uint32_t rows_per_cta = flash::kTiles * flash::kTileRows;
-    const dim3 grid((seq + rows_per_cta - 1) / rows_per_cta, planes, 1);
-    const CUtensorMap* store = static_cast<const CUtensorMap*>(o_map ? o_map : q_map);
+    // One persistent CTA per SM (the plan and the 512 tensor-memory columns admit exactly one).
+    const uint32_t sms = static_cast<uint32_t>(facts.sm_count);
+    const dim3 grid(problem.items < sms ? problem.items : sms, 1, 1);
     flash::flash_forward_kernel<<<grid, flash::kThreads, flash::kSharedBytes,
                                   static_cast<cudaStream_t>(stream)>>>(
         *static_cast<const CUtensorMap*>(q_map), *static_cast<const CUtensorMap*>(k_map),
-        *static_cast<const CUtensorMap*>(v_map), *store, o_f32, lse, seq, scale, causal ? 1u : 0u,
-        device_status);
+        *static_cast<const CUtensorMap*>(v_map), o_f32 ? nullptr : static_cast<uint16_t*>(o_bf16), o_f32, lse,
+        problem, scale, device_status);
     FK_CUDA(cudaGetLastError());
     return FK_OK;
 }
@@ -565,7 +713,7 @@ extern "C" int fk_flash_fwd(const void* q, const void* k, const void* v, void* o
         return fk_fail(FK_ERR_SHAPE,
                        "%u queries x %u heads does not divide the %u queries a tile owns", seq,
                        planes, flash::kTileRows);
-    alignas(64) CUtensorMap maps[4];
+    alignas(64) CUtensorMap maps[3];
     int status = fk_encode_bf16_panels(&maps[0], reinterpret_cast<uint64_t>(q), flash::kTileRows,
                                        flash::kHead, seq, planes);
     if (status == FK_OK)
@@ -574,13 +722,9 @@ extern "C" int fk_flash_fwd(const void* q, const void* k, const void* v, void* o
     if (status == FK_OK)
         status = fk_encode_bf16_panels(&maps[2], reinterpret_cast<uint64_t>(v), flash::kBlockKeys,
                                        flash::kHead, seq, planes);
-    if (status == FK_OK && o_bf16)
-        status = fk_encode_bf16_panels(&maps[3], reinterpret_cast<uint64_t>(o_bf16), 32, flash::kHead,
-                                       seq, planes);
     if (status != FK_OK) return status;
-    return fk_flash_fwd_launch(&maps[0], &maps[1], &maps[2], o_bf16 ? &maps[3] : nullptr,
-                               o_bf16 ? nullptr : o_f32, lse, planes, seq, scale, causal, stream,
-                               device_status);
+    return fk_flash_fwd_launch(&maps[0], &maps[1], &maps[2], o_bf16, o_bf16 ? nullptr : o_f32, lse, planes, seq,
+                               scale, causal, stream, device_status);
 }
 
 // One call at a time per device, like fk_gemm_bf16_host: the staging buffers and status words are

@@ -16,9 +16,16 @@ HEAD = 128
 SCALE = 0.125
 
 
-def grid(sequence: int, planes: int) -> int:
-    """CTAs of a launch: one per pair of 128-row query tiles per plane."""
-    return (sequence + 2 * QUERIES - 1) // (2 * QUERIES) * planes
+def items(sequence: int, planes: int, causal: bool = False) -> int:
+    """Work items of a launch: one per pair of 128-row query tiles per plane; under a causal
+    mask a heavy and a light query block of one plane share an item, so half as many."""
+    pairs = (sequence + 2 * QUERIES - 1) // (2 * QUERIES)
+    return ((pairs + 1) // 2 if causal else pairs) * planes
+
+
+def grid(sequence: int, planes: int, sm_count: int = 148, causal: bool = False) -> int:
+    """CTAs of a launch: one persistent CTA per SM, fewer when there are fewer work items."""
+    return min(items(sequence, planes, causal), sm_count)
 
 
 def _require(name: str, tensor: torch.Tensor) -> None:

@@ -216,13 +216,14 @@ int fk_gemm_bf16_host_noalloc(const uint16_t* a_host, const uint16_t* b_host, ui
  * guards (examples/src/flash_forward.rs:151-158, 477-483), widened to a batch,
  * a non-causal mode, bf16 output and a log-sum-exp vector. Q, K, V and O are
  * packed [planes = batch*heads, seq, 128] bf16; lse is [planes, seq] fp32
- * (natural log), may be null. `o_f32`, when non-null, receives the output as
- * fp32 [planes, seq, 128] (the reference kernel's own output type) instead of
- * bf16 through `o_map`.
+ * (natural log), may be null. Like the reference kernel's `out`, the output is a
+ * device pointer the kernel stores rows through: `o_bf16` ([planes, seq, 128]
+ * bf16, 16-byte aligned), or, when `o_f32` is non-null, fp32 [planes, seq, 128]
+ * (the reference kernel's own output type) instead.
  *   q_map / k_map / v_map: fk_encode_bf16_panels(base, 128 box rows, 128, seq, planes)
- *   o_map:                 fk_encode_bf16_panels(base,  32 box rows, 128, seq, planes)
- * Requires seq % 128 == 0, planes >= 1. `device_status` as for the GEMM. */
-int fk_flash_fwd_launch(const void* q_map, const void* k_map, const void* v_map, const void* o_map,
+ * Requires seq % 128 == 0, planes >= 1. One persistent CTA per SM walks the
+ * (query block, plane) items. `device_status` as for the GEMM. */
+int fk_flash_fwd_launch(const void* q_map, const void* k_map, const void* v_map, void* o_bf16,
                         float* o_f32, float* lse, uint32_t planes, uint32_t seq, float scale,
                         int causal, void* stream, uint32_t* device_status);
 

@@ -220,9 +220,7 @@ inline void run(void* stream, uint64_t q, uint64_t k, uint64_t v, uint64_t o_bf1
     const auto q_map = global::encode_bf16_panels<QUERIES, HEAD>(q, sequence, planes);
     const auto k_map = global::encode_bf16_panels<KEYS, HEAD>(k, sequence, planes);
     const auto v_map = global::encode_bf16_panels<KEYS, HEAD>(v, sequence, planes);
-    global::PanelMap o_map{};
-    if (o_bf16) o_map = global::encode_bf16_panels<32, HEAD>(o_bf16, sequence, planes);
-    check(fk_flash_fwd_launch(q_map.as_ptr(), k_map.as_ptr(), v_map.as_ptr(), o_bf16 ? o_map.as_ptr() : nullptr,
+    check(fk_flash_fwd_launch(q_map.as_ptr(), k_map.as_ptr(), v_map.as_ptr(), reinterpret_cast<void*>(o_bf16),
                               o_bf16 ? nullptr : o_f32, lse, planes, sequence, scale, causal ? 1 : 0, stream, status));
 }
 
