@@ -119,3 +119,90 @@ def run_host_noalloc(a, b, c, m: int, n: int, k: int, group: int = GROUP) -> Non
     def address(x):
         return x.data_ptr() if hasattr(x, "data_ptr") else x.ctypes.data
     check(library().fk_gemm_bf16_host_noalloc(address(a), address(b), address(c), m, n, k, group))
+
+
+class ShardedHostGemm:
+    """``C[:, n0:n1] = A . B[n0:n1]^T`` from HOST buffers on every rank of a node, A replicated.
+
+    The call a multi-GPU user of the host-buffer path makes. Each rank passes only ITS share of
+    A's rows (``shard.a_rows``), its block of B's rows (``shard.gemm_columns``) and receives its
+    column block of C: A crosses PCIe once in total instead of once per rank. Per block of rows
+    (``shard.gather_blocks``) the pipeline is upload -> all-gather into this GPU's own memory
+    (``torch.distributed``, NCCL over NVLink) -> GEMM over the gathered block -> read-back, on four
+    streams, so the copies, the gather and the kernels of different blocks overlap. The kernels read
+    local memory only; the gather is staging. With one rank it is ``run_host``'s pipeline without
+    the gather. Buffers and streams are made once, here; ``run`` allocates nothing.
+    """
+
+    def __init__(self, m: int, n_local: int, k: int, world: int, rank: int, device, group: int = GROUP,
+                 blocks: int = 4, process_group=None):
+        from . import shard
+
+        self.m, self.n, self.k, self.world, self.rank, self.group = m, n_local, k, world, rank, group
+        self.device = torch.device(device)
+        self.process_group = process_group
+        self.row0, self.row1 = shard.a_rows(m, world, rank)
+        self.share = self.row1 - self.row0
+        self.blocks = shard.gather_blocks(m, world, blocks)
+        bf16 = dict(dtype=torch.bfloat16, device=self.device)
+        self.b = torch.empty((n_local, k), **bf16)
+        self.own = [torch.empty((rows, k), **bf16) for _, rows in self.blocks]
+        self.gathered = ([torch.empty((world, rows, k), **bf16) for _, rows in self.blocks] if world > 1
+                         else [own.unsqueeze(0) for own in self.own])
+        self.c = [torch.empty((world * rows, n_local), **bf16) for _, rows in self.blocks]
+        self.status = new_status(self.device)
+        with torch.cuda.device(self.device):
+            self.upload, self.comm, self.compute, self.download = (torch.cuda.Stream() for _ in range(4))
+
+    def run(self, a_share: torch.Tensor, b_block: torch.Tensor, c_out: torch.Tensor) -> None:
+        """``a_share`` [share, k], ``b_block`` [n_local, k], ``c_out`` [m, n_local]: pinned host bf16
+        tensors. Returns once ``c_out`` is complete on the host."""
+        import torch.distributed as dist
+
+        if a_share.shape != (self.share, self.k) or b_block.shape != (self.n, self.k) or c_out.shape != (self.m, self.n):
+            raise ValueError("host operands do not have this plan's shapes")
+        with torch.cuda.device(self.device):
+            start = torch.cuda.Event()
+            start.record(torch.cuda.current_stream())
+            for stream in (self.upload, self.comm, self.compute, self.download):
+                stream.wait_event(start)
+            with torch.cuda.stream(self.compute):
+                self.status.zero_()
+            with torch.cuda.stream(self.upload):
+                self.b.copy_(b_block, non_blocking=True)
+                b_ready = torch.cuda.Event()
+                b_ready.record(self.upload)
+            self.compute.wait_event(b_ready)
+            for index, (offset, rows) in enumerate(self.blocks):
+                with torch.cuda.stream(self.upload):
+                    self.own[index].copy_(a_share[offset:offset + rows], non_blocking=True)
+                    landed = torch.cuda.Event()
+                    landed.record(self.upload)
+                whole = landed
+                if self.world > 1:
+                    with torch.cuda.stream(self.comm):
+                        self.comm.wait_event(landed)
+                        dist.all_gather_into_tensor(self.gathered[index], self.own[index], group=self.process_group)
+                        whole = torch.cuda.Event()
+                        whole.record(self.comm)
+                with torch.cuda.stream(self.compute):
+                    self.compute.wait_event(whole)
+                    a_block = self.gathered[index].view(self.world * rows, self.k)
+                    check(library().fk_gemm_bf16(a_block.data_ptr(), self.b.data_ptr(), self.c[index].data_ptr(),
+                                                 self.world * rows, self.n, self.k, self.n, self.group,
+                                                 self.compute.cuda_stream, self.status.data_ptr()))
+                    computed = torch.cuda.Event()
+                    computed.record(self.compute)
+                with torch.cuda.stream(self.download):
+                    self.download.wait_event(computed)
+                    for slab in range(self.world):
+                        first = slab * self.share + offset
+                        c_out[first:first + rows].copy_(self.c[index][slab * rows:(slab + 1) * rows], non_blocking=True)
+            # Every wait carries the launch deadline (FK_ERR_TIMEOUT instead of a hang).
+            for stream in (self.upload, self.comm, self.compute, self.download):
+                check(library().fk_wait_stream(stream.cuda_stream, library().fk_launch_budget_ms()))
+            check(library().fk_status_check(self.status.data_ptr(), self.compute.cuda_stream))
+
+    def bytes_per_step(self) -> tuple[int, int]:
+        """(host-to-device, device-to-host) bytes one ``run`` copies on this rank."""
+        return (self.share * self.k + self.n * self.k) * 2, self.m * self.n * 2

@@ -2,10 +2,13 @@
 no collective on the data path.
 
 The GEMM replicates A and gives each rank a contiguous block of B's rows (C's
-columns) when the operands are resident on the device; from host buffers, where the upload
-is the cost, it cuts C into a grid of blocks instead (`gemm_grid`); attention (forward and backward) gives each rank a contiguous range of
-(batch x head) planes; the row kernels give each rank a contiguous range of whole
-128-row tiles.
+columns). When the operands start in HOST memory the replication is not paid for over
+PCIe: every rank uploads only its own share of A's rows (`a_rows`) and the ranks complete A
+in their own HBM over NVLink, block of rows by block of rows (`gather_blocks`), each block's
+GEMM starting as soon as it is whole -- staging, outside the kernels, which still read only
+their own GPU's memory. Attention (forward and backward) gives each rank a contiguous range
+of (batch x head) planes; the row kernels give each rank a contiguous range of whole 128-row
+tiles. `gemm_grid` / `gemm_block` describe the alternative of cutting C into a grid of blocks.
 """
 from __future__ import annotations
 
@@ -26,6 +29,43 @@ def gemm_columns(n: int, world: int, rank: int) -> tuple[int, int]:
     start = rank * base + min(rank, extra)
     stop = start + base + (1 if rank < extra else 0)
     return start * BLOCK_N, stop * BLOCK_N
+
+
+def a_rows(m: int, world: int, rank: int, tile: int = 2 * 128) -> tuple[int, int]:
+    """[start, stop) of the rows of A that rank ``rank`` uploads from host memory when A is
+    replicated by an all-gather instead of by ``world`` uploads: whole ``tile``-row pair tiles,
+    the same count on every rank (an all-gather moves equal shares)."""
+    if not 0 <= rank < world:
+        raise ValueError(f"rank {rank} is outside a world of {world}")
+    if m % (tile * world):
+        raise ValueError(f"{m} rows do not split into {world} equal shares of whole {tile}-row tiles")
+    share = m // world
+    return rank * share, (rank + 1) * share
+
+
+def gather_blocks(m: int, world: int, blocks: int, tile: int = 2 * 128) -> list[tuple[int, int]]:
+    """The all-gather schedule of a replicated A: ``[(offset, rows), ...]`` inside every rank's
+    share, at most ``blocks`` of them, each whole ``tile``-row tiles. Gathering block ``(offset,
+    rows)`` yields a ``[world, rows, k]`` buffer whose slab ``r`` is rows ``[r * share + offset,
+    r * share + offset + rows)`` of A -- and, after the GEMM over the buffer, of C."""
+    share = a_rows(m, world, 0, tile)[1]
+    tiles = share // tile
+    count = max(1, min(blocks, tiles))
+    base, extra = divmod(tiles, count)
+    out, offset = [], 0
+    for index in range(count):
+        rows = (base + (1 if index < extra else 0)) * tile
+        out.append((offset, rows))
+        offset += rows
+    return out
+
+
+def gathered_row(m: int, world: int, offset: int, rows: int, buffer_row: int) -> int:
+    """Row of A (and of C) that row ``buffer_row`` of the gathered ``[world * rows, k]`` buffer of
+    block ``(offset, rows)`` holds."""
+    share = m // world
+    slab, within = divmod(buffer_row, rows)
+    return slab * share + offset + within
 
 
 def gemm_grid(m: int, n: int, world: int, tile: int = BLOCK_N) -> tuple[int, int]:

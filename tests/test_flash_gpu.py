@@ -58,6 +58,12 @@ def test_reference_lattice_gate(device, sequence, heads):
     relative = np.abs((out.cpu().numpy().astype(np.float64) - expected) / expected)
     assert not np.isnan(relative).any()
     assert relative.max() <= 2 ** -8, f"worst relative error {relative.max():.3e}"
+    if (sequence, heads) == (256, 2):
+        # The reference states what a correct kernel measures through this very check: 1.66e-3 with its
+        # polynomial 2^x and 1.73e-3 with the ex2 unit (examples/src/flash_forward.rs:469-474) -- the
+        # floor is P's rounding to bf16, not the exponential. This kernel mixes both spellings of
+        # 2^x, so its worst error must land in the same narrow band, not merely under the gate.
+        assert 1.5e-3 <= relative.max() <= 1.9e-3, f"worst relative error {relative.max():.3e}"
 
 
 @pytest.mark.parametrize("causal", [False, True])
@@ -74,6 +80,29 @@ def test_seeded_random_within_tolerance(device, causal, shape):
     got = out.float().cpu().numpy().reshape(planes, sequence, 128).astype(np.float64)
     assert np.abs(got - expected).max() <= 2e-2
     assert np.abs(lse.cpu().numpy().reshape(planes, sequence) - expected_lse).max() <= 2e-2
+
+
+@pytest.mark.parametrize("planes, sequence, causal", [(80, 512, False), (100, 768, True), (170, 256, False),
+                                                      (160, 256, True)])
+def test_more_work_items_than_sms(device, planes, sequence, causal):
+    """The grid is one persistent CTA per SM: with more (query block, plane) items than SMs a CTA
+    walks several, carrying its barrier phases, its K/V ring position and the hand-over of the
+    output accumulator from one item to the next. Causal items are pairs of query blocks (three
+    blocks per plane: a pair and a lone middle block); 256 queries leave a single block per plane."""
+    generator = torch.Generator(device="cpu").manual_seed(11 + planes)
+    q, k, v = (torch.randn((planes, sequence, 128), generator=generator).to(torch.bfloat16) for _ in range(3))
+    out, lse = _run_checked(q.to(device), k.to(device), v.to(device), causal=causal)
+    rows = [0, 127, 128, sequence // 2 + 1, sequence - 1]
+    words = [_to_words(x) for x in (q, k, v)]
+    expected, expected_lse = _oracle_planes(*words, 128 ** -0.5, causal, rows=rows)
+    got = out.float().cpu().numpy().astype(np.float64)[:, rows]
+    assert np.abs(got - expected).max() <= 2e-2
+    assert np.abs(lse.cpu().numpy().astype(np.float64)[:, rows] - expected_lse).max() <= 2e-2
+    # every row of every plane, against fp32 attention over the same bf16 inputs
+    reference = torch.nn.functional.scaled_dot_product_attention(
+        q.to(device).float().unsqueeze(0), k.to(device).float().unsqueeze(0), v.to(device).float().unsqueeze(0),
+        is_causal=causal)[0]
+    assert (out.float() - reference).abs().max().item() <= 2e-2
 
 
 def test_moving_maximum_forces_rescales(device):

@@ -116,6 +116,25 @@ def test_host_buffer_entry_point(device, shape):
     assert wrong == 0
 
 
+@pytest.mark.parametrize("blocks", [1, 4])
+def test_host_buffer_pipeline_over_row_blocks(device, blocks):
+    """The multi-GPU host-buffer pipeline with a world of one (upload by row blocks, GEMM per block,
+    read-back; the all-gather between upload and GEMM is the only step a single rank skips): exact on
+    the reference's integer gate, twice in a row with the same buffers."""
+    m, n, k = 2048, 768, 256
+    a = torch.from_numpy(oracle.gemm_stage("a", m, k).view(np.int16)).view(torch.bfloat16).pin_memory()
+    b = torch.from_numpy(oracle.gemm_stage("b", n, k).view(np.int16)).view(torch.bfloat16).pin_memory()
+    c = torch.empty((m, n), dtype=torch.bfloat16).pin_memory()
+    plan = gemm.ShardedHostGemm(m, n, k, 1, 0, device, blocks=blocks)
+    assert plan.bytes_per_step() == ((m * k + n * k) * 2, m * n * 2)
+    for _ in range(2):
+        c.zero_()
+        plan.run(a, b, c)
+        assert oracle.gemm_check_c(c.view(torch.int16).numpy().view(np.uint16), m, n, k)[0] == 0
+    with pytest.raises(ValueError):
+        plan.run(a[:1024], b, c)
+
+
 @pytest.mark.parametrize("shape, seed, deviation", [((16384, 16384, 16384), 1, None), ((8192, 28672, 8192), 2, 0.02)])
 def test_full_size_properties(device, shape, seed, deviation):
     """At the benchmark's sizes (the 16384-cubed case with N(0, 1)/sqrt(K) entries, the 8192 x 28672

@@ -47,6 +47,33 @@ def test_gemm_blocks_tile_c_and_upload_least(world):
     assert shard.gemm_grid(m, n, 8) == (2, 4) and shard.gemm_grid(m, n, 2) == (1, 2)
 
 
+@pytest.mark.parametrize("m, world, blocks", [(16384, 8, 4), (16384, 2, 4), (16384, 1, 16), (8192, 4, 3), (1024, 2, 8),
+                                              (512, 2, 4), (1536, 3, 2)])
+def test_gathered_row_blocks_cover_a_once(m, world, blocks):
+    """A replicated by all-gather: the ranks' shares tile A, the blocks tile a share in whole 256-row
+    tiles, and every row of A appears in exactly one row of exactly one gathered buffer."""
+    shares = [shard.a_rows(m, world, rank) for rank in range(world)]
+    assert shares[0][0] == 0 and shares[-1][1] == m
+    assert all(a[1] == b[0] for a, b in zip(shares, shares[1:]))
+    assert len({stop - start for start, stop in shares}) == 1
+    plan = shard.gather_blocks(m, world, blocks)
+    assert 1 <= len(plan) <= blocks
+    assert plan[0][0] == 0 and all(a[0] + a[1] == b[0] for a, b in zip(plan, plan[1:]))
+    assert plan[-1][0] + plan[-1][1] == m // world and all(rows % 256 == 0 and rows > 0 for _, rows in plan)
+    seen = np.zeros(m, dtype=np.int32)
+    for offset, rows in plan:
+        for buffer_row in range(world * rows):
+            seen[shard.gathered_row(m, world, offset, rows, buffer_row)] += 1
+    assert (seen == 1).all()
+
+
+def test_a_rows_refuses_unequal_shares():
+    with pytest.raises(ValueError):
+        shard.a_rows(768, 2, 0)  # 1.5 tiles each
+    with pytest.raises(ValueError):
+        shard.a_rows(1024, 2, 2)
+
+
 def test_planes_tile_the_batch():
     for total, world in [(256, 8), (128, 8), (6, 4), (1, 2)]:
         blocks = [shard.planes(total, world, rank) for rank in range(world)]
@@ -90,6 +117,50 @@ def _worker(rank: int, world: int, port: int, results):
             results.put((oracle.gemm_check_c(whole, m, n, k)[0], float(seconds.item())))
     finally:
         dist.destroy_process_group()
+
+
+def _gather_worker(rank: int, world: int, port: int, results):
+    """The host-buffer pipeline's bookkeeping with gloo standing in for NCCL and the oracle for
+    the kernel: each rank holds only its share of A, the blocks are all-gathered, the GEMM of a
+    gathered buffer lands in the rows `gathered_row` names."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        m, n, k = 1024, 512, 128
+        a_whole, b = oracle.gemm_stage("a", m, k), oracle.gemm_stage("b", n, k)
+        row0, row1 = shard.a_rows(m, world, rank)
+        a_share = torch.from_numpy(a_whole[row0:row1].astype(np.int32))  # this rank never touches the rest
+        start, stop = shard.gemm_columns(n, world, rank)
+        c_block = np.zeros((m, stop - start), dtype=np.uint16)
+        for offset, rows in shard.gather_blocks(m, world, 2):
+            gathered = torch.empty((world * rows, k), dtype=torch.int32)
+            dist.all_gather_into_tensor(gathered, a_share[offset:offset + rows].contiguous())
+            product, _ = oracle.gemm_rows(gathered.numpy().astype(np.uint16), b[start:stop], 0, world * rows)
+            for buffer_row in range(world * rows):
+                c_block[shard.gathered_row(m, world, offset, rows, buffer_row)] = product[buffer_row]
+        pieces = [None] * world
+        dist.all_gather_object(pieces, (start, stop, c_block.tobytes()))
+        if rank == 0:
+            whole = np.zeros((m, n), dtype=np.uint16)
+            for s, e, raw in pieces:
+                whole[:, s:e] = np.frombuffer(raw, dtype=np.uint16).reshape(m, e - s)
+            results.put(oracle.gemm_check_c(whole, m, n, k)[0])
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_complete_a_by_all_gather_and_tile_c():
+    context = mp.get_context("spawn")
+    results = context.Queue()
+    world, port = 2, _free_port()
+    workers = [context.Process(target=_gather_worker, args=(rank, world, port, results)) for rank in range(world)]
+    for worker in workers:
+        worker.start()
+    wrong = results.get(timeout=120)
+    for worker in workers:
+        worker.join(timeout=60)
+        assert worker.exitcode == 0
+    assert wrong == 0
 
 
 def test_two_ranks_compute_disjoint_blocks_that_tile_c():

@@ -10,8 +10,9 @@ run stopping at the first failure has already run every other test.
 import numpy as np
 import pytest
 
+import oracle
 from ferro_kittens_b200 import FerroKittensError, gemm
-from ferro_kittens_b200._lib import FK_ERR_TOO_LARGE
+from ferro_kittens_b200._lib import FK_ERR_SHAPE, FK_ERR_TOO_LARGE
 
 pytestmark = pytest.mark.gpu
 
@@ -32,6 +33,36 @@ def test_two_calls_in_a_row_match_the_allocating_entry_point(device):
         gemm.run_host(a, b, expected, m, n, k)
         gemm.run_host_noalloc(a, b, got, m, n, k)
         assert np.array_equal(got, expected), f"call {seed}: {(got != expected).sum()} words differ"
+
+
+def test_the_references_exact_gate_through_this_entry_point(device):
+    """Not only equal to its sibling: the reference's own integer operands and exact check
+    (examples/src/gemm.rs:434-440, 544-578), twice in a row at two shapes."""
+    for m, n, k in [(512, 256, 256), (1024, 1280, 320)]:
+        a, b = oracle.gemm_stage("a", m, k), oracle.gemm_stage("b", n, k)
+        got = np.full((m, n), 0xFFFF, dtype=np.uint16)
+        gemm.run_host_noalloc(a, b, got, m, n, k)
+        assert oracle.gemm_check_c(got, m, n, k)[0] == 0
+
+
+def test_a_shape_the_tiling_does_not_divide_is_refused_before_anything_is_copied(device):
+    a = np.zeros((128, 64), dtype=np.uint16)
+    b = np.zeros((256, 64), dtype=np.uint16)
+    c = np.full((128, 256), 0x1234, dtype=np.uint16)
+    with pytest.raises(FerroKittensError, match="does not divide the 256x256x64 tiling") as error:
+        gemm.run_host_noalloc(a, b, c, 128, 256, 64)
+    assert error.value.code == FK_ERR_SHAPE
+    assert (c == 0x1234).all()
+    with pytest.raises(FerroKittensError, match="group width of 0") as error:
+        gemm.run_host_noalloc(np.zeros((256, 64), dtype=np.uint16), b, np.zeros((256, 256), dtype=np.uint16),
+                              256, 256, 64, group=0)
+    assert error.value.code == FK_ERR_SHAPE
+    # a traversal width past anything sensible is clamped, not overflowed
+    m, n, k = 512, 512, 128
+    a, b = oracle.gemm_stage("a", m, k), oracle.gemm_stage("b", n, k)
+    got = np.zeros((m, n), dtype=np.uint16)
+    gemm.run_host_noalloc(a, b, got, m, n, k, group=0xFFFFFFFF)
+    assert oracle.gemm_check_c(got, m, n, k)[0] == 0
 
 
 def test_shapes_past_the_built_in_staging_are_refused(device):
