@@ -52,7 +52,12 @@ def build_library(force: bool = False, verbose: bool = False, defines: tuple[str
     sources = [CSRC / name for name in SOURCES if (CSRC / name).exists()]
     inputs = sources + list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh")) + [
         PACKAGE.parent / "include" / "ferro_kittens.h"]
-    if not force and not _stale(target, inputs):
+    # The define set a library was built with is recorded beside it, so that a tuning build is never
+    # mistaken for the default one: a library whose record differs from what is asked for is stale.
+    record = target.with_name(target.name + ".defines")
+    wanted = "\n".join(sorted(defines))
+    recorded = record.read_text() if record.exists() else None
+    if not force and not _stale(target, inputs) and recorded == wanted:
         return target
     command = [_nvcc(), *NVCC_FLAGS, *[f"-D{item}" for item in defines], "-shared", "-o", str(target),
                *map(str, sources)]
@@ -63,6 +68,7 @@ def build_library(force: bool = False, verbose: bool = False, defines: tuple[str
         raise RuntimeError("nvcc failed:\n" + result.stdout + result.stderr)
     if verbose:
         sys.stderr.write(result.stderr)
+    record.write_text(wanted)
     return target
 
 

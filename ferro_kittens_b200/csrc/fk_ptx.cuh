@@ -84,10 +84,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
 // How long one try_wait may keep the thread suspended in hardware (ns). The
 // thread wakes as soon as the phase completes, so a long hint costs no latency;
 // it only keeps waiting roles from spending issue slots on polling.
-#ifndef FK_SUSPEND_HINT_NS
-#define FK_SUSPEND_HINT_NS 200000
-#endif
-constexpr uint32_t kSuspendHintNs = FK_SUSPEND_HINT_NS;
+constexpr uint32_t kSuspendHintNs = 200000;
 
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;

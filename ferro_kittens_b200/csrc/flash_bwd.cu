@@ -99,14 +99,11 @@ enum StallCode : uint32_t {
     kMisaligned = 0x4ff,
 };
 
-#ifndef FK_BWD_POLY_MASK
-#define FK_BWD_POLY_MASK 0x5555u
-#endif
 // Of the 16 score pairs of a 32-column chunk, those whose bit is set take 2^x from a polynomial on
 // the FMA pipe instead of the ex2 unit (the forward's trick, same polynomial). Half of them is the
 // measured optimum here: 870 vs 773 TFLOP/s non-causal, 853 vs 806 causal in back-to-back launches;
 // three quarters and more are slower than none.
-constexpr uint32_t kPolyMask = FK_BWD_POLY_MASK;
+constexpr uint32_t kPolyMask = 0x5555u;
 
 // -lse * log2(e) and -delta = -rowsum(dO * O) (negated: they enter as addends), one query row per 16 lanes.
 __global__ void __launch_bounds__(256) stats_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ d_o,

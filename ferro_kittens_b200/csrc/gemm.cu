@@ -38,10 +38,7 @@ constexpr uint32_t kHalves = 2;     // [256, 256] pair tiles per item, stacked a
 constexpr uint32_t kBlockN = 256;   // columns of C per item; each CTA stages kBlockN/2 rows of B
 constexpr uint32_t kHalfN = kBlockN / 2;
 constexpr uint32_t kBlockK = 64;    // one 128-byte swizzle atom of bf16
-#ifndef FK_GEMM_STAGES
-#define FK_GEMM_STAGES 4
-#endif
-constexpr uint32_t kStages = FK_GEMM_STAGES;
+constexpr uint32_t kStages = 4;
 constexpr uint32_t kTmemColumns = kHalves * kBlockN;  // 512
 constexpr uint32_t kEpilogueWarps = 4 * kHalves;
 constexpr uint32_t kStageColumns = 64;  // columns per epilogue pass: one swizzle atom of bf16
