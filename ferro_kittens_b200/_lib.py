@@ -90,6 +90,9 @@ SIGNATURES = {
                               c_uint32, c_uint32, c_void_p, c_void_p]),
     "fk_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_uint32, c_uint32,
                         c_uint32, c_void_p, c_void_p]),
+    "fk_gemm_workspace_bytes": (c_uint64, [c_uint32, c_uint32, c_uint32, c_uint32]),
+    "fk_gemm_fused_workspace": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_uint32,
+                                        c_uint32, c_uint32, c_void_p, c_uint64, c_void_p, c_void_p]),
     "fk_gemm_bf16_host": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_uint32]),
     "fk_gemm_bf16_host_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_uint32, c_uint32, c_uint32, c_uint32]),
     "fk_flash_fwd_launch": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -69,6 +69,11 @@ __device__ __forceinline__ void fence_mbarrier_init() {
 __device__ __forceinline__ void fence_proxy_async_shared() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+/// Orders this thread's async-proxy accesses to global memory (bulk copies and reductions) with
+/// its generic-proxy accesses to the same addresses.
+__device__ __forceinline__ void fence_proxy_async_global() {
+    asm volatile("fence.proxy.async.global;" ::: "memory");
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                  : "memory");

@@ -23,6 +23,12 @@
 //
 // Barriers are initialised once per launch and their phases carried across
 // items; roles meet only through them. Every wait is bounded.
+//
+// Launches under one wave (fewer items than clusters) can split K across the idle
+// clusters (the `true` instantiation): every unit accumulates a run of k-blocks of one
+// item, adds its fp32 tile into a caller-owned workspace through the copy engine's
+// reduce-add, and the unit that arrives last on the band's counter reads the sums back,
+// applies bias / ReLU, rounds ONCE to bf16 and stores -- and leaves the workspace zero.
 
 #include <mutex>
 
@@ -97,6 +103,12 @@ struct Schedule {
     uint32_t accumulate; // non-zero: C += A . B^T through the copy engine's reduce-add
     uint32_t relu;       // non-zero: max(x, 0) on the fp32 value before it is rounded
     const uint16_t* bias;  // null, or n bf16 values added per column in fp32 before rounding
+    // K split across clusters (launches under one wave; the kernel's `true` instantiation):
+    uint32_t splits;       // units per item; 1 everywhere else
+    uint32_t split_blocks; // k-blocks per unit
+    uint32_t n;            // columns of C: the row pitch of `partial`
+    float* partial;        // fp32 [m, n] sums, zero before and after a launch
+    uint32_t* arrivals;    // units that have added their tile, per (item, CTA rank, epilogue warp); zero likewise
 };
 
 struct Item {
@@ -123,10 +135,82 @@ __host__ __device__ __forceinline__ Item item_at(const Schedule& plan, uint32_t 
     return item;
 }
 
+// The fused epilogue on one pass of a band (a column-vector bias and a unary map on the register
+// tile, src/global.rs:410-416, src/reg.rs:261), then the ONE rounding to bf16: `lo` and `hi` hold
+// this lane's row, columns [column, column + 32) and [column + 32, column + 64) as fp32 bits;
+// every lane holds the same columns, so the bias words are broadcast loads.
+__device__ __forceinline__ void finish_pass(uint32_t (&lo)[32], uint32_t (&hi)[32], const Schedule& plan,
+                                            uint32_t column, uint32_t (&packed)[32]) {
+    if (plan.bias || plan.relu) {
+        const float floor = plan.relu ? 0.0f : -INFINITY;
+#pragma unroll
+        for (uint32_t part = 0; part < 2; ++part) {
+            uint32_t* const values = part ? hi : lo;
+            uint32_t words[16];
+            if (plan.bias) {
+                const uint4* source = reinterpret_cast<const uint4*>(plan.bias + column + 32 * part);
+#pragma unroll
+                for (uint32_t q = 0; q < 4; ++q) {
+                    const uint4 v = __ldg(source + q);
+                    words[4 * q] = v.x, words[4 * q + 1] = v.y, words[4 * q + 2] = v.z, words[4 * q + 3] = v.w;
+                }
+            } else {
+#pragma unroll
+                for (uint32_t q = 0; q < 16; ++q) words[q] = 0;
+            }
+#pragma unroll
+            for (uint32_t i = 0; i < 16; ++i) {
+                const float even = __uint_as_float(values[2 * i]) + __uint_as_float(words[i] << 16);
+                const float odd = __uint_as_float(values[2 * i + 1]) + __uint_as_float(words[i] & 0xffff0000u);
+                values[2 * i] = __float_as_uint(fmaxf(even, floor));
+                values[2 * i + 1] = __float_as_uint(fmaxf(odd, floor));
+            }
+        }
+    }
+#pragma unroll
+    for (uint32_t i = 0; i < 16; ++i) {
+        packed[i] = pack_bf16x2(__uint_as_float(lo[2 * i]), __uint_as_float(lo[2 * i + 1]));
+        packed[16 + i] = pack_bf16x2(__uint_as_float(hi[2 * i]), __uint_as_float(hi[2 * i + 1]));
+    }
+}
+
+// A unit of work of a cluster: an item and the run [k0, k1) of its k-blocks. Without a K split a
+// unit is a whole item; with one, consecutive units are the runs of one item, so that they
+// execute on different clusters at the same time.
+struct Unit {
+    Item item;
+    uint32_t index;  // of the item
+    uint32_t k0, k1;
+};
+
+template <bool kSplitK>
+__device__ __forceinline__ uint32_t unit_count(const Schedule& plan) {
+    return kSplitK ? plan.items * plan.splits : plan.items;
+}
+
+template <bool kSplitK>
+__device__ __forceinline__ Unit unit_at(const Schedule& plan, uint32_t number) {
+    Unit unit;
+    if (kSplitK) {
+        unit.index = number / plan.splits;
+        unit.k0 = (number % plan.splits) * plan.split_blocks;
+        const uint32_t stop = unit.k0 + plan.split_blocks;
+        unit.k1 = stop < plan.k_blocks ? stop : plan.k_blocks;
+    } else {
+        unit.index = number;
+        unit.k0 = 0;
+        unit.k1 = plan.k_blocks;
+    }
+    unit.item = item_at(plan, unit.index);
+    return unit;
+}
+
+template <bool kSplitK>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap a_map,
                           const __grid_constant__ CUtensorMap b_map,
-                          const __grid_constant__ CUtensorMap c_map, const Schedule plan,
+                          const __grid_constant__ CUtensorMap c_map,
+                          const __grid_constant__ CUtensorMap partial_map, const Schedule plan,
                           uint32_t* status) {
     extern __shared__ __align__(1024) uint8_t dynamic_shared[];
     const uint32_t raw = smem_u32(dynamic_shared);
@@ -181,15 +265,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         if (lane == 0) {
             uint32_t fill = 0;
             bool live = true;
-            for (uint32_t index = cluster_id_x(); live && index < plan.items;
-                 index += cluster_count_x()) {
-                const Item item = item_at(plan, index);
+            for (uint32_t number = cluster_id_x(); live && number < unit_count<kSplitK>(plan);
+                 number += cluster_count_x()) {
+                const Unit unit = unit_at<kSplitK>(plan, number);
+                const Item& item = unit.item;
                 if (item.halves == 0) continue;
                 const int a_row = static_cast<int>(item.row + kBlockM * rank);
                 const int b_row = static_cast<int>(item.column + kHalfN * rank);
                 // Both CTAs' boxes land on the leader's barrier.
                 const uint32_t pair_bytes = 2 * (item.halves * kATileBytes + kBTileBytes);
-                for (uint32_t k = 0; k < plan.k_blocks; ++k, ++fill) {
+                for (uint32_t k = unit.k0; k < unit.k1; ++k, ++fill) {
                     const uint32_t s = fill % kStages;
                     const uint32_t parity = (fill / kStages) & 1u;
                     if (!mbar_wait(empty + 8 * s, parity ^ 1u, site, kStallProducer, fill)) {
@@ -216,9 +301,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             const uint32_t idesc = plan.idesc;
             uint32_t drain = 0, count = 0;
             bool live = true;
-            for (uint32_t index = cluster_id_x(); live && index < plan.items;
-                 index += cluster_count_x()) {
-                const Item item = item_at(plan, index);
+            for (uint32_t number = cluster_id_x(); live && number < unit_count<kSplitK>(plan);
+                 number += cluster_count_x()) {
+                const Unit unit = unit_at<kSplitK>(plan, number);
+                const Item& item = unit.item;
                 if (item.halves == 0) continue;
                 // The previous item's accumulators must have been read out.
                 if (!mbar_wait(acc_empty, (count & 1u) ^ 1u, site, kStallMmaAccumulator, count)) {
@@ -226,7 +312,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                     break;
                 }
                 tc_fence_after_sync();
-                for (uint32_t k = 0; k < plan.k_blocks; ++k, ++drain) {
+                for (uint32_t k = unit.k0; k < unit.k1; ++k, ++drain) {
                     const uint32_t s = drain % kStages;
                     const uint32_t parity = (drain / kStages) & 1u;
                     if (!mbar_wait(full + 8 * s, parity, site, kStallMmaFull, drain)) {
@@ -240,7 +326,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                         a_ring + (s * kHalves + 1) * kATileBytes, kKMajorLeadingBytes);
                     const uint64_t b_desc =
                         operand_descriptor(b_ring + s * kBTileBytes, kKMajorLeadingBytes);
-                    const uint32_t accumulate = k != 0;
+                    const uint32_t accumulate = k != unit.k0;
                     if (item.halves == 2) {
 #pragma unroll
                         for (uint32_t chunk = 0; chunk < kBlockK / 16; ++chunk) {
@@ -275,9 +361,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         const uint32_t t_row = tmem_address(tmem, 32 * quadrant, half * kBlockN);
         uint32_t count = 0;
         bool live = true;
-        for (uint32_t index = cluster_id_x(); live && index < plan.items;
-             index += cluster_count_x()) {
-            const Item item = item_at(plan, index);
+        for (uint32_t number = cluster_id_x(); live && number < unit_count<kSplitK>(plan);
+             number += cluster_count_x()) {
+            const Unit unit = unit_at<kSplitK>(plan, number);
+            const Item& item = unit.item;
+            const uint32_t index = kSplitK ? number : unit.index;  // the last-unit test below walks units
             if (item.halves == 0) continue;
             if (!mbar_wait(acc_full, count & 1u, site, kStallEpilogue, count)) {
                 live = false;
@@ -286,6 +374,86 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             ++count;
             tc_fence_after_sync();
             const bool mine = half < item.halves;
+            if constexpr (kSplitK) {
+                // This unit's share of the sums: the warp's [32, 256] fp32 band goes into the workspace
+                // 32 columns at a time through the staging tile and the copy engine's reduce-add.
+                const int c_row =
+                    static_cast<int>(item.row + 2 * kBlockM * half + kBlockM * rank + 32 * quadrant);
+                if (mine) {
+#pragma unroll 1
+                    for (uint32_t pass = 0; pass < kBlockN / 32; ++pass) {
+                        uint32_t v[32];
+                        tmem_ld_32x32(t_row + 32 * pass, v);
+                        tmem_wait_ld();
+                        if (lane == 0) tma_store_wait_read<0>();
+                        __syncwarp();
+#pragma unroll
+                        for (uint32_t chunk = 0; chunk < 8; ++chunk)
+                            st_shared_v4(band + swizzled_chunk_offset(lane, chunk, 0), v[4 * chunk], v[4 * chunk + 1],
+                                         v[4 * chunk + 2], v[4 * chunk + 3]);
+                        fence_proxy_async_shared();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_reduce_add_2d(&partial_map, band, static_cast<int>(item.column + 32 * pass), c_row);
+                            tma_store_commit();
+                        }
+                    }
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(mapa(acc_empty, 0));
+                if (!mine) continue;
+                // Count this unit in once its adds have been performed; the unit that completes the
+                // count owns the band from here on.
+                uint32_t* const counter = plan.arrivals + (unit.index * 2 + rank) * kEpilogueWarps + (warp - 2);
+                uint32_t last = 0;
+                if (lane == 0) {
+                    tma_store_wait_all();
+                    fence_proxy_async_global();  // the adds went through the async proxy, the reads below will not
+                    __threadfence();
+                    last = atomicAdd(counter, 1u) + 1u == plan.splits ? 1u : 0u;
+                }
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (!last) continue;
+                __threadfence();
+                fence_proxy_async_global();
+                // Read the sums back (through the L2, where the adds were made), finish them as the
+                // one-launch epilogue does, and leave the workspace as it was found: zero.
+                float* const sums = plan.partial + static_cast<size_t>(c_row + lane) * plan.n + item.column;
+#pragma unroll 1
+                for (uint32_t pass = 0; pass < kPasses; ++pass) {
+                    uint32_t lo[32], hi[32], packed[32];
+                    float4* const source = reinterpret_cast<float4*>(sums + pass * kStageColumns);
+#pragma unroll
+                    for (uint32_t q = 0; q < 8; ++q) {
+                        const float4 x = __ldcg(source + q), y = __ldcg(source + 8 + q);
+                        lo[4 * q] = __float_as_uint(x.x), lo[4 * q + 1] = __float_as_uint(x.y);
+                        lo[4 * q + 2] = __float_as_uint(x.z), lo[4 * q + 3] = __float_as_uint(x.w);
+                        hi[4 * q] = __float_as_uint(y.x), hi[4 * q + 1] = __float_as_uint(y.y);
+                        hi[4 * q + 2] = __float_as_uint(y.z), hi[4 * q + 3] = __float_as_uint(y.w);
+                    }
+#pragma unroll
+                    for (uint32_t q = 0; q < 16; ++q) __stcg(source + q, make_float4(0.0f, 0.0f, 0.0f, 0.0f));
+                    finish_pass(lo, hi, plan, item.column + pass * kStageColumns, packed);
+                    if (lane == 0) tma_store_wait_read<0>();
+                    __syncwarp();
+#pragma unroll
+                    for (uint32_t chunk = 0; chunk < 8; ++chunk)
+                        st_shared_v4(band + swizzled_chunk_offset(lane, chunk, 0), packed[4 * chunk],
+                                     packed[4 * chunk + 1], packed[4 * chunk + 2], packed[4 * chunk + 3]);
+                    fence_proxy_async_shared();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (plan.accumulate)
+                            tma_reduce_add_2d(&c_map, band, static_cast<int>(item.column + pass * kStageColumns), c_row);
+                        else
+                            tma_store_2d(&c_map, band, static_cast<int>(item.column + pass * kStageColumns), c_row);
+                        tma_store_commit();
+                    }
+                }
+                if (lane == 0) *counter = 0;
+                continue;
+            }
             // Read this warp's [32, 256] band out as bf16 pairs, then release the accumulator:
             // the stores below overlap the next item's main loop.
             uint32_t held[kPasses][32];
@@ -296,43 +464,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                     tmem_ld_32x32(t_row + pass * kStageColumns, lo);
                     tmem_ld_32x32(t_row + pass * kStageColumns + 32, hi);
                     tmem_wait_ld();
-                    if (plan.bias || plan.relu) {
-                        // The fused epilogue (a column-vector bias and a unary map on the register
-                        // tile, src/global.rs:410-416, src/reg.rs:261): every lane holds the same 64
-                        // columns, so the bias words are broadcast loads.
-                        const float floor = plan.relu ? 0.0f : -INFINITY;
-#pragma unroll
-                        for (uint32_t part = 0; part < 2; ++part) {
-                            uint32_t* const values = part ? hi : lo;
-                            uint32_t words[16];
-                            if (plan.bias) {
-                                const uint4* source = reinterpret_cast<const uint4*>(
-                                    plan.bias + item.column + pass * kStageColumns + 32 * part);
-#pragma unroll
-                                for (uint32_t q = 0; q < 4; ++q) {
-                                    const uint4 v = __ldg(source + q);
-                                    words[4 * q] = v.x, words[4 * q + 1] = v.y, words[4 * q + 2] = v.z, words[4 * q + 3] = v.w;
-                                }
-                            } else {
-#pragma unroll
-                                for (uint32_t q = 0; q < 16; ++q) words[q] = 0;
-                            }
-#pragma unroll
-                            for (uint32_t i = 0; i < 16; ++i) {
-                                const float even = __uint_as_float(values[2 * i]) + __uint_as_float(words[i] << 16);
-                                const float odd = __uint_as_float(values[2 * i + 1]) + __uint_as_float(words[i] & 0xffff0000u);
-                                values[2 * i] = __float_as_uint(fmaxf(even, floor));
-                                values[2 * i + 1] = __float_as_uint(fmaxf(odd, floor));
-                            }
-                        }
-                    }
-#pragma unroll
-                    for (uint32_t i = 0; i < 16; ++i) {
-                        held[pass][i] =
-                            pack_bf16x2(__uint_as_float(lo[2 * i]), __uint_as_float(lo[2 * i + 1]));
-                        held[pass][16 + i] =
-                            pack_bf16x2(__uint_as_float(hi[2 * i]), __uint_as_float(hi[2 * i + 1]));
-                    }
+                    finish_pass(lo, hi, plan, item.column + pass * kStageColumns, held[pass]);
                 }
             }
             tc_fence_before_sync();
@@ -421,6 +553,11 @@ static Schedule schedule(uint32_t m, uint32_t n, uint32_t k, uint32_t group, uin
     plan.accumulate = (flags & FK_GEMM_ACCUMULATE) ? 1u : 0u;
     plan.relu = (flags & FK_GEMM_RELU) ? 1u : 0u;
     plan.bias = nullptr;
+    plan.splits = 1;
+    plan.split_blocks = k / kBlockK;
+    plan.n = n;
+    plan.partial = nullptr;
+    plan.arrivals = nullptr;
     plan.m = m;
     plan.tiles_m = (m + kHalves * 2 * kBlockM - 1) / (kHalves * 2 * kBlockM);
     plan.tiles_n = n / kBlockN;
@@ -474,17 +611,18 @@ extern "C" int fk_gemm_launch_fused(const void* a_map, const void* b_map, const 
     const int sm_count = facts.sm_count;
     uint32_t limit = 0;
     const int admitted = fk_admit_shared_plan(
-        reinterpret_cast<const void*>(gemm::gemm_bf16_pair_kernel), gemm::kSharedBytes, &limit);
+        reinterpret_cast<const void*>(gemm::gemm_bf16_pair_kernel<false>), gemm::kSharedBytes, &limit);
     if (admitted != FK_OK) return admitted;
 
     const uint32_t clusters = static_cast<uint32_t>(sm_count) / 2;
     gemm::Schedule plan = gemm::schedule(m, n, k, group, clusters, flags);
     plan.bias = static_cast<const uint16_t*>(bias);
     const uint32_t grid = 2 * (plan.items < clusters ? plan.items : clusters);
-    gemm::gemm_bf16_pair_kernel<<<grid, gemm::kThreads, gemm::kSharedBytes,
-                                  static_cast<cudaStream_t>(stream)>>>(
+    // The one-launch kernel never touches its fourth map; it is handed C's.
+    gemm::gemm_bf16_pair_kernel<false><<<grid, gemm::kThreads, gemm::kSharedBytes,
+                                         static_cast<cudaStream_t>(stream)>>>(
         *static_cast<const CUtensorMap*>(a_map), *static_cast<const CUtensorMap*>(b_map),
-        *static_cast<const CUtensorMap*>(c_map), plan, device_status);
+        *static_cast<const CUtensorMap*>(c_map), *static_cast<const CUtensorMap*>(c_map), plan, device_status);
     FK_CUDA(cudaGetLastError());
     return FK_OK;
 }
@@ -531,6 +669,97 @@ extern "C" int fk_gemm_fused(const void* a, const void* b, void* c, const void* 
     if (status != FK_OK) return status;
     return fk_gemm_launch_fused(&maps[0], &maps[1], &maps[2], bias, m, n, k, group, flags, stream,
                                 device_status);
+}
+
+// ---- launches under one wave: K split across the idle clusters, partial sums in a workspace
+//
+// With fewer items than clusters most SMs idle while a few walk all of K: 1024 x 1024 x 16384 keeps
+// 16 clusters busy for 256 k-blocks each. Splitting every item's k-blocks into `splits` runs gives
+// every cluster a run; the runs meet in an fp32 workspace (the bf16 reduce-add of
+// FK_GEMM_ACCUMULATE would round once per run) and the last to arrive rounds once.
+namespace {
+
+// Measured on B200 (back-to-back launches, one launch / split / cuBLAS, microseconds):
+// 1024 x 1024 x 4096: 27 / 37 / 12; 1024 x 1024 x 8192: 66 / 39 / 19; 1024 x 1024 x 16384: 91 / 51 / 34;
+// 512 x 512 x 16384: 86 / 38 / 23; 256 x 256 x 32768: 162 / 37 / 19. The runs' fp32 tiles cross the L2
+// twice (splits x M x N x 4 bytes added, M x N x 4 read back and cleared), which a 64-deep K does not
+// repay: split only from 128 k-blocks on, into runs of at least 32.
+constexpr uint32_t kMinSplitDepth = 128;
+constexpr uint32_t kMinSplitBlocks = 32;
+
+// How a shape would be split on `clusters` resident clusters: 1 = not at all.
+uint32_t split_count(const gemm::Schedule& plan, uint32_t clusters) {
+    if (plan.items == 0 || plan.items * 2 > clusters || plan.k_blocks < kMinSplitDepth) return 1;
+    const uint32_t by_clusters = clusters / plan.items;
+    const uint32_t by_depth = plan.k_blocks / kMinSplitBlocks;
+    const uint32_t splits = by_clusters < by_depth ? by_clusters : by_depth;
+    return splits < 2 ? 1 : splits;
+}
+
+uint64_t arrivals_bytes(const gemm::Schedule& plan) { return uint64_t(plan.items) * 2 * gemm::kEpilogueWarps * 4; }
+
+}  // namespace
+
+extern "C" uint64_t fk_gemm_workspace_bytes(uint32_t m, uint32_t n, uint32_t k, uint32_t sm_count) {
+    if (m == 0 || n == 0 || k == 0 || m % (2 * gemm::kBlockM) || n % gemm::kBlockN || k % gemm::kBlockK) return 0;
+    const uint32_t clusters = sm_count / 2;
+    if (clusters == 0) return 0;
+    const gemm::Schedule plan = gemm::schedule(m, n, k, 1, clusters);
+    if (split_count(plan, clusters) == 1) return 0;
+    return uint64_t(m) * n * 4 + arrivals_bytes(plan);
+}
+
+extern "C" int fk_gemm_fused_workspace(const void* a, const void* b, void* c, const void* bias, uint32_t m,
+                                       uint32_t n, uint32_t k, uint32_t ldc, uint32_t group, uint32_t flags,
+                                       void* workspace, uint64_t workspace_bytes, void* stream,
+                                       uint32_t* device_status) {
+    DeviceFacts facts;
+    const int known = device_facts(&facts);
+    if (known != FK_OK) return known;
+    const uint64_t wanted = fk_gemm_workspace_bytes(m, n, k, static_cast<uint32_t>(facts.sm_count));
+    // Shapes that fill a wave, and callers without a workspace, take the one-launch path (which
+    // also reports every argument error).
+    if (wanted == 0 || !workspace) return fk_gemm_fused(a, b, c, bias, m, n, k, ldc, group, flags, stream, device_status);
+    if (workspace_bytes < wanted)
+        return fk_fail(FK_ERR_TOO_LARGE, "%ux%ux%u splits K over a workspace of %llu bytes; %llu were given", m, n, k,
+                       (unsigned long long)wanted, (unsigned long long)workspace_bytes);
+    if (reinterpret_cast<uintptr_t>(workspace) & 15u)
+        return fk_fail(FK_ERR_ALIGNMENT, "the workspace wants 16-byte alignment");
+    if (!a || !b || !c) return fk_fail(FK_ERR_INVALID, "an operand pointer is null");
+    if (ldc < n) return fk_fail(FK_ERR_SHAPE, "ldc %u is narrower than the %u columns of C", ldc, n);
+    if (flags & ~(FK_GEMM_F16_OPERANDS | FK_GEMM_ACCUMULATE | FK_GEMM_RELU))
+        return fk_fail(FK_ERR_INVALID, "unknown GEMM flags 0x%x", flags);
+    if (reinterpret_cast<uintptr_t>(bias) & 15u)
+        return fk_fail(FK_ERR_ALIGNMENT, "the bias vector wants 16-byte alignment");
+    if (group == 0) return fk_fail(FK_ERR_SHAPE, "a traversal group width of 0 has no tiles in it");
+
+    alignas(64) CUtensorMap maps[4];
+    int status = gemm_maps(a, b, c, m, n, k, ldc, maps, (flags & FK_GEMM_F16_OPERANDS) ? FK_F16 : FK_BF16);
+    if (status != FK_OK) return status;
+    fk_layout_t layout;
+    const uint64_t extents[2] = {n, m};
+    status = fk_layout_packed(&layout, reinterpret_cast<uint64_t>(workspace), FK_F32, 2, extents);
+    if (status == FK_OK) status = fk_tensor_map(&maps[3], &layout, 32, 32, FK_SWIZZLE_128B);
+    if (status != FK_OK) return status;
+
+    uint32_t limit = 0;
+    const int admitted = fk_admit_shared_plan(reinterpret_cast<const void*>(gemm::gemm_bf16_pair_kernel<true>),
+                                              gemm::kSharedBytes, &limit);
+    if (admitted != FK_OK) return admitted;
+    const uint32_t clusters = static_cast<uint32_t>(facts.sm_count) / 2;
+    gemm::Schedule plan = gemm::schedule(m, n, k, group, clusters, flags);
+    plan.bias = static_cast<const uint16_t*>(bias);
+    plan.splits = split_count(plan, clusters);
+    plan.split_blocks = (plan.k_blocks + plan.splits - 1) / plan.splits;
+    plan.splits = (plan.k_blocks + plan.split_blocks - 1) / plan.split_blocks;  // no empty run
+    plan.partial = static_cast<float*>(workspace);
+    plan.arrivals = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(workspace) + uint64_t(m) * n * 4);
+    const uint32_t units = plan.items * plan.splits;
+    const uint32_t grid = 2 * (units < clusters ? units : clusters);
+    gemm::gemm_bf16_pair_kernel<true><<<grid, gemm::kThreads, gemm::kSharedBytes, static_cast<cudaStream_t>(stream)>>>(
+        maps[0], maps[1], maps[2], maps[3], plan, device_status);
+    FK_CUDA(cudaGetLastError());
+    return FK_OK;
 }
 
 extern "C" int fk_gemm(const void* a, const void* b, void* c, uint32_t m, uint32_t n, uint32_t k,

@@ -62,12 +62,24 @@ def launch(a_map, b_map, c_map, m: int, n: int, k: int, group: int = GROUP, stat
                                         group, handle, status.data_ptr() if status is not None else None))
 
 
+def workspace(m: int, n: int, k: int, device, sm_count: int | None = None) -> torch.Tensor | None:
+    """A zeroed workspace for a launch that would split K (fewer items than half a wave), or None.
+
+    Pass it to :func:`run`; every launch leaves it zeroed, so one tensor serves any number of
+    launches of shapes up to this one, as long as they do not overlap on the device."""
+    if sm_count is None:
+        sm_count = torch.cuda.get_device_properties(device).multi_processor_count
+    size = library().fk_gemm_workspace_bytes(m, n, k, sm_count)
+    return torch.zeros(size, dtype=torch.uint8, device=device) if size else None
+
+
 def run(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor | None = None, group: int = GROUP,
         status: torch.Tensor | None = None, accumulate: bool = False, bias: torch.Tensor | None = None,
-        relu: bool = False) -> torch.Tensor:
+        relu: bool = False, workspace: torch.Tensor | None = None) -> torch.Tensor:
     """``C[m, n] (+)= map(sum_k A[m, k] * B[n, k] + bias[n])``; A is [m, k], B is [n, k], both bf16 or both fp16 on
     one GPU, C bf16. With ``accumulate`` the rounded product is added into ``c`` (in bf16, by the
-    copy engine), which must then be given and hold values."""
+    copy engine), which must then be given and hold values. With a ``workspace`` (see :func:`workspace`) a
+    launch under one wave splits K across the idle SMs."""
     for name, tensor in (("a", a), ("b", b)):
         if not tensor.is_cuda:
             raise RuntimeError(f"{name} must live on a CUDA device: there is no CPU path")
@@ -92,11 +104,15 @@ def run(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor | None = None, group: 
         raise ValueError("bias must be a contiguous bfloat16 [n] tensor on the device")
     flags = ((F16_OPERANDS if a.dtype == torch.float16 else 0) | (ACCUMULATE if accumulate else 0)
              | (RELU if relu else 0))
+    if workspace is not None and (not workspace.is_cuda or not workspace.is_contiguous()):
+        raise ValueError("the workspace must be a contiguous tensor on the device")
     with torch.cuda.device(a.device):
         handle = torch.cuda.current_stream().cuda_stream
-        check(library().fk_gemm_fused(a.data_ptr(), b.data_ptr(), c.data_ptr(),
-                                      bias.data_ptr() if bias is not None else None, m, n, k, c.stride(0), group,
-                                      flags, handle, status.data_ptr() if status is not None else None))
+        check(library().fk_gemm_fused_workspace(
+            a.data_ptr(), b.data_ptr(), c.data_ptr(), bias.data_ptr() if bias is not None else None, m, n, k,
+            c.stride(0), group, flags, workspace.data_ptr() if workspace is not None else None,
+            workspace.numel() * workspace.element_size() if workspace is not None else 0, handle,
+            status.data_ptr() if status is not None else None))
     return c
 
 

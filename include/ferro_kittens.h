@@ -185,6 +185,25 @@ int fk_gemm_launch(const void* a_map, const void* b_map, const void* c_map, uint
 int fk_gemm(const void* a, const void* b, void* c, uint32_t m, uint32_t n, uint32_t k, uint32_t ldc,
             uint32_t group, uint32_t flags, void* stream, uint32_t* device_status);
 
+/* Launches under one wave. The reference switches to a narrow `[256, 128]` cluster tile when a
+ * launch holds at most half a wave of its wide tiles (`gemm_sol_m256_n128`,
+ * examples/src/gemm_sol.rs:1063, dispatch :1335-1337), so that more SMs take part; this entry
+ * reaches the idle SMs by splitting K instead: every item's k-blocks are cut into runs, one per
+ * cluster, each run adds its fp32 tile into `workspace` through the copy engine's reduce-add
+ * (`tma_store_add_2d`, src/shared.rs:974-1009, on fp32 here: the sums are rounded to bf16 ONCE,
+ * after the last run, by whichever run arrives last), bias / ReLU / accumulate as in fk_gemm_fused.
+ *   fk_gemm_workspace_bytes: bytes the shape needs on a device of `sm_count` SMs, 0 when it
+ *     would not be split (at least half a wave of items, or K under 8192: the runs' fp32 tiles
+ *     cross the L2 twice, which a shallower K does not repay);
+ *   `workspace`: device memory, 16-byte aligned, ALL ZERO before its first use -- every launch
+ *     leaves it all zero again, so it is cleared once, not per call. Launches that share a
+ *     workspace must not overlap on the device. With a null workspace, or a shape that would not
+ *     be split, the call is fk_gemm_fused. */
+uint64_t fk_gemm_workspace_bytes(uint32_t m, uint32_t n, uint32_t k, uint32_t sm_count);
+int fk_gemm_fused_workspace(const void* a, const void* b, void* c, const void* bias, uint32_t m, uint32_t n,
+                            uint32_t k, uint32_t ldc, uint32_t group, uint32_t flags, void* workspace,
+                            uint64_t workspace_bytes, void* stream, uint32_t* device_status);
+
 /* The whole of `gemm::run` from HOST buffers (:503-537): stage A and B, launch,
  * read C back; blocks until C is on the host. Device buffers are cached per
  * device and grown on demand. One call at a time per device: the staging buffers, the three
