@@ -42,11 +42,18 @@ def mix64(x: torch.Tensor) -> torch.Tensor:
     return z ^ _lsr(z, 31)
 
 
+def _key(seed: int, tensor: int, draw: int) -> int:
+    return _signed((seed * 0xD1342543DE82EF95 + tensor * 0xA0761D6478BD642F + draw * 0xE7037ED1A0B428DB) & ((1 << 64) - 1))
+
+
+def _hashed_index(first: int, count: int, device) -> torch.Tensor:
+    return mix64(torch.arange(first, first + count, dtype=torch.int64, device=device))
+
+
 def _stream(seed: int, tensor: int, first: int, count: int, draw: int, device) -> torch.Tensor:
-    """Hash words of flat indices ``[first, first + count)``, draw number ``draw``."""
-    index = torch.arange(first, first + count, dtype=torch.int64, device=device)
-    key = _signed((seed * 0xD1342543DE82EF95 + tensor * 0xA0761D6478BD642F + draw * 0xE7037ED1A0B428DB) & ((1 << 64) - 1))
-    return mix64(mix64(index) ^ key)
+    """Hash words of flat indices ``[first, first + count)``, draw number ``draw``:
+    ``mix64(mix64(index) ^ key(seed, tensor, draw))``."""
+    return mix64(_hashed_index(first, count, device) ^ _key(seed, tensor, draw))
 
 
 def uniform(seed: int, tensor: int, first: int, count: int, device="cpu") -> torch.Tensor:
@@ -56,24 +63,32 @@ def uniform(seed: int, tensor: int, first: int, count: int, device="cpu") -> tor
 
 
 def normal(seed: int, tensor: int, first: int, count: int, device="cpu") -> torch.Tensor:
-    """fp64 Irwin-Hall(12) values (mean 0, variance 1) for flat indices ``[first, first + count)``."""
-    total = torch.zeros(count, dtype=torch.int64, device=device)
+    """fp64 Irwin-Hall(12) values (mean 0, variance 1) for flat indices ``[first, first + count)``:
+    the twelve 16-bit lanes of draws 1, 2 and 3, summed."""
+    hashed = _hashed_index(first, count, device)
+    pairs = torch.zeros(count, dtype=torch.int64, device=device)
     for draw in range(3):
-        word = _stream(seed, tensor, first, count, 1 + draw, device)
-        for lane in range(4):
-            total += _lsr(word, 16 * lane) & 0xFFFF
+        word = mix64(hashed ^ _key(seed, tensor, 1 + draw))
+        # lanes 0 and 2 in one add, lanes 1 and 3 in another: two 32-bit fields each holding a sum of lanes
+        pairs += (word & 0x0000FFFF0000FFFF) + (_lsr(word, 16) & 0x0000FFFF0000FFFF)
+    total = (pairs & 0xFFFFFFFF) + _lsr(pairs, 32)
     # twelve lanes of mean 32767.5 and variance (2^32 - 1) / 12 each
     return (total.to(torch.float64) - 12 * 32767.5) * (1.0 / 65536.0)
 
 
 def bf16_rows(kind: str, seed: int, tensor: int, row0: int, rows: int, columns: int, scale: float = 1.0,
-              device="cpu", chunk_rows: int = 1024) -> torch.Tensor:
+              device="cpu", chunk_rows: int | None = None) -> torch.Tensor:
     """Rows ``[row0, row0 + rows)`` of a row-major ``[*, columns]`` matrix as bf16.
 
     ``kind`` is ``"normal"`` (value x ``scale`` in fp64, narrowed to fp32 and then to bf16, each a
     single IEEE rounding, so host and device agree) or ``"uniform"``.
-    Generated in blocks of ``chunk_rows`` rows to bound the temporaries.
+    Generated in blocks of ``chunk_rows`` rows to bound the temporaries: by default about a million
+    elements on the host (the element-wise passes then stay in cache) and sixteen million on a device
+    (few launches).
     """
+    if chunk_rows is None:
+        on_host = torch.device(device).type == "cpu"
+        chunk_rows = max(1, ((1 << 20) if on_host else (1 << 24)) // max(1, columns))
     out = torch.empty((rows, columns), dtype=torch.bfloat16, device=device)
     for start in range(0, rows, chunk_rows):
         stop = min(rows, start + chunk_rows)
