@@ -431,8 +431,6 @@ static const char* stall_role(uint32_t code) {
         case 0x206: return "flash softmax waiting for O";
         case 0x207: return "flash MMA waiting for the previous item's output to be read out";
         case 0x208: return "flash loader waiting for a free Q buffer";
-        case 0x209: return "flash role waiting on the item queue";
-        case 0x20a: return "flash softmax warp waiting for its sibling warp";
         case 0x1ff: return "gemm found its shared memory base off a 1024-byte boundary";
         case 0x2ff: return "flash found its shared memory base off a 1024-byte boundary";
         case 0x301: return "self-test wait on a barrier nothing arrives on";
