@@ -542,6 +542,186 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     if (warp == 1) tmem_dealloc<2>(tmem, kTmemColumns);
 }
 
+// ------------------------------------------------------------------ the narrow tile
+//
+// Launches of a few wide items leave most SMs idle, and when K is shallow too the wide kernel's
+// fixed cost (cluster rendezvous, a 4 x 48 KiB ring that is latency-bound on 16 clusters, a serial
+// [128, 256] epilogue per CTA) is most of the launch. The reference meets such launches with a
+// narrow cluster tile (`gemm_sol_m256_n128`, examples/src/gemm_sol.rs:1063, dispatch :1335-1337);
+// here they get one CTA per [128, 128] tile of C, no cluster, cta_group::1 MMAs (M128 N128 K16),
+// three 32 KiB stages and 128 tensor-memory columns, so that two CTAs share an SM and one's
+// epilogue runs under the other's main loop. Same operand maps, same C map, same fused epilogue.
+namespace narrow {
+
+constexpr uint32_t kTile = 128;     // rows and columns of C per CTA
+// Three stages let two CTAs share an SM, which a grid of more tiles than SMs wants (one's epilogue
+// under the other's main loop); a grid of fewer tiles leaves every CTA alone on its SM, where three
+// 32 KiB stages are too few bytes in flight to cover the L2's latency, and takes six.
+constexpr uint32_t kStagesShared = 3;
+constexpr uint32_t kStagesAlone = 6;
+constexpr uint32_t kEpilogueWarps = 4;
+constexpr uint32_t kThreads = (2 + kEpilogueWarps) * 32;
+constexpr uint32_t kTileBytes = kTile * kBlockK * 2;  // one [128, 64] operand tile
+constexpr uint32_t kTmemColumns = kTile;
+
+template <uint32_t kStages>
+struct Plan {
+    SharedPlan a_ring, b_ring, bands, full, empty, acc_full, tmem_slot, stop, end;
+    constexpr Plan()
+        : a_ring(SharedPlan{}.tile_ring(kTile, kBlockK, 2, kStages)),
+          b_ring(a_ring.tile_ring(kTile, kBlockK, 2, kStages)),
+          bands(b_ring.tile_ring(32, kStageColumns, 2, kEpilogueWarps)),
+          full(bands.semaphores(kStages)),
+          empty(full.semaphores(kStages)),
+          acc_full(empty.semaphore()),
+          tmem_slot(acc_full.tmem_slot()),
+          stop(tmem_slot.word()),
+          end(stop) {}
+};
+template <uint32_t kStages>
+constexpr uint32_t shared_bytes() {
+    return static_cast<uint32_t>(Plan<kStages>{}.end.bytes());
+}
+// Two CTAs per SM: each pays about 1 KiB of reserved shared memory on top of its plan.
+static_assert(2 * (shared_bytes<kStagesShared>() + 1024) <= 233472, "two narrow CTAs must fit one SM's shared memory");
+static_assert(shared_bytes<kStagesAlone>() <= 232448, "plan exceeds the opt-in shared memory of an sm_100 CTA");
+
+template <uint32_t kStages>
+__global__ void __launch_bounds__(kThreads, kStages == kStagesShared ? 2 : 1)
+    gemm_bf16_narrow_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
+                            const __grid_constant__ CUtensorMap c_map, const Schedule plan, uint32_t* status) {
+    constexpr Plan<kStages> kPlan{};
+    static_assert(kPlan.a_ring.at % 1024 == 0 && kPlan.b_ring.at % 1024 == 0 && kPlan.bands.at % 1024 == 0,
+                  "swizzled tiles must start on a 1024-byte boundary");
+    extern __shared__ __align__(1024) uint8_t dynamic_shared[];
+    const uint32_t base = smem_u32(dynamic_shared);
+    if (base & (kBaseAlign - 1)) {
+        if (threadIdx.x == 0 && status) atomicCAS(status, 0u, static_cast<uint32_t>(kMisaligned));
+        return;
+    }
+    const uint32_t a_ring = base + kPlan.a_ring.at;
+    const uint32_t b_ring = base + kPlan.b_ring.at;
+    const uint32_t bands = base + kPlan.bands.at;
+    const uint32_t full = base + kPlan.full.at;
+    const uint32_t empty = base + kPlan.empty.at;
+    const uint32_t acc_full = base + kPlan.acc_full.at;
+    const uint32_t slot = base + kPlan.tmem_slot.at;
+    volatile uint32_t* stop_flag = reinterpret_cast<volatile uint32_t*>(dynamic_shared + kPlan.stop.at);
+    volatile uint32_t* slot_ptr = reinterpret_cast<volatile uint32_t*>(dynamic_shared + kPlan.tmem_slot.at);
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t row0 = kTile * blockIdx.y;
+    const uint32_t column0 = kTile * blockIdx.x;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < kStages; ++s) {
+            mbar_init(full + 8 * s, 1);
+            mbar_init(empty + 8 * s, 1);
+        }
+        mbar_init(acc_full, 1);
+        *stop_flag = 0;
+        fence_mbarrier_init();
+        prefetch_tensormap(&a_map);
+        prefetch_tensormap(&b_map);
+        prefetch_tensormap(&c_map);
+    }
+    if (warp == 1) {
+        tmem_alloc<1>(slot, kTmemColumns);
+        tmem_relinquish<1>();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *slot_ptr;
+    const StallSite site{status, stop_flag, 0};
+    // A k-block is four MMAs, 256 tensor cycles: a thread suspended in try_wait wakes later than
+    // that, so the two roles on the operand ring poll instead.
+    const StallSite prompt{status, stop_flag, 0, kWaitBudgetCycles, true};
+
+    if (warp == 0) {
+        // ------------------------------------------------ producer
+        if (lane == 0) {
+            for (uint32_t k = 0; k < plan.k_blocks; ++k) {
+                const uint32_t s = k % kStages;
+                if (!mbar_wait(empty + 8 * s, ((k / kStages) & 1u) ^ 1u, prompt, kStallProducer, k)) break;
+                mbar_arrive_expect_tx(full + 8 * s, 2 * kTileBytes);
+                const int column = static_cast<int>(kBlockK * k);
+                tma_load_2d(a_ring + s * kTileBytes, &a_map, column, static_cast<int>(row0), full + 8 * s);
+                tma_load_2d(b_ring + s * kTileBytes, &b_map, column, static_cast<int>(column0), full + 8 * s);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issue
+        // One elected thread (see the note at elect_one: the tight issue sequence matters when an
+        // MMA is 64 cycles of the pipe).
+        if (elect_one()) {
+            bool live = true;
+            for (uint32_t k = 0; k < plan.k_blocks; ++k) {
+                const uint32_t s = k % kStages;
+                if (!mbar_wait(full + 8 * s, (k / kStages) & 1u, prompt, kStallMmaFull, k)) {
+                    live = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint64_t a_desc = operand_descriptor(a_ring + s * kTileBytes, kKMajorLeadingBytes);
+                const uint64_t b_desc = operand_descriptor(b_ring + s * kTileBytes, kKMajorLeadingBytes);
+#pragma unroll
+                for (uint32_t chunk = 0; chunk < kBlockK / 16; ++chunk) {
+                    const uint64_t step = (chunk * kKMajorChunkBytes) >> 4;
+                    mma_ss<1>(tmem, a_desc + step, b_desc + step, plan.idesc, (k != 0) | chunk);
+                }
+                mma_commit<1>(empty + 8 * s);
+            }
+            if (live) mma_commit<1>(acc_full);
+        }
+    } else {
+        // ------------------------------------------------ epilogue: one 32-row band per warp
+        const uint32_t quadrant = warp & 3u;
+        const uint32_t band = bands + (warp - 2) * kBandBytes;
+        const uint32_t t_row = tmem_address(tmem, 32 * quadrant, 0);
+        if (mbar_wait(acc_full, 0, site, kStallEpilogue, 0)) {
+            tc_fence_after_sync();
+            const int c_row = static_cast<int>(row0 + 32 * quadrant);
+#pragma unroll 1
+            for (uint32_t pass = 0; pass < kTile / kStageColumns; ++pass) {
+                uint32_t lo[32], hi[32], packed[32];
+                tmem_ld_32x32(t_row + pass * kStageColumns, lo);
+                tmem_ld_32x32(t_row + pass * kStageColumns + 32, hi);
+                tmem_wait_ld();
+                finish_pass(lo, hi, plan, column0 + pass * kStageColumns, packed);
+                if (lane == 0) tma_store_wait_read<0>();
+                __syncwarp();
+#pragma unroll
+                for (uint32_t chunk = 0; chunk < 8; ++chunk)
+                    st_shared_v4(band + swizzled_chunk_offset(lane, chunk, 0), packed[4 * chunk], packed[4 * chunk + 1],
+                                 packed[4 * chunk + 2], packed[4 * chunk + 3]);
+                fence_proxy_async_shared();
+                __syncwarp();
+                if (lane == 0) {
+                    const int column = static_cast<int>(column0 + pass * kStageColumns);
+                    if (plan.accumulate)
+                        tma_reduce_add_2d(&c_map, band, column, c_row);
+                    else
+                        tma_store_2d(&c_map, band, column, c_row);
+                    tma_store_commit();
+                }
+            }
+            if (lane == 0) tma_store_wait_before_exit();
+        }
+    }
+
+    // ---------------------------------------------------- teardown
+    if (*stop_flag) {
+        for (int i = 0; i < 256; ++i) __nanosleep(1000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc<1>(tmem, kTmemColumns);
+}
+
+}  // namespace narrow
+
 // The item list of a launch over `clusters` resident clusters: whole [512, 256]
 // tiles, with the last partial wave re-cut into single halves when it holds at
 // most half a wave of tiles (two short half-waves then beat one long one).
@@ -590,11 +770,26 @@ extern "C" uint32_t fk_gemm_grid(uint32_t m, uint32_t n, uint32_t sm_count) {
     return 2 * (plan.items < clusters ? plan.items : clusters);
 }
 
+// Which launches take the narrow tile when the caller does not say. Measured on B200 (device time per
+// launch from CUDA-graph replays, wide / narrow, microseconds): 1024 x 1024 x 512: 8.4 / 5.5;
+// 1024 x 1024 x 4096: 25.5 / 17.2; 2048 x 1024 x 8192: 46.4 / 31.1; 2048 x 2048 x 256: 7.6 / 5.7;
+// 2048 x 2048 x 1024: 11.5 / 10.0; 2048 x 2048 x 2048: 16.5 / 16.1; 2048 x 2048 x 4096: 26.4 / 29.9;
+// 4096 x 2048 x 512: 12.9 / 12.4; 3072 x 3072 x 1024: 20.1 / 19.9; 4096 x 4096 x 256: 14.5 / 17.9.
+// So: up to 128 narrow tiles at any depth (the wide items would leave most SMs idle), up to two
+// CTAs per SM's worth while K is at most 2048 (past that the wide tile's operand reuse wins).
+static bool narrow_by_default(uint32_t m, uint32_t n, uint32_t k, uint32_t sm_count) {
+    const uint64_t tiles = uint64_t(m / gemm::narrow::kTile) * (n / gemm::narrow::kTile);
+    if (tiles <= 128) return true;
+    return tiles <= 2ull * sm_count && k <= 2048;
+}
+
 extern "C" int fk_gemm_launch_fused(const void* a_map, const void* b_map, const void* c_map,
                                     const void* bias, uint32_t m, uint32_t n, uint32_t k, uint32_t group,
                                     uint32_t flags, void* stream, uint32_t* device_status) {
-    if (flags & ~(FK_GEMM_F16_OPERANDS | FK_GEMM_ACCUMULATE | FK_GEMM_RELU))
+    if (flags & ~(FK_GEMM_F16_OPERANDS | FK_GEMM_ACCUMULATE | FK_GEMM_RELU | FK_GEMM_TILE_NARROW | FK_GEMM_TILE_WIDE))
         return fk_fail(FK_ERR_INVALID, "unknown GEMM flags 0x%x", flags);
+    if ((flags & FK_GEMM_TILE_NARROW) && (flags & FK_GEMM_TILE_WIDE))
+        return fk_fail(FK_ERR_INVALID, "the narrow and the wide tile were both asked for");
     if (reinterpret_cast<uintptr_t>(bias) & 15u)
         return fk_fail(FK_ERR_ALIGNMENT, "the bias vector wants 16-byte alignment");
     if (!a_map || !b_map || !c_map) return fk_fail(FK_ERR_INVALID, "a tensor map pointer is null");
@@ -617,6 +812,27 @@ extern "C" int fk_gemm_launch_fused(const void* a_map, const void* b_map, const 
     const uint32_t clusters = static_cast<uint32_t>(sm_count) / 2;
     gemm::Schedule plan = gemm::schedule(m, n, k, group, clusters, flags);
     plan.bias = static_cast<const uint16_t*>(bias);
+    if ((flags & FK_GEMM_TILE_NARROW) || (!(flags & FK_GEMM_TILE_WIDE) && narrow_by_default(m, n, k, static_cast<uint32_t>(sm_count)))) {
+        // One CTA per [128, 128] tile; the A and B maps' boxes are [64, 128] already, C's [64, 32].
+        plan.idesc = instruction_descriptor(gemm::narrow::kTile, gemm::narrow::kTile, false, false,
+                                            (flags & FK_GEMM_F16_OPERANDS) ? 0u : 1u);
+        const dim3 tiles(n / gemm::narrow::kTile, m / gemm::narrow::kTile, 1);
+        if (tiles.y > 65535) return fk_fail(FK_ERR_SHAPE, "%u rows is past what the narrow tile's grid takes", m);
+        const auto launch_narrow = [&](auto kernel, uint32_t bytes) -> int {
+            const int narrow_admitted = fk_admit_shared_plan(reinterpret_cast<const void*>(kernel), bytes, &limit);
+            if (narrow_admitted != FK_OK) return narrow_admitted;
+            kernel<<<tiles, gemm::narrow::kThreads, bytes, static_cast<cudaStream_t>(stream)>>>(
+                *static_cast<const CUtensorMap*>(a_map), *static_cast<const CUtensorMap*>(b_map),
+                *static_cast<const CUtensorMap*>(c_map), plan, device_status);
+            FK_CUDA(cudaGetLastError());
+            return FK_OK;
+        };
+        if (uint64_t(tiles.x) * tiles.y <= static_cast<uint64_t>(sm_count))
+            return launch_narrow(gemm::narrow::gemm_bf16_narrow_kernel<gemm::narrow::kStagesAlone>,
+                                 gemm::narrow::shared_bytes<gemm::narrow::kStagesAlone>());
+        return launch_narrow(gemm::narrow::gemm_bf16_narrow_kernel<gemm::narrow::kStagesShared>,
+                             gemm::narrow::shared_bytes<gemm::narrow::kStagesShared>());
+    }
     const uint32_t grid = 2 * (plan.items < clusters ? plan.items : clusters);
     // The one-launch kernel never touches its fourth map; it is handed C's.
     gemm::gemm_bf16_pair_kernel<false><<<grid, gemm::kThreads, gemm::kSharedBytes,
@@ -683,8 +899,9 @@ namespace {
 // 1024 x 1024 x 4096: 27 / 37 / 12; 1024 x 1024 x 8192: 66 / 39 / 19; 1024 x 1024 x 16384: 91 / 51 / 34;
 // 512 x 512 x 16384: 86 / 38 / 23; 256 x 256 x 32768: 162 / 37 / 19. The runs' fp32 tiles cross the L2
 // twice (splits x M x N x 4 bytes added, M x N x 4 read back and cleared), which a 64-deep K does not
-// repay: split only from 128 k-blocks on, into runs of at least 32.
-constexpr uint32_t kMinSplitDepth = 128;
+// repay, and up to K = 8192 the narrow tile on its own beats the split (1024 x 1024 x 8192: wide 45,
+// split 36, narrow 30): split only from 256 k-blocks on, into runs of at least 32.
+constexpr uint32_t kMinSplitDepth = 256;
 constexpr uint32_t kMinSplitBlocks = 32;
 
 // How a shape would be split on `clusters` resident clusters: 1 = not at all.
@@ -727,8 +944,8 @@ extern "C" int fk_gemm_fused_workspace(const void* a, const void* b, void* c, co
         return fk_fail(FK_ERR_ALIGNMENT, "the workspace wants 16-byte alignment");
     if (!a || !b || !c) return fk_fail(FK_ERR_INVALID, "an operand pointer is null");
     if (ldc < n) return fk_fail(FK_ERR_SHAPE, "ldc %u is narrower than the %u columns of C", ldc, n);
-    if (flags & ~(FK_GEMM_F16_OPERANDS | FK_GEMM_ACCUMULATE | FK_GEMM_RELU))
-        return fk_fail(FK_ERR_INVALID, "unknown GEMM flags 0x%x", flags);
+    if (flags & ~(FK_GEMM_F16_OPERANDS | FK_GEMM_ACCUMULATE | FK_GEMM_RELU | FK_GEMM_TILE_WIDE))
+        return fk_fail(FK_ERR_INVALID, "unknown GEMM flags 0x%x for a launch that splits K", flags);
     if (reinterpret_cast<uintptr_t>(bias) & 15u)
         return fk_fail(FK_ERR_ALIGNMENT, "the bias vector wants 16-byte alignment");
     if (group == 0) return fk_fail(FK_ERR_SHAPE, "a traversal group width of 0 has no tiles in it");

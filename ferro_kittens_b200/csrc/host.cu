@@ -177,8 +177,14 @@ extern "C" int fk_tensor_map(void* map_out, const fk_layout_t* layout, uint32_t 
     if (status != FK_OK) return status;
     // The driver call wants a context current on the calling thread; a thread that has made no
     // runtime call yet has none (the encode then fails with CUDA_ERROR_INVALID_CONTEXT). A null
-    // free binds the device's primary context and does nothing else.
-    FK_CUDA(cudaFree(nullptr));
+    // free binds the device's primary context and does nothing else. Once per thread: the call is
+    // not allowed while a stream of the thread is capturing, and a thread that captures has made
+    // runtime calls before.
+    static thread_local bool bound = false;
+    if (!bound) {
+        FK_CUDA(cudaFree(nullptr));
+        bound = true;
+    }
 
     cuuint64_t dims[5], strides[4];
     cuuint32_t boxes[5], element_strides[5];

@@ -22,6 +22,11 @@ F16_OPERANDS = 1
 ACCUMULATE = 2
 #: max(x, 0) before the rounding (the `Relu` unary map, src/reg.rs:261).
 RELU = 4
+#: Pick the kernel instead of letting the launch choose: one CTA per [128, 128] tile (the reference's
+#: narrow entry for launches at or below half a wave, examples/src/gemm_sol.rs:1063), or the wide
+#: persistent two-CTA clusters.
+TILE_NARROW = 8
+TILE_WIDE = 16
 
 
 def tile_grid(m: int, n: int) -> tuple[int, int]:
@@ -75,7 +80,7 @@ def workspace(m: int, n: int, k: int, device, sm_count: int | None = None) -> to
 
 def run(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor | None = None, group: int = GROUP,
         status: torch.Tensor | None = None, accumulate: bool = False, bias: torch.Tensor | None = None,
-        relu: bool = False, workspace: torch.Tensor | None = None) -> torch.Tensor:
+        relu: bool = False, workspace: torch.Tensor | None = None, tile: str | None = None) -> torch.Tensor:
     """``C[m, n] (+)= map(sum_k A[m, k] * B[n, k] + bias[n])``; A is [m, k], B is [n, k], both bf16 or both fp16 on
     one GPU, C bf16. With ``accumulate`` the rounded product is added into ``c`` (in bf16, by the
     copy engine), which must then be given and hold values. With a ``workspace`` (see :func:`workspace`) a
@@ -102,8 +107,10 @@ def run(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor | None = None, group: 
     if bias is not None and (not bias.is_cuda or bias.dtype != torch.bfloat16 or bias.shape != (n,)
                              or not bias.is_contiguous()):
         raise ValueError("bias must be a contiguous bfloat16 [n] tensor on the device")
+    if tile not in (None, "narrow", "wide"):
+        raise ValueError("tile is None (the launch chooses), 'narrow' or 'wide'")
     flags = ((F16_OPERANDS if a.dtype == torch.float16 else 0) | (ACCUMULATE if accumulate else 0)
-             | (RELU if relu else 0))
+             | (RELU if relu else 0) | {None: 0, "narrow": TILE_NARROW, "wide": TILE_WIDE}[tile])
     if workspace is not None and (not workspace.is_cuda or not workspace.is_contiguous()):
         raise ValueError("the workspace must be a contiguous tensor on the device")
     with torch.cuda.device(a.device):

@@ -167,6 +167,14 @@ int fk_gemm_bf16(const void* a, const void* b, void* c, uint32_t m, uint32_t n, 
  *                         values beforehand.
  *   FK_GEMM_RELU          max(x, 0) on the fp32 value before its one rounding to bf16: the `Relu`
  *                         unary map on a register tile (src/reg.rs:261, 1502-1504).
+ *   FK_GEMM_TILE_NARROW / FK_GEMM_TILE_WIDE  pick the kernel instead of letting the launch choose:
+ *                         the wide one (persistent two-CTA clusters, [512, 256] items) or the
+ *                         narrow one (one CTA per [128, 128] tile, two CTAs an SM), which the
+ *                         reference ships as its own entry for launches at or below half a wave
+ *                         (`gemm_sol_m256_n128`, examples/src/gemm_sol.rs:1063, dispatch :1335-1337).
+ *                         Unasked, a launch of at most 128 narrow tiles, or of at most two per SM
+ *                         with K <= 2048, takes the narrow tile. Same operand maps, same C map,
+ *                         same results.
  * The `_fused` entries also take `bias`: null, or n bf16 values (16-byte aligned) added per column
  * in fp32 before the rounding -- a column vector every row shares (`load_vec` / `add_col`,
  * src/global.rs:410-416, as examples/src/layernorm.rs:200-203 uses them for beta). Bias first,
@@ -175,6 +183,8 @@ int fk_gemm_bf16(const void* a, const void* b, void* c, uint32_t m, uint32_t n, 
 #define FK_GEMM_F16_OPERANDS 1u
 #define FK_GEMM_ACCUMULATE 2u
 #define FK_GEMM_RELU 4u
+#define FK_GEMM_TILE_NARROW 8u
+#define FK_GEMM_TILE_WIDE 16u
 int fk_gemm_launch_fused(const void* a_map, const void* b_map, const void* c_map, const void* bias, uint32_t m,
                          uint32_t n, uint32_t k, uint32_t group, uint32_t flags, void* stream,
                          uint32_t* device_status);
@@ -193,8 +203,8 @@ int fk_gemm(const void* a, const void* b, void* c, uint32_t m, uint32_t n, uint3
  * (`tma_store_add_2d`, src/shared.rs:974-1009, on fp32 here: the sums are rounded to bf16 ONCE,
  * after the last run, by whichever run arrives last), bias / ReLU / accumulate as in fk_gemm_fused.
  *   fk_gemm_workspace_bytes: bytes the shape needs on a device of `sm_count` SMs, 0 when it
- *     would not be split (at least half a wave of items, or K under 8192: the runs' fp32 tiles
- *     cross the L2 twice, which a shallower K does not repay);
+ *     would not be split (at least half a wave of items, or K under 16384: the runs' fp32 tiles
+ *     cross the L2 twice, which a shallower K does not repay -- the narrow tile serves those);
  *   `workspace`: device memory, 16-byte aligned, ALL ZERO before its first use -- every launch
  *     leaves it all zero again, so it is cleared once, not per call. Launches that share a
  *     workspace must not overlap on the device. With a null workspace, or a shape that would not

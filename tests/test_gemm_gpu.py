@@ -25,9 +25,11 @@ def _to_words(tensor: torch.Tensor) -> np.ndarray:
     return tensor.view(torch.int16).cpu().numpy().view(np.uint16)
 
 
-def _run_checked(a, b, group=gemm.GROUP):
+def _run_checked(a, b, group=gemm.GROUP, tile="wide"):
+    """These are the gates of the wide kernel (the replacement of `gemm_cg2_staged_x8x4`): small
+    shapes would otherwise take the narrow tile, which has its own gates in test_gemm_variants_gpu.py."""
     status = gemm.new_status(a.device)
-    c = gemm.run(a, b, group=group, status=status)
+    c = gemm.run(a, b, group=group, status=status, tile=tile)
     gemm.check_status(status)
     return c
 
@@ -56,13 +58,15 @@ def test_integer_operands_other_shapes_exact(device, shape):
     assert wrong == 0, f"{wrong} wrong, first at {first}"
 
 
-def test_config_1_uniform_1024_cubed(device):
-    """GEMM 1024^3, entries uniform[-1, 1) from seed 0, against the oracle over the same bf16 words."""
+@pytest.mark.parametrize("tile", ["wide", None])
+def test_config_1_uniform_1024_cubed(device, tile):
+    """GEMM 1024^3, entries uniform[-1, 1) from seed 0, against the oracle over the same bf16 words:
+    on the wide kernel, and as a launch this small runs when nothing is asked for (the narrow tile)."""
     m = n = k = 1024
     generator = torch.Generator(device="cpu").manual_seed(0)
     a = (torch.rand((m, k), generator=generator) * 2 - 1).to(torch.bfloat16)
     b = (torch.rand((n, k), generator=generator) * 2 - 1).to(torch.bfloat16)
-    c = _run_checked(a.to(device), b.to(device))
+    c = _run_checked(a.to(device), b.to(device), tile=tile)
     a_words, b_words = _to_words(a), _to_words(b)
     expected, exact = oracle.gemm_rows(a_words, b_words, 0, m, want_f64=True)
     got = oracle.bf16_to_f32(_to_words(c)).astype(np.float64)
@@ -114,6 +118,34 @@ def test_host_buffer_entry_point(device, shape):
     gemm.run_host(a, b, c, m, n, k)
     wrong, _, _ = oracle.gemm_check_c(c, m, n, k)
     assert wrong == 0
+
+
+def test_two_threads_calling_the_host_entry_on_one_device_take_turns(device):
+    """The host-buffer entries share the device's staging buffers, streams and status words and hold
+    the device's lock for the whole call: two threads with different shapes (the second outgrows the
+    first's staging, which is freed and re-made) both get the exact answer."""
+    import threading
+
+    shapes = [(1024, 768, 256), (2048, 1280, 512), (512, 256, 1088)]
+    results = {}
+
+    def worker(index, shape):
+        m, n, k = shape
+        a, b = oracle.gemm_stage("a", m, k), oracle.gemm_stage("b", n, k)
+        wrong = 0
+        for _ in range(4):
+            c = np.full((m, n), 0xFFFF, dtype=np.uint16)
+            torch.cuda.set_device(device)
+            gemm.run_host(a, b, c, m, n, k)
+            wrong += oracle.gemm_check_c(c, m, n, k)[0]
+        results[index] = wrong
+
+    threads = [threading.Thread(target=worker, args=(index, shape)) for index, shape in enumerate(shapes)]
+    for thread in threads:
+        thread.start()
+    for thread in threads:
+        thread.join()
+    assert results == {0: 0, 1: 0, 2: 0}
 
 
 @pytest.mark.parametrize("blocks", [1, 4])

@@ -100,7 +100,7 @@ def test_unknown_flags_and_missing_c_are_refused(device):
         gemm.run(a, a, accumulate=True)
     c = torch.zeros((256, 256), dtype=torch.bfloat16, device=device)
     with pytest.raises(FerroKittensError, match="unknown GEMM flags"):
-        check(library().fk_gemm(a.data_ptr(), a.data_ptr(), c.data_ptr(), 256, 256, 64, 256, 8, 8,
+        check(library().fk_gemm(a.data_ptr(), a.data_ptr(), c.data_ptr(), 256, 256, 64, 256, 8, 32,
                                 torch.cuda.current_stream().cuda_stream, None))
 
 
@@ -149,3 +149,72 @@ def test_bias_guards(device):
         gemm.run(a, a, bias=torch.zeros(128, dtype=torch.bfloat16, device=device))
     with pytest.raises(ValueError, match="bias must be"):
         gemm.run(a, a, bias=torch.zeros(256, dtype=torch.float32, device=device))
+
+
+# ---- the narrow tile: one CTA per [128, 128] tile (the reference's entry for launches at or below
+# ---- half a wave, examples/src/gemm_sol.rs:1063, 1335-1337), asked for by name and chosen by default
+
+@pytest.mark.parametrize("shape", [(256, 256, 64), (512, 256, 256), (1024, 768, 512), (768, 1280, 1088),
+                                   (2048, 2048, 256), (4096, 4096, 256)])
+def test_narrow_tile_is_exact_on_the_reference_gate(device, shape):
+    """One k-block, a ring that wraps (17 k-blocks on 3 stages), more tiles than two CTAs per SM hold
+    at once (1024 on 148 SMs): `==` on bf16 words against the reference's integer check."""
+    m, n, k = shape
+    a = _device_words(oracle.gemm_stage("a", m, k), device, torch.bfloat16)
+    b = _device_words(oracle.gemm_stage("b", n, k), device, torch.bfloat16)
+    status = gemm.new_status(device)
+    c = gemm.run(a, b, status=status, tile="narrow")
+    torch.cuda.synchronize(device)
+    gemm.check_status(status)
+    wrong, _, first = oracle.gemm_check_c(_words(c), m, n, k)
+    assert wrong == 0, f"{wrong} of {m * n} wrong, first at {first}"
+    wide = gemm.run(a, b, tile="wide")
+    assert torch.equal(c, wide)
+
+
+def test_narrow_tile_fused_epilogue_fp16_and_accumulate(device):
+    m, n, k = 512, 512, 128
+    a = _device_words(oracle.gemm_stage_f16("a", m, k), device, torch.float16)
+    b = _device_words(oracle.gemm_stage_f16("b", n, k), device, torch.float16)
+    bias_values = ((np.arange(n) * 3) % 13 - 6).astype(np.float32)
+    bias = _device_words(oracle.f32_to_bf16(bias_values), device, torch.bfloat16)
+    held = oracle.f32_to_bf16(np.full((m, n), 1.5, dtype=np.float32))
+    c = _device_words(held.copy(), device, torch.bfloat16)
+    status = gemm.new_status(device)
+    gemm.run(a, b, c, status=status, accumulate=True, bias=bias, relu=True, tile="narrow")
+    torch.cuda.synchronize(device)
+    gemm.check_status(status)
+    fused = oracle.f32_to_bf16(np.maximum(oracle.gemm_exact(m, n, k) + bias_values[None, :], np.float32(0.0)))
+    assert np.array_equal(_words(c), oracle.bf16_add_words(held, fused))
+
+
+def test_narrow_tile_respects_the_leading_dimension(device):
+    m, n, k, ldc = 512, 256, 256, 384
+    a = _device_words(oracle.gemm_stage("a", m, k), device, torch.bfloat16)
+    b = _device_words(oracle.gemm_stage("b", n, k), device, torch.bfloat16)
+    backing = torch.full((m, ldc), 7.0, dtype=torch.bfloat16, device=device)
+    c = backing[:, :n]
+    gemm.run(a, b, c, tile="narrow")
+    torch.cuda.synchronize(device)
+    assert oracle.gemm_check_c(_words(c), m, n, k)[0] == 0
+    assert (backing[:, n:] == 7.0).all()
+
+
+def test_small_shallow_launches_take_the_narrow_tile_by_default(device):
+    """Both kernels accumulate a tile's k-blocks in the same order, so their results are equal bit for
+    bit and the choice is not observable in the values; what is checked is that the default launch of
+    a small, shallow problem is valid and equal to the forced ones, and that the flags are policed."""
+    m, n, k = 1024, 1024, 512
+    generator = torch.Generator(device="cpu").manual_seed(17)
+    a = (torch.rand((m, k), generator=generator) * 2 - 1).to(torch.bfloat16).to(device)
+    b = (torch.rand((n, k), generator=generator) * 2 - 1).to(torch.bfloat16).to(device)
+    default, narrow, wide = gemm.run(a, b), gemm.run(a, b, tile="narrow"), gemm.run(a, b, tile="wide")
+    reference = a.double() @ b.double().T
+    for c in (default, narrow, wide):
+        assert (c.double() - reference).abs().max().item() <= 1e-2 * k ** 0.5
+    assert torch.equal(default, narrow)
+    with pytest.raises(ValueError, match="tile is None"):
+        gemm.run(a, b, tile="tall")
+    with pytest.raises(FerroKittensError, match="both asked for"):
+        check(library().fk_gemm(a.data_ptr(), b.data_ptr(), default.data_ptr(), m, n, k, n, 8, 8 | 16,
+                                torch.cuda.current_stream().cuda_stream, None))
