@@ -52,6 +52,18 @@ __device__ __forceinline__ void cluster_sync() {
 __device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
     asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
+/// 16 bytes into the shared memory of any CTA of the cluster (a shared::cluster address from `mapa`).
+__device__ __forceinline__ void st_shared_cluster_v4(uint32_t cluster_addr, uint32_t a, uint32_t b, uint32_t c,
+                                                     uint32_t d) {
+    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(a), "r"(b), "r"(c),
+                 "r"(d)
+                 : "memory");
+}
+/// Makes what peer CTAs wrote into this CTA's shared memory before their release-arrive visible
+/// to the loads that follow a wait on the barrier they arrived on.
+__device__ __forceinline__ void fence_acq_rel_cluster() {
+    asm volatile("fence.acq_rel.cluster;" ::: "memory");
+}
 
 // ---------------------------------------------------------------- mbarrier
 
@@ -415,6 +427,10 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
                                              uint32_t d) {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c),
                  "r"(d)
+                 : "memory");
+}
+__device__ __forceinline__ void ld_shared_v4(uint32_t addr, uint32_t (&v)[4]) {
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(addr)
                  : "memory");
 }
 __device__ __forceinline__ float ex2_approx(float x) {

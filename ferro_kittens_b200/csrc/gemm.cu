@@ -563,10 +563,16 @@ constexpr uint32_t kEpilogueWarps = 4;
 constexpr uint32_t kThreads = (2 + kEpilogueWarps) * 32;
 constexpr uint32_t kTileBytes = kTile * kBlockK * 2;  // one [128, 64] operand tile
 constexpr uint32_t kTmemColumns = kTile;
+// K split across a cluster: the CTAs of a cluster take consecutive runs of one tile's k-blocks and
+// the others hand their fp32 tiles to the first through distributed shared memory, into its
+// operand ring, which is idle by then: one [128, 128] fp32 tile, 64 KiB, per contributor.
+constexpr uint32_t kMaxSlices = 4;
+constexpr uint32_t kPartialBytes = kTile * kTile * 4;
+static_assert((kMaxSlices - 1) * kPartialBytes <= 2 * kStagesAlone * kTileBytes, "the partial tiles must fit the ring");
 
 template <uint32_t kStages>
 struct Plan {
-    SharedPlan a_ring, b_ring, bands, full, empty, acc_full, tmem_slot, stop, end;
+    SharedPlan a_ring, b_ring, bands, full, empty, acc_full, go, partial_full, tmem_slot, stop, end;
     constexpr Plan()
         : a_ring(SharedPlan{}.tile_ring(kTile, kBlockK, 2, kStages)),
           b_ring(a_ring.tile_ring(kTile, kBlockK, 2, kStages)),
@@ -574,7 +580,9 @@ struct Plan {
           full(bands.semaphores(kStages)),
           empty(full.semaphores(kStages)),
           acc_full(empty.semaphore()),
-          tmem_slot(acc_full.tmem_slot()),
+          go(acc_full.semaphore()),
+          partial_full(go.semaphore()),
+          tmem_slot(partial_full.tmem_slot()),
           stop(tmem_slot.word()),
           end(stop) {}
 };
@@ -586,7 +594,13 @@ constexpr uint32_t shared_bytes() {
 static_assert(2 * (shared_bytes<kStagesShared>() + 1024) <= 233472, "two narrow CTAs must fit one SM's shared memory");
 static_assert(shared_bytes<kStagesAlone>() <= 232448, "plan exceeds the opt-in shared memory of an sm_100 CTA");
 
-template <uint32_t kStages>
+// Byte offset of 16-byte chunk `chunk` (0..31) of row `row` inside a partial tile: the chunk index
+// is folded with the row so that the eight lanes of a quarter-warp touch eight different bank groups.
+__device__ __forceinline__ uint32_t partial_offset(uint32_t row, uint32_t chunk) {
+    return row * (kTile * 4) + (((chunk ^ row) & 31u) << 4);
+}
+
+template <uint32_t kStages, bool kSliced>
 __global__ void __launch_bounds__(kThreads, kStages == kStagesShared ? 2 : 1)
     gemm_bf16_narrow_kernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap b_map,
                             const __grid_constant__ CUtensorMap c_map, const Schedule plan, uint32_t* status) {
@@ -605,6 +619,8 @@ __global__ void __launch_bounds__(kThreads, kStages == kStagesShared ? 2 : 1)
     const uint32_t full = base + kPlan.full.at;
     const uint32_t empty = base + kPlan.empty.at;
     const uint32_t acc_full = base + kPlan.acc_full.at;
+    const uint32_t go = base + kPlan.go.at;
+    const uint32_t partial_full = base + kPlan.partial_full.at;
     const uint32_t slot = base + kPlan.tmem_slot.at;
     volatile uint32_t* stop_flag = reinterpret_cast<volatile uint32_t*>(dynamic_shared + kPlan.stop.at);
     volatile uint32_t* slot_ptr = reinterpret_cast<volatile uint32_t*>(dynamic_shared + kPlan.tmem_slot.at);
@@ -613,6 +629,12 @@ __global__ void __launch_bounds__(kThreads, kStages == kStagesShared ? 2 : 1)
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t row0 = kTile * blockIdx.y;
     const uint32_t column0 = kTile * blockIdx.x;
+    // This CTA's run of k-blocks: all of them, or its slice of the cluster's.
+    const uint32_t slices = kSliced ? gridDim.z : 1u;
+    const uint32_t slice = kSliced ? cluster_ctarank() : 0u;
+    const uint32_t run = (plan.k_blocks + slices - 1) / slices;
+    const uint32_t k0 = slice * run;
+    const uint32_t k1 = k0 + run < plan.k_blocks ? k0 + run : plan.k_blocks;
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
@@ -620,6 +642,8 @@ __global__ void __launch_bounds__(kThreads, kStages == kStagesShared ? 2 : 1)
             mbar_init(empty + 8 * s, 1);
         }
         mbar_init(acc_full, 1);
+        mbar_init(go, 1);
+        mbar_init(partial_full, (slices > 1 ? slices - 1 : 1) * kEpilogueWarps);
         *stop_flag = 0;
         fence_mbarrier_init();
         prefetch_tensormap(&a_map);
@@ -632,6 +656,7 @@ __global__ void __launch_bounds__(kThreads, kStages == kStagesShared ? 2 : 1)
     }
     tc_fence_before_sync();
     __syncthreads();
+    if (kSliced) cluster_sync();  // every CTA's barriers exist before a peer arrives on them
     tc_fence_after_sync();
     const uint32_t tmem = *slot_ptr;
     const StallSite site{status, stop_flag, 0};
@@ -642,9 +667,9 @@ __global__ void __launch_bounds__(kThreads, kStages == kStagesShared ? 2 : 1)
     if (warp == 0) {
         // ------------------------------------------------ producer
         if (lane == 0) {
-            for (uint32_t k = 0; k < plan.k_blocks; ++k) {
-                const uint32_t s = k % kStages;
-                if (!mbar_wait(empty + 8 * s, ((k / kStages) & 1u) ^ 1u, prompt, kStallProducer, k)) break;
+            for (uint32_t k = k0; k < k1; ++k) {
+                const uint32_t s = (k - k0) % kStages;
+                if (!mbar_wait(empty + 8 * s, (((k - k0) / kStages) & 1u) ^ 1u, prompt, kStallProducer, k)) break;
                 mbar_arrive_expect_tx(full + 8 * s, 2 * kTileBytes);
                 const int column = static_cast<int>(kBlockK * k);
                 tma_load_2d(a_ring + s * kTileBytes, &a_map, column, static_cast<int>(row0), full + 8 * s);
@@ -657,9 +682,9 @@ __global__ void __launch_bounds__(kThreads, kStages == kStagesShared ? 2 : 1)
         // MMA is 64 cycles of the pipe).
         if (elect_one()) {
             bool live = true;
-            for (uint32_t k = 0; k < plan.k_blocks; ++k) {
-                const uint32_t s = k % kStages;
-                if (!mbar_wait(full + 8 * s, (k / kStages) & 1u, prompt, kStallMmaFull, k)) {
+            for (uint32_t k = k0; k < k1; ++k) {
+                const uint32_t s = (k - k0) % kStages;
+                if (!mbar_wait(full + 8 * s, ((k - k0) / kStages) & 1u, prompt, kStallMmaFull, k)) {
                     live = false;
                     break;
                 }
@@ -669,7 +694,7 @@ __global__ void __launch_bounds__(kThreads, kStages == kStagesShared ? 2 : 1)
 #pragma unroll
                 for (uint32_t chunk = 0; chunk < kBlockK / 16; ++chunk) {
                     const uint64_t step = (chunk * kKMajorChunkBytes) >> 4;
-                    mma_ss<1>(tmem, a_desc + step, b_desc + step, plan.idesc, (k != 0) | chunk);
+                    mma_ss<1>(tmem, a_desc + step, b_desc + step, plan.idesc, (k != k0) | chunk);
                 }
                 mma_commit<1>(empty + 8 * s);
             }
@@ -680,15 +705,59 @@ __global__ void __launch_bounds__(kThreads, kStages == kStagesShared ? 2 : 1)
         const uint32_t quadrant = warp & 3u;
         const uint32_t band = bands + (warp - 2) * kBandBytes;
         const uint32_t t_row = tmem_address(tmem, 32 * quadrant, 0);
-        if (mbar_wait(acc_full, 0, site, kStallEpilogue, 0)) {
-            tc_fence_after_sync();
+        bool live = mbar_wait(acc_full, 0, site, kStallEpilogue, 0);
+        if (live) tc_fence_after_sync();
+        const uint32_t row = 32 * quadrant + lane;  // of the tile
+        if (kSliced && live && slice != 0) {
+            // A contributor: once the first CTA's ring is idle (`go`), this warp's 32 rows of the fp32
+            // tile go into its slot there, then the warp counts itself in.
+            live = mbar_wait(go, 0, site, kStallEpilogue, 1);
+            if (live) {
+                const uint32_t slot_base = a_ring + (slice - 1) * kPartialBytes;
+#pragma unroll 1
+                for (uint32_t part = 0; part < kTile / 32; ++part) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(t_row + 32 * part, v);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (uint32_t chunk = 0; chunk < 8; ++chunk)
+                        st_shared_cluster_v4(mapa(slot_base + partial_offset(row, 8 * part + chunk), 0), v[4 * chunk],
+                                             v[4 * chunk + 1], v[4 * chunk + 2], v[4 * chunk + 3]);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(mapa(partial_full, 0));
+            }
+        } else if (live) {
+            if (kSliced) {
+                // The first CTA: its MMAs have retired, so its ring is free for the others' tiles.
+                if (warp == 2 && lane == 0)
+                    for (uint32_t peer = 1; peer < slices; ++peer) mbar_arrive_cluster(mapa(go, peer));
+                live = mbar_wait(partial_full, 0, site, kStallEpilogue, 2);
+                fence_acq_rel_cluster();
+            }
             const int c_row = static_cast<int>(row0 + 32 * quadrant);
 #pragma unroll 1
-            for (uint32_t pass = 0; pass < kTile / kStageColumns; ++pass) {
+            for (uint32_t pass = 0; live && pass < kTile / kStageColumns; ++pass) {
                 uint32_t lo[32], hi[32], packed[32];
                 tmem_ld_32x32(t_row + pass * kStageColumns, lo);
                 tmem_ld_32x32(t_row + pass * kStageColumns + 32, hi);
                 tmem_wait_ld();
+                if (kSliced) {
+                    for (uint32_t peer = 1; peer < slices; ++peer) {
+                        const uint32_t slot_base = a_ring + (peer - 1) * kPartialBytes;
+#pragma unroll
+                        for (uint32_t chunk = 0; chunk < 8; ++chunk) {
+                            uint32_t x[4], y[4];
+                            ld_shared_v4(slot_base + partial_offset(row, 16 * pass + chunk), x);
+                            ld_shared_v4(slot_base + partial_offset(row, 16 * pass + 8 + chunk), y);
+#pragma unroll
+                            for (uint32_t i = 0; i < 4; ++i) {
+                                lo[4 * chunk + i] = __float_as_uint(__uint_as_float(lo[4 * chunk + i]) + __uint_as_float(x[i]));
+                                hi[4 * chunk + i] = __float_as_uint(__uint_as_float(hi[4 * chunk + i]) + __uint_as_float(y[i]));
+                            }
+                        }
+                    }
+                }
                 finish_pass(lo, hi, plan, column0 + pass * kStageColumns, packed);
                 if (lane == 0) tma_store_wait_read<0>();
                 __syncwarp();
@@ -717,6 +786,7 @@ __global__ void __launch_bounds__(kThreads, kStages == kStagesShared ? 2 : 1)
     }
     tc_fence_before_sync();
     __syncthreads();
+    if (kSliced) cluster_sync();  // no CTA leaves while a peer may still write into it or arrive on it
     if (warp == 1) tmem_dealloc<1>(tmem, kTmemColumns);
 }
 
@@ -818,20 +888,42 @@ extern "C" int fk_gemm_launch_fused(const void* a_map, const void* b_map, const 
                                             (flags & FK_GEMM_F16_OPERANDS) ? 0u : 1u);
         const dim3 tiles(n / gemm::narrow::kTile, m / gemm::narrow::kTile, 1);
         if (tiles.y > 65535) return fk_fail(FK_ERR_SHAPE, "%u rows is past what the narrow tile's grid takes", m);
-        const auto launch_narrow = [&](auto kernel, uint32_t bytes) -> int {
+        const auto launch_narrow = [&](auto kernel, uint32_t bytes, uint32_t slices) -> int {
             const int narrow_admitted = fk_admit_shared_plan(reinterpret_cast<const void*>(kernel), bytes, &limit);
             if (narrow_admitted != FK_OK) return narrow_admitted;
-            kernel<<<tiles, gemm::narrow::kThreads, bytes, static_cast<cudaStream_t>(stream)>>>(
-                *static_cast<const CUtensorMap*>(a_map), *static_cast<const CUtensorMap*>(b_map),
-                *static_cast<const CUtensorMap*>(c_map), plan, device_status);
-            FK_CUDA(cudaGetLastError());
+            cudaLaunchConfig_t config = {};
+            config.gridDim = dim3(tiles.x, tiles.y, slices);
+            config.blockDim = dim3(gemm::narrow::kThreads, 1, 1);
+            config.dynamicSmemBytes = bytes;
+            config.stream = static_cast<cudaStream_t>(stream);
+            cudaLaunchAttribute cluster;
+            cluster.id = cudaLaunchAttributeClusterDimension;
+            cluster.val.clusterDim.x = 1, cluster.val.clusterDim.y = 1, cluster.val.clusterDim.z = slices;
+            config.attrs = &cluster;
+            config.numAttrs = slices > 1 ? 1 : 0;
+            FK_CUDA(cudaLaunchKernelEx(&config, kernel, *static_cast<const CUtensorMap*>(a_map),
+                                       *static_cast<const CUtensorMap*>(b_map), *static_cast<const CUtensorMap*>(c_map),
+                                       plan, device_status));
             return FK_OK;
         };
-        if (uint64_t(tiles.x) * tiles.y <= static_cast<uint64_t>(sm_count))
-            return launch_narrow(gemm::narrow::gemm_bf16_narrow_kernel<gemm::narrow::kStagesAlone>,
-                                 gemm::narrow::shared_bytes<gemm::narrow::kStagesAlone>());
-        return launch_narrow(gemm::narrow::gemm_bf16_narrow_kernel<gemm::narrow::kStagesShared>,
-                             gemm::narrow::shared_bytes<gemm::narrow::kStagesShared>());
+        const uint64_t count = uint64_t(tiles.x) * tiles.y;
+        // Few tiles and a deep K: a cluster per tile, each CTA a run of the k-blocks. The hand-over
+        // (two cluster rendezvous, 64 KiB per contributor through distributed shared memory, the
+        // first CTA summing them) costs 5-7 us, a k-block on a lone CTA ~0.25 us: worth it from 128
+        // k-blocks on, in runs of at least 32 (1024 x 1024 x 8192: 30.4 -> 24.5 us; 512 x 512 x 16384:
+        // 56 -> 26; but 512 x 768 x 2048 in four runs of 8: 10.4 -> 17.5).
+        uint32_t slices = 1;
+        while (plan.k_blocks >= 128 && slices < gemm::narrow::kMaxSlices &&
+               count * (2 * slices) <= static_cast<uint64_t>(sm_count) && plan.k_blocks / (2 * slices) >= 32)
+            slices *= 2;
+        if (slices > 1)
+            return launch_narrow(gemm::narrow::gemm_bf16_narrow_kernel<gemm::narrow::kStagesAlone, true>,
+                                 gemm::narrow::shared_bytes<gemm::narrow::kStagesAlone>(), slices);
+        if (count <= static_cast<uint64_t>(sm_count))
+            return launch_narrow(gemm::narrow::gemm_bf16_narrow_kernel<gemm::narrow::kStagesAlone, false>,
+                                 gemm::narrow::shared_bytes<gemm::narrow::kStagesAlone>(), 1);
+        return launch_narrow(gemm::narrow::gemm_bf16_narrow_kernel<gemm::narrow::kStagesShared, false>,
+                             gemm::narrow::shared_bytes<gemm::narrow::kStagesShared>(), 1);
     }
     const uint32_t grid = 2 * (plan.items < clusters ? plan.items : clusters);
     // The one-launch kernel never touches its fourth map; it is handed C's.
@@ -895,18 +987,23 @@ extern "C" int fk_gemm_fused(const void* a, const void* b, void* c, const void* 
 // FK_GEMM_ACCUMULATE would round once per run) and the last to arrive rounds once.
 namespace {
 
-// Measured on B200 (back-to-back launches, one launch / split / cuBLAS, microseconds):
+// Measured on B200 (back-to-back launches, wide kernel in one launch / split / cuBLAS, microseconds):
 // 1024 x 1024 x 4096: 27 / 37 / 12; 1024 x 1024 x 8192: 66 / 39 / 19; 1024 x 1024 x 16384: 91 / 51 / 34;
 // 512 x 512 x 16384: 86 / 38 / 23; 256 x 256 x 32768: 162 / 37 / 19. The runs' fp32 tiles cross the L2
-// twice (splits x M x N x 4 bytes added, M x N x 4 read back and cleared), which a 64-deep K does not
-// repay, and up to K = 8192 the narrow tile on its own beats the split (1024 x 1024 x 8192: wide 45,
-// split 36, narrow 30): split only from 256 k-blocks on, into runs of at least 32.
-constexpr uint32_t kMinSplitDepth = 256;
+// twice (splits x M x N x 4 bytes added, M x N x 4 read back and cleared), and the narrow kernel with K
+// cut across a cluster of four beats the split wherever it has tiles enough (512 x 512 x 16384: 26 us,
+// 1024 x 1024 x 16384: 38), so what is left for this path is a handful of tiles under a very deep K,
+// where four CTAs a tile are still too few: at most 16 narrow tiles, from 512 k-blocks on, in runs of
+// at least 32.
+constexpr uint32_t kMinSplitDepth = 512;
 constexpr uint32_t kMinSplitBlocks = 32;
+constexpr uint32_t kMaxSplitTiles = 16;
 
 // How a shape would be split on `clusters` resident clusters: 1 = not at all.
 uint32_t split_count(const gemm::Schedule& plan, uint32_t clusters) {
-    if (plan.items == 0 || plan.items * 2 > clusters || plan.k_blocks < kMinSplitDepth) return 1;
+    const uint64_t narrow_tiles = uint64_t(plan.m / gemm::narrow::kTile) * (plan.tiles_n * (gemm::kBlockN / gemm::narrow::kTile));
+    if (plan.items == 0 || plan.items * 2 > clusters || plan.k_blocks < kMinSplitDepth || narrow_tiles > kMaxSplitTiles)
+        return 1;
     const uint32_t by_clusters = clusters / plan.items;
     const uint32_t by_depth = plan.k_blocks / kMinSplitBlocks;
     const uint32_t splits = by_clusters < by_depth ? by_clusters : by_depth;

@@ -173,8 +173,10 @@ int fk_gemm_bf16(const void* a, const void* b, void* c, uint32_t m, uint32_t n, 
  *                         reference ships as its own entry for launches at or below half a wave
  *                         (`gemm_sol_m256_n128`, examples/src/gemm_sol.rs:1063, dispatch :1335-1337).
  *                         Unasked, a launch of at most 128 narrow tiles, or of at most two per SM
- *                         with K <= 2048, takes the narrow tile. Same operand maps, same C map,
- *                         same results.
+ *                         with K <= 2048, takes the narrow tile; with K >= 8192 and SMs to spare
+ *                         a tile's k-blocks are cut across a cluster of two or four CTAs that
+ *                         hand their fp32 tiles to the first through distributed shared memory.
+ *                         Same operand maps, same C map, same results up to fp32 summation order.
  * The `_fused` entries also take `bias`: null, or n bf16 values (16-byte aligned) added per column
  * in fp32 before the rounding -- a column vector every row shares (`load_vec` / `add_col`,
  * src/global.rs:410-416, as examples/src/layernorm.rs:200-203 uses them for beta). Bias first,
@@ -203,8 +205,9 @@ int fk_gemm(const void* a, const void* b, void* c, uint32_t m, uint32_t n, uint3
  * (`tma_store_add_2d`, src/shared.rs:974-1009, on fp32 here: the sums are rounded to bf16 ONCE,
  * after the last run, by whichever run arrives last), bias / ReLU / accumulate as in fk_gemm_fused.
  *   fk_gemm_workspace_bytes: bytes the shape needs on a device of `sm_count` SMs, 0 when it
- *     would not be split (at least half a wave of items, or K under 16384: the runs' fp32 tiles
- *     cross the L2 twice, which a shallower K does not repay -- the narrow tile serves those);
+ *     would not be split: the runs' fp32 tiles cross the L2 twice, and the narrow tile with K cut
+ *     across a cluster of CTAs (every GEMM entry does that by itself) is faster wherever a launch
+ *     has tiles enough, so this path takes launches of at most 16 narrow tiles with K >= 32768;
  *   `workspace`: device memory, 16-byte aligned, ALL ZERO before its first use -- every launch
  *     leaves it all zero again, so it is cleared once, not per call. Launches that share a
  *     workspace must not overlap on the device. With a null workspace, or a shape that would not

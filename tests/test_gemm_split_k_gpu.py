@@ -32,20 +32,20 @@ def _run(a, b, workspace, **kwargs):
 def test_which_shapes_split(device):
     sms = torch.cuda.get_device_properties(device).multi_processor_count
     lib = library()
-    assert lib.fk_gemm_workspace_bytes(1024, 1024, 16384, sms) >= 1024 * 1024 * 4
-    assert lib.fk_gemm_workspace_bytes(512, 768, 16384, sms) >= 512 * 768 * 4
+    assert lib.fk_gemm_workspace_bytes(256, 256, 32768, sms) >= 256 * 256 * 4
+    assert lib.fk_gemm_workspace_bytes(512, 512, 65536, sms) >= 512 * 512 * 4
     assert lib.fk_gemm_workspace_bytes(16384, 16384, 16384, sms) == 0  # many waves
-    assert lib.fk_gemm_workspace_bytes(2048, 2048, 16384, sms) == 0    # already most of a wave
-    assert lib.fk_gemm_workspace_bytes(1024, 1024, 8192, sms) == 0     # too shallow to repay the fp32 round trip
+    assert lib.fk_gemm_workspace_bytes(1024, 1024, 32768, sms) == 0    # tiles enough for the cluster-sliced narrow kernel
+    assert lib.fk_gemm_workspace_bytes(256, 256, 16384, sms) == 0      # too shallow to repay the fp32 round trip
     assert lib.fk_gemm_workspace_bytes(512, 256, 256, sms) == 0        # four k-blocks: nothing to cut
     assert lib.fk_gemm_workspace_bytes(500, 256, 256, sms) == 0        # not a shape at all
     assert gemm.workspace(16384, 16384, 16384, device) is None
 
 
-# The reference's integer gate (examples/src/gemm.rs:434-440, 544-578) at depths that split: a square
-# cut four ways, a three-tile strip, a K that does not divide into equal runs (257 k-blocks: seven runs
-# of 33 and one of 26) under a ragged last row tile, and one tile cut eight ways.
-@pytest.mark.parametrize("shape", [(1024, 1024, 16384), (512, 768, 16384), (768, 512, 16448), (256, 256, 16384)])
+# The reference's integer gate (examples/src/gemm.rs:434-440, 544-578) at depths that split: one tile
+# cut sixteen ways, a two-tile strip, a K that does not divide into equal runs (513 k-blocks) under a
+# ragged last row tile, and a square of four tiles.
+@pytest.mark.parametrize("shape", [(256, 256, 32768), (256, 512, 32768), (768, 256, 32832), (512, 512, 32768)])
 def test_exact_on_the_reference_gate_twice_with_one_workspace(device, shape):
     m, n, k = shape
     a = _device_words(oracle.gemm_stage("a", m, k), device, torch.bfloat16)
@@ -60,8 +60,8 @@ def test_exact_on_the_reference_gate_twice_with_one_workspace(device, shape):
 
 
 def test_a_larger_workspace_serves_smaller_shapes_and_group_widths(device):
-    workspace = gemm.workspace(1024, 1024, 16384, device)
-    for (m, n, k), group in [((512, 768, 16384), 1), ((1024, 512, 16384), 3), ((256, 256, 16384), 8),
+    workspace = gemm.workspace(512, 512, 32768, device)
+    for (m, n, k), group in [((256, 512, 32768), 1), ((512, 256, 32768), 3), ((256, 256, 32768), 8),
                              ((1024, 1024, 512), 8)]:  # the last does not split and leaves the workspace alone
         a = _device_words(oracle.gemm_stage("a", m, k), device, torch.bfloat16)
         b = _device_words(oracle.gemm_stage("b", n, k), device, torch.bfloat16)
@@ -73,7 +73,7 @@ def test_a_larger_workspace_serves_smaller_shapes_and_group_widths(device):
 @pytest.mark.parametrize("operands", ["bf16", "f16"])
 def test_fused_epilogue_after_the_last_run(device, operands):
     """bias + ReLU + C += on the summed fp32 value, one rounding: the same cells as the one-launch path."""
-    m, n, k = 512, 512, 16384
+    m, n, k = 512, 256, 32768
     stage = oracle.gemm_stage if operands == "bf16" else oracle.gemm_stage_f16
     dtype = torch.bfloat16 if operands == "bf16" else torch.float16
     a, b = _device_words(stage("a", m, k), device, dtype), _device_words(stage("b", n, k), device, dtype)
@@ -90,7 +90,7 @@ def test_fused_epilogue_after_the_last_run(device, operands):
 
 
 def test_seeded_random_within_tolerance_and_close_to_one_launch(device):
-    m, n, k = 1024, 768, 16384
+    m, n, k = 512, 512, 32768
     generator = torch.Generator(device="cpu").manual_seed(5)
     a = (torch.rand((m, k), generator=generator) * 2 - 1).to(torch.bfloat16).to(device)
     b = (torch.rand((n, k), generator=generator) * 2 - 1).to(torch.bfloat16).to(device)
@@ -105,7 +105,7 @@ def test_seeded_random_within_tolerance_and_close_to_one_launch(device):
 
 
 def test_a_short_workspace_is_refused_and_none_falls_back(device):
-    m, n, k = 1024, 1024, 16384
+    m, n, k = 256, 512, 32768
     a = torch.zeros((m, k), dtype=torch.bfloat16, device=device)
     b = torch.zeros((n, k), dtype=torch.bfloat16, device=device)
     with pytest.raises(FerroKittensError, match="splits K over a workspace") as error:

@@ -155,10 +155,15 @@ def test_bias_guards(device):
 # ---- half a wave, examples/src/gemm_sol.rs:1063, 1335-1337), asked for by name and chosen by default
 
 @pytest.mark.parametrize("shape", [(256, 256, 64), (512, 256, 256), (1024, 768, 512), (768, 1280, 1088),
-                                   (2048, 2048, 256), (4096, 4096, 256)])
+                                   (2048, 2048, 256), (4096, 4096, 256),
+                                   (1024, 1024, 4096), (512, 768, 2048), (256, 256, 4096), (768, 512, 1088),
+                                   (256, 512, 8192)])
 def test_narrow_tile_is_exact_on_the_reference_gate(device, shape):
     """One k-block, a ring that wraps (17 k-blocks on 3 stages), more tiles than two CTAs per SM hold
-    at once (1024 on 148 SMs): `==` on bf16 words against the reference's integer check."""
+    at once (1024 on 148 SMs); then the shapes whose few tiles are cut along K across a cluster
+    (two CTAs for 1024 x 1024 x 4096, four for the 24-tile and the 4-tile launch, two ragged runs of
+    9 and 8 k-blocks for K = 1088, four runs of 32 for K = 8192): `==` on bf16 words against the
+    reference's integer check."""
     m, n, k = shape
     a = _device_words(oracle.gemm_stage("a", m, k), device, torch.bfloat16)
     b = _device_words(oracle.gemm_stage("b", n, k), device, torch.bfloat16)
