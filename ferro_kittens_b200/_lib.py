@@ -117,6 +117,7 @@ SIGNATURES = {
     "fk_selftest_call_guard": (c_int, [c_int, c_uint32, POINTER(c_uint64), POINTER(c_uint64)]),
     "fk_status_check": (c_int, [c_void_p, c_void_p]),
     "fk_selftest_stall": (c_int, [c_void_p, c_void_p, c_uint32]),
+    "fk_selftest_exp2": (c_int, [c_void_p, c_void_p, c_uint32, c_void_p]),
 }
 
 _library = None

@@ -489,6 +489,24 @@ __global__ void stall_probe_kernel(uint32_t* status, long long budget_cycles) {
     if (threadIdx.x == 0) fk::mbar_inval(bar);
 }
 
+// The FMA-pipe 2^x the attention kernels use for a share of their exponentials, alone: y[i] = 2^x[i]
+// for pairs of inputs, so that a test can hold it to the bound the reference states for its own
+// `exp2_approx` (src/reg.rs:81-93, test :2047-2062).
+__global__ void exp2_probe_kernel(const float2* x, float2* y, uint32_t pairs) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < pairs) y[i] = fk::exp2_pair_fma(x[i]);
+}
+
+extern "C" int fk_selftest_exp2(const float* x, float* y, uint32_t count, void* stream) {
+    if (!x || !y || count % 2) return fk_fail(FK_ERR_INVALID, "null pointer or an odd number of values");
+    const uint32_t pairs = count / 2;
+    if (pairs == 0) return FK_OK;
+    exp2_probe_kernel<<<(pairs + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const float2*>(x), reinterpret_cast<float2*>(y), pairs);
+    FK_CUDA(cudaGetLastError());
+    return FK_OK;
+}
+
 extern "C" int fk_selftest_stall(void* stream, uint32_t* device_status, uint32_t budget_cycles) {
     if (!device_status) return fk_fail(FK_ERR_INVALID, "the status pointer is null");
     stall_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(device_status, budget_cycles);

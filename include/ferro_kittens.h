@@ -344,6 +344,13 @@ int fk_status_check(const uint32_t* device_status, void* stream);
  * FK_ERR_DEVICE_STALL; the context stays usable. */
 int fk_selftest_stall(void* stream, uint32_t* device_status, uint32_t budget_cycles);
 
+/* `exp2_approx` (src/reg.rs:81-93) as the attention kernels compute it for a share of their
+ * exponentials (the same split and polynomial, on packed fp32 pairs with fused multiply-adds):
+ * y[i] = 2^x[i] for `count` (even) device floats, so that a test can hold the device arithmetic to
+ * the bound the reference's own test states (relative error under 1e-4 over [-125, 125],
+ * src/reg.rs:2047-2062). */
+int fk_selftest_exp2(const float* x, float* y, uint32_t count, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

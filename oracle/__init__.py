@@ -34,6 +34,8 @@ _lib.fko_gemm_stage.argtypes = [c_int, c_size_t, c_size_t, _u16p]
 _lib.fko_gemm_stage.restype = None
 _lib.fko_to_f16.argtypes = [c_float]
 _lib.fko_to_f16.restype = c_uint16
+_lib.fko_exp2_approx.argtypes = [c_float]
+_lib.fko_exp2_approx.restype = c_float
 _lib.fko_bf16_add.argtypes = [c_uint16, c_uint16]
 _lib.fko_bf16_add.restype = c_uint16
 _lib.fko_gemm_stage_f16.argtypes = [c_int, c_size_t, c_size_t, _u16p]
@@ -139,6 +141,11 @@ def gemm_stage_f16(which: str, rows: int, k: int) -> np.ndarray:
 
 def to_f16(value: float) -> int:
     return _lib.fko_to_f16(value)
+
+
+def exp2_approx(value: float) -> float:
+    """The reference's polynomial 2^x (src/reg.rs:81-93), in its own operation order."""
+    return float(_lib.fko_exp2_approx(value))
 
 
 def bf16_add(held: int, added: int) -> int:

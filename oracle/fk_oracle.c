@@ -112,6 +112,38 @@ uint16_t fko_bf16_add(uint16_t held, uint16_t added) {
 
 /* ---------------------------------------------------------------- GEMM operands */
 
+/* `exp2_approx` (src/reg.rs:81-93): clamp to +-125, split x = n + f with f in [-0.5, 0.5] by the
+ * 1.5 * 2^23 shift, a degree-3 polynomial for 2^f (C0..C3 as the reference spells them), n added into
+ * the exponent field. Plain fp32 multiplies and adds in the reference's order, no fused operations:
+ * compile with -ffp-contract=off semantics in mind (the expression below is written so that a
+ * contraction cannot change it: every product is stored to a float first). The reference's own
+ * test holds it to a relative error under 1e-4 over [-125, 125] (src/reg.rs:2047-2062). */
+float fko_exp2_approx(float x) {
+    const float shift = 12582912.0f; /* 1.5 * 2^23 */
+    const float c0 = 0.99992807f, c1 = 0.69326099f, c2 = 0.24261112f, c3 = 0.05517167f;
+    x = fminf(fmaxf(x, -125.0f), 125.0f);
+    volatile float shifted = x + shift;
+    uint32_t shifted_bits;
+    float shifted_value = shifted;
+    memcpy(&shifted_bits, &shifted_value, sizeof shifted_bits);
+    const int32_t integer = (int32_t)shifted_bits - 0x4b400000;
+    volatile float whole = shifted_value - shift;
+    volatile float fraction = x - whole;
+    volatile float t3 = fraction * c3;
+    volatile float s2 = c2 + t3;
+    volatile float t2 = fraction * s2;
+    volatile float s1 = c1 + t2;
+    volatile float t1 = fraction * s1;
+    volatile float poly = c0 + t1;
+    float poly_value = poly;
+    uint32_t poly_bits;
+    memcpy(&poly_bits, &poly_value, sizeof poly_bits);
+    poly_bits = (uint32_t)((int32_t)poly_bits + (int32_t)((uint32_t)integer << 23));
+    float out;
+    memcpy(&out, &poly_bits, sizeof out);
+    return out;
+}
+
 /* examples/src/gemm.rs:434-436 */
 float fko_gemm_a_value(size_t row, size_t depth) { return (float)((row * 5 + depth * 3) % 7) - 3.0f; }
 

@@ -163,3 +163,25 @@ def test_full_size_sampled_rows(device, config):
         assert np.abs(lse[b, h, rows].cpu().numpy() - expected_lse[0]).max() <= 2e-2
     bound = v.float().abs().amax(dim=2, keepdim=True)
     assert (out.float().abs() <= bound * (1 + 2 ** -7)).all()
+
+
+def test_device_exp2_polynomial_against_the_references(device):
+    """The FMA-pipe 2^x the kernels use for a share of the exponentials is the reference's `exp2_approx`
+    (src/reg.rs:81-93) with fused multiply-adds: within two fp32 places of the restatement of the
+    reference's own operation order, and inside the bound the reference's test states for it."""
+    from ferro_kittens_b200._lib import check, library
+
+    x = torch.arange(-125.0, 125.0, 0.137, dtype=torch.float32)
+    x = torch.cat([x, torch.tensor([-1.0e30, -126.5, -125.0, 0.0, 0.5, -0.5, 3.5, 124.999], dtype=torch.float32)])
+    if x.numel() % 2:
+        x = torch.cat([x, torch.zeros(1)])
+    x_device, y_device = x.to(device), torch.empty(x.numel(), dtype=torch.float32, device=device)
+    check(library().fk_selftest_exp2(x_device.data_ptr(), y_device.data_ptr(), x.numel(),
+                                     torch.cuda.current_stream().cuda_stream))
+    got = y_device.cpu().double().numpy()
+    restated = np.array([oracle.exp2_approx(float(v)) for v in x.numpy()], dtype=np.float64)
+    assert np.abs(got / restated - 1.0).max() <= 2.5e-7
+    inside = x.numpy() >= -125.0
+    exact = np.exp2(x.double().numpy()[inside])
+    assert np.abs(got[inside] / exact - 1.0).max() < 1.0e-4
+    assert (got[~inside] <= 2.0 ** -124).all()

@@ -199,3 +199,19 @@ def test_attention_backward_oracle_matches_float64_autograd():
         (torch.softmax(scores, dim=-1) @ vd).backward(g.double())
         for mine, theirs in ((dq, qd), (dk, kd), (dv, vd)):
             assert np.abs(mine - theirs.grad.numpy()).max() < 1e-12
+
+
+def test_exp2_polynomial_stays_inside_the_references_bound():
+    """The reference's own test of `exp2_approx` (src/reg.rs:2047-2062) and its doc example (:75-79),
+    on the restatement: relative error under 1e-4 from -125 to 125 in steps of 0.137, and the clamp
+    that the masked-score sentinel depends on."""
+    x = np.float32(-125.0)
+    worst = 0.0
+    while x <= 125.0:
+        approx, exact = oracle.exp2_approx(float(x)), 2.0 ** float(x)
+        worst = max(worst, abs((approx - exact) / exact))
+        x = np.float32(x + np.float32(0.137))
+    assert worst < 1.0e-4
+    assert worst > 5.0e-5  # the stated maximum is 7.5e-5: a polynomial far better than that is not the reference's
+    assert oracle.exp2_approx(-1.0e30) <= 2.0 ** -124
+    assert abs(oracle.exp2_approx(3.5) / 2.0 ** 3.5 - 1.0) < 1.0e-4
