@@ -331,12 +331,13 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         c = torch.empty((m, n_local), dtype=torch.bfloat16, device=device)
         c_ref = torch.empty_like(c)
         status = gemm.new_status(device)
-        a_map, b_map, c_map = gemm.maps(a, b, c)
+        # maps built once, as the reference's `run` does, to the item width this shard's waves want
+        maps = gemm.TiledMaps(a, b, c)
         if cublaslt.fkb_prepare(m, n_local, k) != 0:
             raise RuntimeError(cublaslt.fkb_last_error().decode())
 
         def step():
-            gemm.launch(a_map, b_map, c_map, m, n_local, k, args.group, status)
+            gemm.launch_tiled(maps, m, n_local, k, args.group, status)
 
         def library_step():
             if cublaslt.fkb_gemm(a.data_ptr(), b.data_ptr(), c_ref.data_ptr(), stream) != 0:
@@ -377,7 +378,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         achieved = flops_rank / (ours["seconds"] / args.steps) / 1e12
         result = {
             "config": {"m": m, "n": n, "k": k, "seed": config["seed"], "entries": config["entries"],
-                       "columns_per_rank": n_local},
+                       "columns_per_rank": n_local, "item_columns": maps.columns},
             "ours": ours_out, "cublaslt_alone": theirs_out,
             "interleaved": {"pairs": max(10, args.steps), "ours": side["ours"], "cublaslt": side["cublaslt"],
                             "ratio_ours_over_cublaslt_at_median": side["cublaslt"]["median_ms"] / side["ours"]["median_ms"],
@@ -651,8 +652,9 @@ def run_only(args, local_rank: int) -> None:
         a = (torch.randn((m, k), generator=generator, device=device) / math.sqrt(k)).to(torch.bfloat16)
         b = (torch.randn((n, k), generator=generator, device=device) / math.sqrt(k)).to(torch.bfloat16)
         c = torch.empty((m, n), dtype=torch.bfloat16, device=device)
-        a_map, b_map, c_map = gemm.maps(a, b, c)
-        fn = lambda: gemm.launch(a_map, b_map, c_map, m, n, k, args.group, status)  # noqa: E731
+        maps = gemm.TiledMaps(a, b, c, columns=args.item_columns or None)
+        flags = gemm.TILE_WIDE if args.item_columns else 0
+        fn = lambda: gemm.launch_tiled(maps, m, n, k, args.group, status, flags=flags)  # noqa: E731
         flops = 2.0 * m * n * k
         name = f"gemm_bf16_{m}x{n}x{k}"
     elif args.only in ("softmax", "layernorm", "groupnorm"):
@@ -701,6 +703,8 @@ def run_only(args, local_rank: int) -> None:
     gemm.check_status(status)
     line = {"only": name, "steps": args.steps, "ms_per_step": seconds / args.steps * 1e3,
             "tflops": flops * args.steps / seconds / 1e12}
+    if args.only == "gemm":
+        line["item_columns"] = maps.columns
     if args.only == "gemm" and args.beside_library:
         # The library's kernel for the same product, launched the same number of times, so that a
         # launch list of this command holds both.
@@ -717,6 +721,8 @@ def main() -> None:
     parser.add_argument("--rows", type=int, default=1 << 20, help="rows of 128 columns for the row kernels")
     parser.add_argument("--beside-library", action="store_true",
                         help="with --only gemm: also launch torch.matmul (cuBLAS) on the same operands")
+    parser.add_argument("--item-columns", type=int, default=0, choices=[0, 256, 224, 192],
+                        help="with --only gemm: force the wide kernel with items this many columns wide (0: the launch chooses)")
     parser.add_argument("--m", type=int, default=8192)
     parser.add_argument("--n", type=int, default=8192)
     parser.add_argument("--k", type=int, default=8192)

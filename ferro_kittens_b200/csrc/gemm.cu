@@ -12,7 +12,9 @@
 //               and one [128, 64] tile of B: 48 KiB for 1024 tensor cycles, against 32 KiB for
 //               512 with a single [256, 256] tile -- what keeps the operand feed under the
 //               L2->SM rate without multicast. The last partial wave of a launch is re-cut
-//               into single-half items when that shortens it.
+//               into single-half items when that shortens it, and a launch whose tile count sits
+//               just past a whole number of waves takes narrower items ([512, 224] or [512, 192],
+//               the MMA's N) when those fill the waves better.
 //   warp 0      producer: this CTA's A and B tiles per k-block, by TMA, into a kStages-deep
 //               SWIZZLE_128B ring; every load of the pair completes on the leader's `full`.
 //   warp 1      (leader CTA only) MMA issue: 4 chained MMAs per half per k-block;
@@ -49,6 +51,8 @@ constexpr uint32_t kTmemColumns = kHalves * kBlockN;  // 512
 constexpr uint32_t kEpilogueWarps = 4 * kHalves;
 constexpr uint32_t kStageColumns = 64;  // columns per epilogue pass: one swizzle atom of bf16
 constexpr uint32_t kPasses = kBlockN / kStageColumns;
+// What an item's fourth epilogue pass is: 64 columns (items 256 wide), 32 (224) or nothing (192).
+enum LastPass : uint32_t { kLastNone = 0, kLastNarrow = 1, kLastWhole = 2 };
 constexpr uint32_t kThreads = (2 + kEpilogueWarps) * 32;
 constexpr uint32_t kATileBytes = kBlockM * kBlockK * 2;
 constexpr uint32_t kBTileBytes = kHalfN * kBlockK * 2;
@@ -94,7 +98,8 @@ enum StallCode : uint32_t {
 struct Schedule {
     uint32_t m;          // rows of C
     uint32_t tiles_m;    // [512, 256] tile rows: ceil(m / 512)
-    uint32_t tiles_n;    // tile columns: n / 256
+    uint32_t tiles_n;    // tile columns: n / tile_n
+    uint32_t tile_n;     // columns of C per item (the MMAs' N): 256, or 224 / 192 where that fills the waves better
     uint32_t group;      // traversal width of `grouped`
     uint32_t k_blocks;   // k / 64
     uint32_t whole;      // leading items that are whole two-half tiles
@@ -128,7 +133,7 @@ __host__ __device__ __forceinline__ Item item_at(const Schedule& plan, uint32_t 
     const TileCoord at = grouped(tile, plan.tiles_m, plan.tiles_n, plan.group);
     Item item;
     item.row = kHalves * 2 * kBlockM * at.row + 2 * kBlockM * first_half;
-    item.column = kBlockN * at.column;
+    item.column = plan.tile_n * at.column;
     item.halves = item.row >= plan.m ? 0u
                   : (halves == 2 && item.row + 2 * kBlockM >= plan.m) ? 1u
                                                                        : halves;
@@ -138,13 +143,16 @@ __host__ __device__ __forceinline__ Item item_at(const Schedule& plan, uint32_t 
 // The fused epilogue on one pass of a band (a column-vector bias and a unary map on the register
 // tile, src/global.rs:410-416, src/reg.rs:261), then the ONE rounding to bf16: `lo` and `hi` hold
 // this lane's row, columns [column, column + 32) and [column + 32, column + 64) as fp32 bits;
-// every lane holds the same columns, so the bias words are broadcast loads.
+// every lane holds the same columns, so the bias words are broadcast loads. `parts` == 1 is the
+// 32-column pass that ends an item whose width is not a multiple of 64: only `lo` is real then
+// (the bias is not read past it) and only the first 16 words of `packed` mean anything.
 __device__ __forceinline__ void finish_pass(uint32_t (&lo)[32], uint32_t (&hi)[32], const Schedule& plan,
-                                            uint32_t column, uint32_t (&packed)[32]) {
+                                            uint32_t column, uint32_t (&packed)[32], uint32_t parts = 2) {
     if (plan.bias || plan.relu) {
         const float floor = plan.relu ? 0.0f : -INFINITY;
 #pragma unroll
         for (uint32_t part = 0; part < 2; ++part) {
+            if (part >= parts) break;
             uint32_t* const values = part ? hi : lo;
             uint32_t words[16];
             if (plan.bias) {
@@ -210,8 +218,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap a_map,
                           const __grid_constant__ CUtensorMap b_map,
                           const __grid_constant__ CUtensorMap c_map,
-                          const __grid_constant__ CUtensorMap partial_map, const Schedule plan,
+                          const __grid_constant__ CUtensorMap extra_map, const Schedule plan,
                           uint32_t* status) {
+    // `extra_map`: the fp32 workspace's map in the K-split instantiation; in the one-launch one,
+    // C's store map with a [32, 32] box for the last pass of items 224 or 160 columns wide.
     extern __shared__ __align__(1024) uint8_t dynamic_shared[];
     const uint32_t raw = smem_u32(dynamic_shared);
     const uint32_t base = raw;
@@ -271,9 +281,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 const Item& item = unit.item;
                 if (item.halves == 0) continue;
                 const int a_row = static_cast<int>(item.row + kBlockM * rank);
-                const int b_row = static_cast<int>(item.column + kHalfN * rank);
+                // Each CTA stages its half of the item's columns: tile_n / 2 rows of B (the B map's box).
+                const int b_row = static_cast<int>(item.column + (plan.tile_n / 2) * rank);
                 // Both CTAs' boxes land on the leader's barrier.
-                const uint32_t pair_bytes = 2 * (item.halves * kATileBytes + kBTileBytes);
+                const uint32_t pair_bytes = 2 * (item.halves * kATileBytes + (plan.tile_n / 2) * kBlockK * 2);
                 for (uint32_t k = unit.k0; k < unit.k1; ++k, ++fill) {
                     const uint32_t s = fill % kStages;
                     const uint32_t parity = (fill / kStages) & 1u;
@@ -394,7 +405,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                         fence_proxy_async_shared();
                         __syncwarp();
                         if (lane == 0) {
-                            tma_reduce_add_2d(&partial_map, band, static_cast<int>(item.column + 32 * pass), c_row);
+                            tma_reduce_add_2d(&extra_map, band, static_cast<int>(item.column + 32 * pass), c_row);
                             tma_store_commit();
                         }
                     }
@@ -454,17 +465,25 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 if (lane == 0) *counter = 0;
                 continue;
             }
-            // Read this warp's [32, 256] band out as bf16 pairs, then release the accumulator:
-            // the stores below overlap the next item's main loop.
+            // Read this warp's band of the item out as bf16 pairs, then release the accumulator: the
+            // stores below overlap the next item's main loop. An item is 256, 224 or 192 columns wide:
+            // three passes of 64 columns, then a fourth of 64, of 32 (`kLastNarrow`) or none.
+            const uint32_t last_pass = plan.tile_n == kBlockN ? kLastWhole : plan.tile_n == kBlockN - 32 ? kLastNarrow : kLastNone;
             uint32_t held[kPasses][32];
             if (mine) {
 #pragma unroll
                 for (uint32_t pass = 0; pass < kPasses; ++pass) {
                     uint32_t lo[32], hi[32];
-                    tmem_ld_32x32(t_row + pass * kStageColumns, lo);
-                    tmem_ld_32x32(t_row + pass * kStageColumns + 32, hi);
-                    tmem_wait_ld();
-                    finish_pass(lo, hi, plan, item.column + pass * kStageColumns, held[pass]);
+                    if (pass + 1 < kPasses || last_pass == kLastWhole) {
+                        tmem_ld_32x32(t_row + pass * kStageColumns, lo);
+                        tmem_ld_32x32(t_row + pass * kStageColumns + 32, hi);
+                        tmem_wait_ld();
+                        finish_pass(lo, hi, plan, item.column + pass * kStageColumns, held[pass]);
+                    } else if (last_pass == kLastNarrow) {
+                        tmem_ld_32x32(t_row + pass * kStageColumns, lo);
+                        tmem_wait_ld();
+                        finish_pass(lo, lo, plan, item.column + pass * kStageColumns, held[pass], 1);
+                    }
                 }
             }
             tc_fence_before_sync();
@@ -474,6 +493,29 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 
             const int c_row =
                 static_cast<int>(item.row + 2 * kBlockM * half + kBlockM * rank + 32 * quadrant);
+            // A 64-column pass of this lane's row into a [32, 64] SWIZZLE_128B staging tile.
+            const auto stage = [&](uint32_t tile, const uint32_t (&words)[32]) {
+#pragma unroll
+                for (uint32_t chunk = 0; chunk < 8; ++chunk)
+                    st_shared_v4(tile + swizzled_chunk_offset(lane, chunk, 0), words[4 * chunk], words[4 * chunk + 1],
+                                 words[4 * chunk + 2], words[4 * chunk + 3]);
+            };
+            // The 32-column pass: dense rows of 64 bytes (the narrow store map is not swizzled).
+            const auto stage_narrow = [&](uint32_t tile, const uint32_t (&words)[32]) {
+#pragma unroll
+                for (uint32_t chunk = 0; chunk < 4; ++chunk)
+                    st_shared_v4(tile + 64 * lane + 16 * chunk, words[4 * chunk], words[4 * chunk + 1],
+                                 words[4 * chunk + 2], words[4 * chunk + 3]);
+            };
+            // One thread: a staged pass to C (the 32-column pass through the narrow store map, which
+            // this instantiation receives in place of the workspace's).
+            const auto store = [&](const CUtensorMap* map, uint32_t tile, uint32_t pass) {
+                const int column = static_cast<int>(item.column + pass * kStageColumns);
+                if (plan.accumulate)
+                    tma_reduce_add_2d(map, tile, column, c_row);
+                else
+                    tma_store_2d(map, tile, column, c_row);
+            };
             if (index + cluster_count_x() >= plan.items) {
                 // This CTA's last item: no load is outstanding or to come and every MMA that read
                 // the operand ring has retired (acc_full), so the ring is free shared memory. Each
@@ -481,48 +523,38 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 // stores go out back to back instead of waiting for one staging tile in turn.
                 const uint32_t spare = a_ring + (warp - 2) * kPasses * kBandBytes;
 #pragma unroll
-                for (uint32_t pass = 0; pass < kPasses; ++pass)
-#pragma unroll
-                    for (uint32_t chunk = 0; chunk < 8; ++chunk)
-                        st_shared_v4(spare + pass * kBandBytes + swizzled_chunk_offset(lane, chunk, 0),
-                                     held[pass][4 * chunk], held[pass][4 * chunk + 1],
-                                     held[pass][4 * chunk + 2], held[pass][4 * chunk + 3]);
+                for (uint32_t pass = 0; pass + 1 < kPasses; ++pass) stage(spare + pass * kBandBytes, held[pass]);
+                if (last_pass == kLastWhole) stage(spare + (kPasses - 1) * kBandBytes, held[kPasses - 1]);
+                if (last_pass == kLastNarrow) stage_narrow(spare + (kPasses - 1) * kBandBytes, held[kPasses - 1]);
                 fence_proxy_async_shared();
                 __syncwarp();
                 if (lane == 0) {
 #pragma unroll
-                    for (uint32_t pass = 0; pass < kPasses; ++pass) {
-                        if (plan.accumulate)
-                            tma_reduce_add_2d(&c_map, spare + pass * kBandBytes,
-                                              static_cast<int>(item.column + pass * kStageColumns), c_row);
-                        else
-                            tma_store_2d(&c_map, spare + pass * kBandBytes,
-                                         static_cast<int>(item.column + pass * kStageColumns), c_row);
-                    }
+                    for (uint32_t pass = 0; pass + 1 < kPasses; ++pass) store(&c_map, spare + pass * kBandBytes, pass);
+                    if (last_pass == kLastWhole) store(&c_map, spare + (kPasses - 1) * kBandBytes, kPasses - 1);
+                    if (last_pass == kLastNarrow) store(&extra_map, spare + (kPasses - 1) * kBandBytes, kPasses - 1);
                     tma_store_commit();
                 }
                 continue;
             }
 #pragma unroll
             for (uint32_t pass = 0; pass < kPasses; ++pass) {
+                if (pass + 1 == kPasses && last_pass == kLastNone) break;
                 // The store that last read this warp's staging tile must be done reading it.
                 if (lane == 0) tma_store_wait_read<0>();
                 __syncwarp();
-#pragma unroll
-                for (uint32_t chunk = 0; chunk < 8; ++chunk)
-                    st_shared_v4(band + swizzled_chunk_offset(lane, chunk, 0), held[pass][4 * chunk],
-                                 held[pass][4 * chunk + 1], held[pass][4 * chunk + 2],
-                                 held[pass][4 * chunk + 3]);
+                if (pass + 1 == kPasses && last_pass == kLastNarrow)
+                    stage_narrow(band, held[pass]);
+                else
+                    stage(band, held[pass]);
                 // Every writer publishes to the async proxy, then one lane stores.
                 fence_proxy_async_shared();
                 __syncwarp();
                 if (lane == 0) {
-                    if (plan.accumulate)
-                        tma_reduce_add_2d(&c_map, band,
-                                          static_cast<int>(item.column + pass * kStageColumns), c_row);
+                    if (pass + 1 == kPasses && last_pass == kLastNarrow)
+                        store(&extra_map, band, pass);
                     else
-                        tma_store_2d(&c_map, band,
-                                     static_cast<int>(item.column + pass * kStageColumns), c_row);
+                        store(&c_map, band, pass);
                     tma_store_commit();
                 }
             }
@@ -796,10 +828,11 @@ __global__ void __launch_bounds__(kThreads, kStages == kStagesShared ? 2 : 1)
 // tiles, with the last partial wave re-cut into single halves when it holds at
 // most half a wave of tiles (two short half-waves then beat one long one).
 static Schedule schedule(uint32_t m, uint32_t n, uint32_t k, uint32_t group, uint32_t clusters,
-                         uint32_t flags = 0) {
+                         uint32_t flags = 0, uint32_t tile_n = kBlockN) {
     Schedule plan;
-    plan.idesc = instruction_descriptor(2 * kBlockM, kBlockN, false, false,
+    plan.idesc = instruction_descriptor(2 * kBlockM, tile_n, false, false,
                                         (flags & FK_GEMM_F16_OPERANDS) ? 0u : 1u);
+    plan.tile_n = tile_n;
     plan.accumulate = (flags & FK_GEMM_ACCUMULATE) ? 1u : 0u;
     plan.relu = (flags & FK_GEMM_RELU) ? 1u : 0u;
     plan.bias = nullptr;
@@ -810,7 +843,7 @@ static Schedule schedule(uint32_t m, uint32_t n, uint32_t k, uint32_t group, uin
     plan.arrivals = nullptr;
     plan.m = m;
     plan.tiles_m = (m + kHalves * 2 * kBlockM - 1) / (kHalves * 2 * kBlockM);
-    plan.tiles_n = n / kBlockN;
+    plan.tiles_n = n / tile_n;
     // A width at or past the tile rows is already the column-major walk; clamping keeps
     // `group * columns` inside 32 bits whatever the caller passes.
     plan.group = group < plan.tiles_m ? group : plan.tiles_m;
@@ -821,6 +854,35 @@ static Schedule schedule(uint32_t m, uint32_t n, uint32_t k, uint32_t group, uin
     plan.whole = recut ? tiles - tail : tiles;
     plan.items = plan.whole + kHalves * (tiles - plan.whole);
     return plan;
+}
+
+// Time of a launch in units of one cluster walking K over 32 columns of a two-half item: whole
+// waves, and a last one that costs half when `schedule` re-cuts it.
+static uint32_t wave_cost(const Schedule& plan, uint32_t clusters) {
+    const uint32_t tiles = plan.tiles_m * plan.tiles_n;
+    const uint32_t tail = tiles % clusters;
+    const uint32_t half_waves = 2 * (tiles / clusters) + (tail == 0 ? 0u : plan.whole != tiles ? 1u : 2u);
+    return half_waves * (plan.tile_n / 32);
+}
+
+// Columns per item for a launch of the wide kernel whose maps this library builds. A tile count just
+// past a whole number of waves wastes most of its last wave: 8192 x 3584 (an eighth of the 28672-column
+// up-projection) is 224 items of [512, 256] = 3 waves of 74 and 2 items, 3.5 wave-times even re-cut,
+// but 256 items of [512, 224] = 3 waves and 34, which re-cut into 68 halves fill half a wave:
+// 3.5 x 224 / 256 = 3.06. Measured on B200 (back-to-back launches at the power limit, 256 / 224 wide):
+// 8192 x 3584 x 8192: 364 / 343 us; 2048 x 5376 x 4096: 107 / 95; but 8192 x 7168 x 8192 (6.5 wave-times
+// against 6.125): 704 / 720, and 8192 x 28672 x 8192 (24.5 both): 2822 / 2873 -- the narrower item costs
+// about 2 % per flop (A re-read more often, more items to drain), and at the power limit a thin last
+// wave is partly repaid in clock by the SMs that idle through it. So narrower items must promise 10 %.
+static uint32_t choose_tile_n(uint32_t m, uint32_t n, uint32_t k, uint32_t clusters) {
+    uint32_t best = kBlockN;
+    uint32_t best_cost = wave_cost(schedule(m, n, k, 1, clusters, 0, kBlockN), clusters);
+    for (uint32_t tile_n = kBlockN - 32; tile_n >= kBlockN - 64; tile_n -= 32) {
+        if (n % tile_n) continue;
+        const uint32_t cost = wave_cost(schedule(m, n, k, 1, clusters, 0, tile_n), clusters);
+        if (100ull * cost < 90ull * best_cost) best = tile_n, best_cost = cost;
+    }
+    return best;
 }
 
 }  // namespace gemm
@@ -853,9 +915,17 @@ static bool narrow_by_default(uint32_t m, uint32_t n, uint32_t k, uint32_t sm_co
     return tiles <= 2ull * sm_count && k <= 2048;
 }
 
-extern "C" int fk_gemm_launch_fused(const void* a_map, const void* b_map, const void* c_map,
-                                    const void* bias, uint32_t m, uint32_t n, uint32_t k, uint32_t group,
-                                    uint32_t flags, void* stream, uint32_t* device_status) {
+static bool takes_narrow(uint32_t m, uint32_t n, uint32_t k, uint32_t flags, uint32_t sm_count) {
+    return (flags & FK_GEMM_TILE_NARROW) || (!(flags & FK_GEMM_TILE_WIDE) && narrow_by_default(m, n, k, sm_count));
+}
+
+// The launch behind every GEMM entry. `tile_n` is the width of the wide kernel's items: 256 with the
+// caller's maps (B's box is then 128 rows); the entries that build the maps themselves may pass 224
+// or 192 with a B box of tile_n / 2 rows and, when tile_n is an odd multiple of 32, `c_narrow_map`,
+// C's store map with a [32, 32] box (otherwise unused: any valid map).
+static int launch_fused(const void* a_map, const void* b_map, const void* c_map, const void* c_narrow_map,
+                        uint32_t tile_n, const void* bias, uint32_t m, uint32_t n, uint32_t k, uint32_t group,
+                        uint32_t flags, void* stream, uint32_t* device_status) {
     if (flags & ~(FK_GEMM_F16_OPERANDS | FK_GEMM_ACCUMULATE | FK_GEMM_RELU | FK_GEMM_TILE_NARROW | FK_GEMM_TILE_WIDE))
         return fk_fail(FK_ERR_INVALID, "unknown GEMM flags 0x%x", flags);
     if ((flags & FK_GEMM_TILE_NARROW) && (flags & FK_GEMM_TILE_WIDE))
@@ -880,9 +950,10 @@ extern "C" int fk_gemm_launch_fused(const void* a_map, const void* b_map, const 
     if (admitted != FK_OK) return admitted;
 
     const uint32_t clusters = static_cast<uint32_t>(sm_count) / 2;
-    gemm::Schedule plan = gemm::schedule(m, n, k, group, clusters, flags);
+    const bool narrow = takes_narrow(m, n, k, flags, static_cast<uint32_t>(sm_count));
+    gemm::Schedule plan = gemm::schedule(m, n, k, group, clusters, flags, narrow ? gemm::kBlockN : tile_n);
     plan.bias = static_cast<const uint16_t*>(bias);
-    if ((flags & FK_GEMM_TILE_NARROW) || (!(flags & FK_GEMM_TILE_WIDE) && narrow_by_default(m, n, k, static_cast<uint32_t>(sm_count)))) {
+    if (narrow) {
         // One CTA per [128, 128] tile; the A and B maps' boxes are [64, 128] already, C's [64, 32].
         plan.idesc = instruction_descriptor(gemm::narrow::kTile, gemm::narrow::kTile, false, false,
                                             (flags & FK_GEMM_F16_OPERANDS) ? 0u : 1u);
@@ -926,13 +997,44 @@ extern "C" int fk_gemm_launch_fused(const void* a_map, const void* b_map, const 
                              gemm::narrow::shared_bytes<gemm::narrow::kStagesShared>(), 1);
     }
     const uint32_t grid = 2 * (plan.items < clusters ? plan.items : clusters);
-    // The one-launch kernel never touches its fourth map; it is handed C's.
     gemm::gemm_bf16_pair_kernel<false><<<grid, gemm::kThreads, gemm::kSharedBytes,
                                          static_cast<cudaStream_t>(stream)>>>(
         *static_cast<const CUtensorMap*>(a_map), *static_cast<const CUtensorMap*>(b_map),
-        *static_cast<const CUtensorMap*>(c_map), *static_cast<const CUtensorMap*>(c_map), plan, device_status);
+        *static_cast<const CUtensorMap*>(c_map), *static_cast<const CUtensorMap*>(c_narrow_map), plan, device_status);
     FK_CUDA(cudaGetLastError());
     return FK_OK;
+}
+
+extern "C" int fk_gemm_launch_fused(const void* a_map, const void* b_map, const void* c_map,
+                                    const void* bias, uint32_t m, uint32_t n, uint32_t k, uint32_t group,
+                                    uint32_t flags, void* stream, uint32_t* device_status) {
+    return launch_fused(a_map, b_map, c_map, c_map, gemm::kBlockN, bias, m, n, k, group, flags, stream, device_status);
+}
+
+extern "C" uint32_t fk_gemm_item_columns(uint32_t m, uint32_t n, uint32_t k, uint32_t flags, uint32_t sm_count) {
+    if (m == 0 || n == 0 || k == 0 || m % (2 * gemm::kBlockM) || n % gemm::kBlockN || k % gemm::kBlockK || sm_count < 2)
+        return gemm::kBlockN;
+    if (takes_narrow(m, n, k, flags, sm_count)) return gemm::kBlockN;
+    return gemm::choose_tile_n(m, n, k, sm_count / 2);
+}
+
+extern "C" int fk_gemm_launch_tiled(const void* a_map, const void* b_map, const void* c_map, const void* c_tail_map,
+                                    uint32_t item_columns, const void* bias, uint32_t m, uint32_t n, uint32_t k,
+                                    uint32_t group, uint32_t flags, void* stream, uint32_t* device_status) {
+    if (item_columns != gemm::kBlockN && item_columns != gemm::kBlockN - 32 && item_columns != gemm::kBlockN - 64)
+        return fk_fail(FK_ERR_SHAPE, "items are 256, 224 or 192 columns wide, not %u", item_columns);
+    if (n % item_columns) return fk_fail(FK_ERR_SHAPE, "items of %u columns do not divide the %u columns of C", item_columns, n);
+    if (item_columns == gemm::kBlockN - 32 && !c_tail_map)
+        return fk_fail(FK_ERR_INVALID, "items of 224 columns store their last 32 through a map of their own, which is null");
+    if (item_columns != gemm::kBlockN) {
+        DeviceFacts facts;
+        const int known = device_facts(&facts);
+        if (known != FK_OK) return known;
+        if (takes_narrow(m, n, k, flags, static_cast<uint32_t>(facts.sm_count)))
+            return fk_fail(FK_ERR_INVALID, "this launch takes the narrow kernel, whose maps are the 256-column ones");
+    }
+    return launch_fused(a_map, b_map, c_map, c_tail_map ? c_tail_map : c_map, item_columns, bias, m, n, k, group, flags,
+                        stream, device_status);
 }
 
 extern "C" int fk_gemm_launch(const void* a_map, const void* b_map, const void* c_map, uint32_t m,
@@ -949,17 +1051,21 @@ extern "C" int fk_gemm_bf16_launch(const void* a_map, const void* b_map, const v
 
 // The three maps `gemm::run` builds (examples/src/gemm.rs:506-513), plus the
 // store map for C: dims [n, m] with the caller's leading dimension.
+// `tile_n` other than 256: B's box is tile_n / 2 rows, and maps[3] is C's store map with a [32, 32]
+// box, not swizzled (maps[3] is not written otherwise).
 static int gemm_maps(const void* a, const void* b, void* c, uint32_t m, uint32_t n, uint32_t k,
-                     uint32_t ldc, CUtensorMap* maps, uint32_t operand_element = FK_BF16) {
+                     uint32_t ldc, CUtensorMap* maps, uint32_t operand_element = FK_BF16,
+                     uint32_t tile_n = gemm::kBlockN) {
     fk_layout_t layout;
     const uint64_t a_extents[2] = {k, m}, b_extents[2] = {k, n}, c_extents[2] = {n, m};
     const uint64_t c_strides[2] = {1, ldc};
     int status = fk_layout_packed(&layout, reinterpret_cast<uint64_t>(a), operand_element, 2, a_extents);
     if (status == FK_OK) status = fk_tensor_map(&maps[0], &layout, gemm::kBlockK, gemm::kBlockM, FK_SWIZZLE_128B);
     if (status == FK_OK) status = fk_layout_packed(&layout, reinterpret_cast<uint64_t>(b), operand_element, 2, b_extents);
-    if (status == FK_OK) status = fk_tensor_map(&maps[1], &layout, gemm::kBlockK, gemm::kHalfN, FK_SWIZZLE_128B);
+    if (status == FK_OK) status = fk_tensor_map(&maps[1], &layout, gemm::kBlockK, tile_n / 2, FK_SWIZZLE_128B);
     if (status == FK_OK) status = fk_layout_strided(&layout, reinterpret_cast<uint64_t>(c), FK_BF16, 2, c_extents, c_strides);
     if (status == FK_OK) status = fk_tensor_map(&maps[2], &layout, gemm::kStageColumns, 32, FK_SWIZZLE_128B);
+    if (status == FK_OK && tile_n != gemm::kBlockN) status = fk_tensor_map(&maps[3], &layout, 32, 32, FK_SWIZZLE_NONE);
     return status;
 }
 
@@ -972,11 +1078,17 @@ extern "C" int fk_gemm_fused(const void* a, const void* b, void* c, const void* 
         return fk_fail(FK_ERR_SHAPE, "%ux%ux%u does not divide the %ux%ux%u tiling", m, n, k,
                        2 * gemm::kBlockM, gemm::kBlockN, gemm::kBlockK);
     if (ldc < n) return fk_fail(FK_ERR_SHAPE, "ldc %u is narrower than the %u columns of C", ldc, n);
-    alignas(64) CUtensorMap maps[3];
-    const int status = gemm_maps(a, b, c, m, n, k, ldc, maps, (flags & FK_GEMM_F16_OPERANDS) ? FK_F16 : FK_BF16);
+    // The maps are this call's own, so the wide kernel's items may be as wide as fills the waves best.
+    uint32_t tile_n = gemm::kBlockN;
+    DeviceFacts facts;
+    if (device_facts(&facts) == FK_OK && facts.sm_count >= 2 &&
+        !takes_narrow(m, n, k, flags, static_cast<uint32_t>(facts.sm_count)))
+        tile_n = gemm::choose_tile_n(m, n, k, static_cast<uint32_t>(facts.sm_count) / 2);
+    alignas(64) CUtensorMap maps[4];
+    const int status = gemm_maps(a, b, c, m, n, k, ldc, maps, (flags & FK_GEMM_F16_OPERANDS) ? FK_F16 : FK_BF16, tile_n);
     if (status != FK_OK) return status;
-    return fk_gemm_launch_fused(&maps[0], &maps[1], &maps[2], bias, m, n, k, group, flags, stream,
-                                device_status);
+    return launch_fused(&maps[0], &maps[1], &maps[2], tile_n != gemm::kBlockN ? &maps[3] : &maps[2], tile_n, bias, m, n,
+                        k, group, flags, stream, device_status);
 }
 
 // ---- launches under one wave: K split across the idle clusters, partial sums in a workspace

@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import torch
 
-from ._lib import check, library
+from ._lib import FK_SWIZZLE_NONE, check, library
 from .global_layout import GlobalLayout
 
 BLOCK_M = 128
@@ -65,6 +65,39 @@ def launch(a_map, b_map, c_map, m: int, n: int, k: int, group: int = GROUP, stat
     handle = (stream or torch.cuda.current_stream()).cuda_stream
     check(library().fk_gemm_bf16_launch(a_map.as_ptr(), b_map.as_ptr(), c_map.as_ptr(), m, n, k,
                                         group, handle, status.data_ptr() if status is not None else None))
+
+
+def item_columns(m: int, n: int, k: int, device, flags: int = 0) -> int:
+    """Columns of C per item the wide kernel would take for this shape on ``device``: 256, or 224 / 192
+    where a launch's tiles sit just past a whole number of waves and narrower items fill them better."""
+    sm_count = torch.cuda.get_device_properties(device).multi_processor_count
+    return library().fk_gemm_item_columns(m, n, k, flags, sm_count)
+
+
+class TiledMaps:
+    """The maps of a launch whose item width was chosen for the shape (:func:`item_columns`): B's box is
+    ``columns / 2`` rows, and items of 224 columns store their last 32 through ``c_tail``."""
+
+    def __init__(self, a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, columns: int | None = None):
+        m, k = a.shape
+        n = b.shape[0]
+        self.columns = item_columns(m, n, k, a.device) if columns is None else columns
+        self.a = GlobalLayout.packed(a.data_ptr(), [k, m]).tensor_map(BLOCK_M)
+        self.b = GlobalLayout.packed(b.data_ptr(), [k, n]).tensor_map(self.columns // 2)
+        c_layout = GlobalLayout.strided(c.data_ptr(), [n, m], [1, c.stride(0)])
+        self.c = c_layout.tensor_map(32)
+        self.c_tail = c_layout.tensor_map(32, 32, FK_SWIZZLE_NONE) if self.columns % 64 else None
+
+
+def launch_tiled(maps: TiledMaps, m: int, n: int, k: int, group: int = GROUP, status=None, stream=None,
+                 flags: int = 0, bias: torch.Tensor | None = None) -> None:
+    """:func:`launch` for maps built to the chosen item width."""
+    handle = (stream or torch.cuda.current_stream()).cuda_stream
+    check(library().fk_gemm_launch_tiled(maps.a.as_ptr(), maps.b.as_ptr(), maps.c.as_ptr(),
+                                         maps.c_tail.as_ptr() if maps.c_tail is not None else None, maps.columns,
+                                         bias.data_ptr() if bias is not None else None,
+                                         m, n, k, group, flags, handle,
+                                         status.data_ptr() if status is not None else None))
 
 
 def workspace(m: int, n: int, k: int, device, sm_count: int | None = None) -> torch.Tensor | None:

@@ -192,6 +192,20 @@ int fk_gemm_launch_fused(const void* a_map, const void* b_map, const void* c_map
                          uint32_t* device_status);
 int fk_gemm_fused(const void* a, const void* b, void* c, const void* bias, uint32_t m, uint32_t n, uint32_t k,
                   uint32_t ldc, uint32_t group, uint32_t flags, void* stream, uint32_t* device_status);
+/* Items narrower than 256 columns. The persistent kernel's time is whole waves of items, so a launch
+ * whose [512, 256] tile count sits just past a whole number of waves wastes most of its last wave:
+ * 8192 x 3584 (an eighth of the 28672-column up-projection) is 3 waves of 74 and 2 tiles. Items of
+ * 224 or 192 columns (the MMAs' N) can fill the waves better: 256 items of [512, 224] run in 3.06
+ * wave-times of the wide item instead of 3.5. The entries that take pointers choose by themselves.
+ * A caller that keeps its own maps (as the reference's `run` does, examples/src/gemm.rs:506-513) asks
+ * fk_gemm_item_columns for the width this device would choose (256, 224 or 192) and builds B's map
+ * with a box of item_columns / 2 rows, and for 224 a second store map of C with a [32, 32] box and
+ * no swizzle (`c_tail_map`: the item's last 32 columns; null otherwise); fk_gemm_launch_tiled is
+ * fk_gemm_launch_fused for such maps. */
+uint32_t fk_gemm_item_columns(uint32_t m, uint32_t n, uint32_t k, uint32_t flags, uint32_t sm_count);
+int fk_gemm_launch_tiled(const void* a_map, const void* b_map, const void* c_map, const void* c_tail_map,
+                         uint32_t item_columns, const void* bias, uint32_t m, uint32_t n, uint32_t k,
+                         uint32_t group, uint32_t flags, void* stream, uint32_t* device_status);
 int fk_gemm_launch(const void* a_map, const void* b_map, const void* c_map, uint32_t m, uint32_t n,
                    uint32_t k, uint32_t group, uint32_t flags, void* stream, uint32_t* device_status);
 int fk_gemm(const void* a, const void* b, void* c, uint32_t m, uint32_t n, uint32_t k, uint32_t ldc,

@@ -223,3 +223,93 @@ def test_small_shallow_launches_take_the_narrow_tile_by_default(device):
     with pytest.raises(FerroKittensError, match="both asked for"):
         check(library().fk_gemm(a.data_ptr(), b.data_ptr(), default.data_ptr(), m, n, k, n, 8, 8 | 16,
                                 torch.cuda.current_stream().cuda_stream, None))
+
+
+# ---- items narrower than 256 columns: the wide kernel's [512, 224] and [512, 192] items, which fill the
+# ---- waves of launches whose [512, 256] tile count sits just past a whole number of waves
+
+def _run_tiled(a, b, c, columns, flags=0, bias=None, group=gemm.GROUP):
+    m, k = a.shape
+    n = b.shape[0]
+    status = gemm.new_status(a.device)
+    maps = gemm.TiledMaps(a, b, c, columns=columns)
+    gemm.launch_tiled(maps, m, n, k, group, status, flags=flags | gemm.TILE_WIDE, bias=bias)
+    torch.cuda.synchronize(a.device)
+    gemm.check_status(status)
+    return c
+
+
+@pytest.mark.parametrize("shape, columns", [((1024, 1792, 512), 224), ((768, 1792, 320), 224), ((1024, 1536, 512), 192),
+                                            ((4096, 3584, 256), 224), ((2560, 1536, 256), 192), ((512, 5376, 1088), 224),
+                                            ((4608, 5376, 128), 192), ((1024, 1792, 512), 256)])
+@pytest.mark.parametrize("group", [8, 3])
+def test_narrower_items_are_exact_on_the_reference_gate(device, shape, columns, group):
+    """One item per cluster and several (the last one's passes are staged together), ragged tile rows,
+    a K that wraps the ring: every width the launch can choose, forced here, on the integer gate."""
+    m, n, k = shape
+    a = _device_words(oracle.gemm_stage("a", m, k), device, torch.bfloat16)
+    b = _device_words(oracle.gemm_stage("b", n, k), device, torch.bfloat16)
+    c = torch.full((m, n), -3.0, dtype=torch.bfloat16, device=device)
+    _run_tiled(a, b, c, columns, group=group)
+    wrong, _, first = oracle.gemm_check_c(_words(c), m, n, k)
+    assert wrong == 0, f"{wrong} of {m * n} wrong, first at {first}"
+
+
+@pytest.mark.parametrize("columns", [224, 192])
+def test_narrower_items_fused_epilogue_leading_dimension_and_accumulate(device, columns):
+    """Bias (read per 32-column pass, never past column n), ReLU, a padded C whose margin stays
+    untouched, fp16 operands, and the reduce-add through both store maps."""
+    m, n, k = 1024, 5376, 256  # 21 x 256 = 24 x 224 = 28 x 192 columns
+    a = _device_words(oracle.gemm_stage_f16("a", m, k), device, torch.float16)
+    b = _device_words(oracle.gemm_stage_f16("b", n, k), device, torch.float16)
+    bias_values = ((np.arange(n) * 7) % 23 - 11).astype(np.float32) * 0.5
+    bias = _device_words(oracle.f32_to_bf16(bias_values), device, torch.bfloat16)
+    wide = torch.full((m, n + 64), 7.0, dtype=torch.bfloat16, device=device)
+    c = wide[:, :n]
+    _run_tiled(a, b, c, columns, flags=gemm.F16_OPERANDS | gemm.RELU, bias=bias)
+    fused = oracle.f32_to_bf16(np.maximum(oracle.gemm_exact(m, n, k) + bias_values[None, :], np.float32(0.0)))
+    assert np.array_equal(_words(c), fused)
+    assert (wide[:, n:] == 7.0).all()
+    _run_tiled(a, b, c, columns, flags=gemm.F16_OPERANDS | gemm.RELU | gemm.ACCUMULATE, bias=bias)
+    assert np.array_equal(_words(c), oracle.bf16_add_words(fused, fused))
+    assert (wide[:, n:] == 7.0).all()
+
+
+def test_the_launch_chooses_the_width_that_fills_its_waves(device):
+    """8192 x 3584 is 224 tiles of [512, 256]: three waves of 74 clusters and two tiles over. The entries
+    that build their own maps take 256 items of [512, 224] instead; same answer, bit for bit, as the
+    256-column items give."""
+    m, n, k = 8192, 3584, 256
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    if sms == 148:
+        assert gemm.item_columns(m, n, k, device) == 224
+        assert gemm.item_columns(m, 8 * n, k, device) == 256
+    a = _device_words(oracle.gemm_stage("a", m, k), device, torch.bfloat16)
+    b = _device_words(oracle.gemm_stage("b", n, k), device, torch.bfloat16)
+    c = _run(a, b)
+    wrong, _, first = oracle.gemm_check_c(_words(c), m, n, k)
+    assert wrong == 0, f"{wrong} of {m * n} wrong, first at {first}"
+    generator = torch.Generator(device=device).manual_seed(3)
+    a = (torch.randn((m, 1024), generator=generator, device=device) * 0.05).to(torch.bfloat16)
+    b = (torch.randn((n, 1024), generator=generator, device=device) * 0.05).to(torch.bfloat16)
+    chosen = _run(a, b)
+    plain = _run_tiled(a, b, torch.empty_like(chosen), 256)
+    assert torch.equal(chosen, plain)
+
+
+def test_widths_the_kernel_does_not_have_are_refused(device):
+    a = torch.zeros((1024, 64), dtype=torch.bfloat16, device=device)
+    b = torch.zeros((1792, 64), dtype=torch.bfloat16, device=device)
+    c = torch.zeros((1024, 1792), dtype=torch.bfloat16, device=device)
+    maps = gemm.TiledMaps(a, b, c, columns=224)
+    with pytest.raises(FerroKittensError, match="takes the narrow kernel"):
+        gemm.launch_tiled(maps, 1024, 1792, 64)
+    maps.columns = 208
+    with pytest.raises(FerroKittensError, match="256, 224 or 192 columns wide"):
+        gemm.launch_tiled(maps, 1024, 1792, 64, flags=gemm.TILE_WIDE)
+    maps.columns = 192
+    with pytest.raises(FerroKittensError, match="do not divide"):
+        gemm.launch_tiled(maps, 1024, 1792, 64, flags=gemm.TILE_WIDE)
+    maps.columns, maps.c_tail = 224, None
+    with pytest.raises(FerroKittensError, match="a map of their own"):
+        gemm.launch_tiled(maps, 1024, 1792, 64, flags=gemm.TILE_WIDE)

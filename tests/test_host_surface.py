@@ -209,6 +209,39 @@ def test_grid_is_whole_clusters_capped_at_one_per_sm_pair():
     assert lib.fk_gemm_grid(16384, 2048, 148) == 148
 
 
+def _wave_time(m, n, columns, clusters):
+    """Wave-times of [512, 256] items a launch takes with items `columns` wide: whole waves, and a last
+    one that costs half when it holds at most half a wave of tiles (it is re-cut into halves)."""
+    tiles = -(-m // 512) * (n // columns)
+    tail = tiles % clusters
+    return (tiles // clusters + (0 if tail == 0 else 0.5 if 2 * tail <= clusters else 1)) * columns / 256
+
+
+@pytest.mark.parametrize("sm_count", [148, 132, 64])
+def test_item_width_follows_the_wave_arithmetic(sm_count):
+    lib = library()
+    clusters = sm_count // 2
+    for m, n, k in [(8192, 3584, 8192), (8192, 7168, 8192), (8192, 14336, 8192), (8192, 28672, 8192),
+                    (16384, 16384, 16384), (16384, 2048, 16384), (2048, 5376, 4096), (4096, 10752, 512),
+                    (3072, 3072, 4096), (768, 5376, 8192)]:
+        chosen = lib.fk_gemm_item_columns(m, n, k, 0, sm_count)
+        assert chosen in (256, 224, 192) and n % chosen == 0
+        candidates = {columns: _wave_time(m, n, columns, clusters) for columns in (256, 224, 192) if n % columns == 0}
+        # narrower items cost about 2 % per flop: they are taken only where the waves promise 10 %
+        if chosen != 256:
+            assert candidates[chosen] < 0.90 * candidates[256]
+        else:
+            assert min(candidates.values()) >= 0.90 * candidates[256] - 1e-9
+    if sm_count == 148:
+        assert lib.fk_gemm_item_columns(8192, 3584, 8192, 0, 148) == 224   # 3.5 wave-times -> 3.06
+        assert lib.fk_gemm_item_columns(8192, 28672, 8192, 0, 148) == 256
+        assert lib.fk_gemm_item_columns(8192, 7168, 8192, 0, 148) == 256    # 6.5 -> 6.125: not enough
+    # launches the narrow kernel takes keep the 256-column maps; so do shapes the tiling refuses
+    assert lib.fk_gemm_item_columns(1024, 1792, 512, 0, 148) == 256
+    assert lib.fk_gemm_item_columns(1024, 1792, 512, 16, 148) in (256, 224)
+    assert lib.fk_gemm_item_columns(1000, 1792, 512, 0, 148) == 256
+
+
 # ---------------------------------------------------------------- layouts
 
 def test_packed_and_strided_strides():
