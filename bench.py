@@ -295,6 +295,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     from ferro_kittens_b200._lib import check, library
     from ferro_kittens_b200.build import build_cublaslt
 
+    args.group = args.group or gemm.GROUP
+
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device: the library has no CPU path")
     torch.cuda.set_device(local_rank)
@@ -642,6 +644,7 @@ def run_only(args, local_rank: int) -> None:
     from ferro_kittens_b200 import gemm
     from ferro_kittens_b200._lib import check, library
 
+    args.group = args.group or gemm.GROUP
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     stream = torch.cuda.current_stream().cuda_stream
@@ -733,7 +736,7 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--group", type=int, default=8)
+    parser.add_argument("--group", type=int, default=0, help="traversal width of the GEMM's item walk (0: the library's default)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--settle", type=float, default=0.5,
                         help="seconds of back-to-back launches before the timed K steps of every block")

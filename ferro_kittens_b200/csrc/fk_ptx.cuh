@@ -376,6 +376,32 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
         : "memory");
 }
 
+/// Cluster launch control (sm_100): a running cluster asks the hardware for the work of a cluster of
+/// its grid that has not started yet. The 16-byte answer is written to shared memory at `response`
+/// and completes 16 bytes on the mbarrier `bar`; a granted request means that cluster will never
+/// start and its work is the asker's. After a refusal (nothing is left to take) no further request
+/// may be made.
+__device__ __forceinline__ void clc_try_cancel(uint32_t response, uint32_t bar) {
+    asm volatile(
+        "clusterlaunchcontrol.try_cancel.async.shared::cta.mbarrier::complete_tx::bytes.b128 [%0], [%1];" ::"r"(response),
+        "r"(bar)
+        : "memory");
+}
+/// Decode the answer at `response`: true and the x index of the taken cluster's first CTA, or false.
+__device__ __forceinline__ bool clc_query(uint32_t response, uint32_t& first_cta_x) {
+    uint32_t granted, x = 0;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b128 answer;\n\tld.shared.b128 answer, [%2];\n\t"
+        "clusterlaunchcontrol.query_cancel.is_canceled.pred.b128 p, answer;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "@p clusterlaunchcontrol.query_cancel.get_first_ctaid::x.b32.b128 %1, answer;\n\t}"
+        : "=r"(granted), "+r"(x)
+        : "r"(response)
+        : "memory");
+    first_cta_x = x;
+    return granted != 0;
+}
+
 /// 1 in exactly one lane of a converged warp, 0 in the others. Use it as a BRANCH around the
 /// whole issuing role (`if (elect_one()) { waits, MMAs, commits }`): the compiler then knows the
 /// region runs in a single thread and emits the tight issue sequence -- 23 cycles of the thread's

@@ -23,6 +23,14 @@
 //               tcgen05.ld -> bf16 pairs held in registers -> accumulator handed back ->
 //               SWIZZLE_128B staging -> TMA store, overlapping the next item's main loop.
 //
+//   warp 10     (leader CTA only, launches of more items than resident clusters) the item feed: the
+//               grid has one cluster per item, the resident clusters never exit, and this warp asks
+//               the hardware for the next cluster that has not started (cluster launch control),
+//               one item ahead, and publishes its index to every role of both CTAs. The items in
+//               flight are therefore always the next ones of the traversal, however far the
+//               clusters' speeds drift apart over a launch: a static round-robin lets slow clusters
+//               fall waves behind, and the operand panels live in L2 multiply.
+//
 // Barriers are initialised once per launch and their phases carried across
 // items; roles meet only through them. Every wait is bounded.
 //
@@ -53,14 +61,21 @@ constexpr uint32_t kStageColumns = 64;  // columns per epilogue pass: one swizzl
 constexpr uint32_t kPasses = kBlockN / kStageColumns;
 // What an item's fourth epilogue pass is: 64 columns (items 256 wide), 32 (224) or nothing (192).
 enum LastPass : uint32_t { kLastNone = 0, kLastNarrow = 1, kLastWhole = 2 };
-constexpr uint32_t kThreads = (2 + kEpilogueWarps) * 32;
+constexpr uint32_t kFeedWarp = 2 + kEpilogueWarps;
+constexpr uint32_t kThreads = (3 + kEpilogueWarps) * 32;
+// The item feed: a ring of item indices every role reads in turn. Its readers are, per CTA, the
+// producer thread and the epilogue warps, and the leader's MMA thread.
+constexpr uint32_t kFeedSlots = 2;
+constexpr uint32_t kFeedReaders = 2 * (1 + kEpilogueWarps) + 1;
+constexpr uint32_t kNoItem = 0xffffffffu;
 constexpr uint32_t kATileBytes = kBlockM * kBlockK * 2;
 constexpr uint32_t kBTileBytes = kHalfN * kBlockK * 2;
 constexpr uint32_t kBandBytes = 32 * kStageColumns * 2;  // one warp's [32, 64] bf16 staging tile
 
 // The shared plan, one walk for the kernel's offsets and the launch's total.
 struct Plan {
-    SharedPlan a_ring, b_ring, bands, full, empty, acc_full, acc_empty, tmem_slot, stop, end;
+    SharedPlan a_ring, b_ring, bands, full, empty, acc_full, acc_empty, feed_full, feed_empty, feed_go, claim_full,
+        claim_answer, feed_ring, tmem_slot, stop, end;
     constexpr Plan()
         : a_ring(SharedPlan{}.tile_ring(kBlockM, kBlockK, 2, kStages * kHalves)),
           b_ring(a_ring.tile_ring(kHalfN, kBlockK, 2, kStages)),
@@ -69,7 +84,13 @@ struct Plan {
           empty(full.semaphores(kStages)),
           acc_full(empty.semaphore()),
           acc_empty(acc_full.semaphore()),
-          tmem_slot(acc_empty.tmem_slot()),
+          feed_full(acc_empty.semaphores(kFeedSlots)),
+          feed_empty(feed_full.semaphores(kFeedSlots)),
+          feed_go(feed_empty.semaphore()),
+          claim_full(feed_go.semaphore()),
+          claim_answer(claim_full.reserve(16, 16)),
+          feed_ring(claim_answer.reserve(4 * kFeedSlots, 4)),
+          tmem_slot(feed_ring.tmem_slot()),
           stop(tmem_slot.word()),
           end(stop) {}
 };
@@ -91,6 +112,8 @@ enum StallCode : uint32_t {
     kStallMmaFull = 0x102,
     kStallMmaAccumulator = 0x103,
     kStallEpilogue = 0x104,
+    kStallFeed = 0x105,
+    kStallClaim = 0x106,
     kMisaligned = 0x1ff,
 };
 
@@ -102,6 +125,7 @@ struct Schedule {
     uint32_t tile_n;     // columns of C per item (the MMAs' N): 256, or 224 / 192 where that fills the waves better
     uint32_t group;      // traversal width of `grouped`
     uint32_t k_blocks;   // k / 64
+    uint32_t dynamic;    // non-zero: one cluster per item in the grid, items handed out by the feed warp
     uint32_t whole;      // leading items that are whole two-half tiles
     uint32_t items;      // whole + 2 * (tiles - whole): the rest are single halves
     uint32_t idesc;      // tcgen05 instruction descriptor (operand format differs by entry point)
@@ -237,6 +261,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     const uint32_t empty = base + kPlan.empty.at;
     const uint32_t acc_full = base + kPlan.acc_full.at;
     const uint32_t acc_empty = base + kPlan.acc_empty.at;
+    const uint32_t feed_full = base + kPlan.feed_full.at;
+    const uint32_t feed_empty = base + kPlan.feed_empty.at;
+    const uint32_t feed_go = base + kPlan.feed_go.at;
+    const uint32_t claim_full = base + kPlan.claim_full.at;
+    const uint32_t claim_answer = base + kPlan.claim_answer.at;
+    const uint32_t feed_ring = base + kPlan.feed_ring.at;
+    volatile uint32_t* feed_words = reinterpret_cast<volatile uint32_t*>(dynamic_shared + kPlan.feed_ring.at);
     const uint32_t slot = base + kPlan.tmem_slot.at;
     const uint32_t stop_addr = base + kPlan.stop.at;
     volatile uint32_t* stop_flag =
@@ -254,6 +285,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         }
         mbar_init(acc_full, 1);
         mbar_init(acc_empty, 2 * kEpilogueWarps);
+        for (uint32_t s = 0; s < kFeedSlots; ++s) {
+            mbar_init(feed_full + 8 * s, 1);
+            mbar_init(feed_empty + 8 * s, kFeedReaders);
+        }
+        mbar_init(feed_go, 1);
+        mbar_init(claim_full, 1);
         *stop_flag = 0;
         fence_mbarrier_init();
         prefetch_tensormap(&a_map);
@@ -270,13 +307,35 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 
     const StallSite site{status, stop_flag, mapa(stop_addr, peer)};
 
+    // How a role learns its next unit of work. Static launches (no more units than resident
+    // clusters, or a K split): cluster c walks units c, c + clusters, ... . Dynamic launches: the
+    // role's next entry of the feed ring, which it hands back as soon as it has read it. `taken`
+    // counts the role's reads, `previous` is the unit it read last; false = no further unit.
+    const auto take = [&](uint32_t& taken, uint32_t previous, uint32_t& number, bool& live, bool whole_warp) -> bool {
+        if (kSplitK || !plan.dynamic) {
+            number = taken == 0 ? cluster_id_x() : previous + cluster_count_x();
+            ++taken;
+            return number < unit_count<kSplitK>(plan);
+        }
+        const uint32_t s = taken % kFeedSlots;
+        if (!mbar_wait(feed_full + 8 * s, (taken / kFeedSlots) & 1u, site, kStallFeed, taken)) {
+            live = false;
+            return false;
+        }
+        fence_acq_rel_cluster();  // the entry was written from the leader CTA
+        number = feed_words[s];
+        if (whole_warp) __syncwarp();
+        if (!whole_warp || lane == 0) mbar_arrive_cluster(mapa(feed_empty + 8 * s, 0));
+        ++taken;
+        return number != kNoItem;
+    };
+
     if (warp == 0) {
         // ------------------------------------------------ producer (both CTAs)
         if (lane == 0) {
-            uint32_t fill = 0;
+            uint32_t fill = 0, taken = 0, number = 0;
             bool live = true;
-            for (uint32_t number = cluster_id_x(); live && number < unit_count<kSplitK>(plan);
-                 number += cluster_count_x()) {
+            while (live && take(taken, number, number, live, false)) {
                 const Unit unit = unit_at<kSplitK>(plan, number);
                 const Item& item = unit.item;
                 if (item.halves == 0) continue;
@@ -310,10 +369,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         // own cost per MMA does not show here (lane 0 or an elected lane: 1436 vs 1439 TFLOP/s).
         if (rank == 0 && lane == 0) {
             const uint32_t idesc = plan.idesc;
-            uint32_t drain = 0, count = 0;
+            uint32_t drain = 0, count = 0, taken = 0, number = 0;
             bool live = true;
-            for (uint32_t number = cluster_id_x(); live && number < unit_count<kSplitK>(plan);
-                 number += cluster_count_x()) {
+            while (live && take(taken, number, number, live, false)) {
+                // The feed claims one item ahead: the next when this one begins.
+                if (!kSplitK && plan.dynamic) mbar_arrive(feed_go);
                 const Unit unit = unit_at<kSplitK>(plan, number);
                 const Item& item = unit.item;
                 if (item.halves == 0) continue;
@@ -364,26 +424,71 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 ++count;
             }
         }
+    } else if (warp == kFeedWarp) {
+        // ------------------------------------------------ item feed (leader only, dynamic launches)
+        if (!kSplitK && plan.dynamic && rank == 0 && lane == 0) {
+            uint32_t published = 0, started = 0, claims = 0;
+            bool live = true;
+            // An entry goes to the same slot of both CTAs' rings, then each CTA's `feed_full`.
+            const auto publish = [&](uint32_t value) {
+                const uint32_t s = published % kFeedSlots;
+                if (!mbar_wait(feed_empty + 8 * s, ((published / kFeedSlots) & 1u) ^ 1u, site, kStallFeed, published)) {
+                    live = false;
+                    return;
+                }
+                fence_acq_rel_cluster();  // the peer's readers are done with the slot
+                feed_words[s] = value;
+                st_shared_cluster_u32(mapa(feed_ring + 4 * s, 1), value);
+                mbar_arrive(feed_full + 8 * s);
+                mbar_arrive_cluster(mapa(feed_full + 8 * s, 1));
+                ++published;
+            };
+            // This cluster's own item is the one the grid launched it for.
+            publish(cluster_id_x());
+            while (live) {
+                // One item ahead and no more (a claimed item is this cluster's to do, however late):
+                // the next claim goes out when the MMA thread begins the item published last.
+                if (!mbar_wait(feed_go, started & 1u, site, kStallFeed, started)) break;
+                ++started;
+                mbar_arrive_expect_tx(claim_full, 16);
+                clc_try_cancel(claim_answer, claim_full);
+                if (!mbar_wait(claim_full, claims & 1u, site, kStallClaim, claims)) break;
+                ++claims;
+                uint32_t first_cta = 0;
+                const bool granted = clc_query(claim_answer, first_cta);
+                fence_proxy_async_shared();  // the answer is read before a later claim may overwrite it
+                publish(granted ? first_cta / 2 : kNoItem);
+                if (!granted) break;  // after a refusal no further request may be made
+            }
+        }
     } else {
         // ------------------------------------------------ epilogue (both CTAs)
         const uint32_t half = (warp - 2) >> 2;  // which accumulator this warp drains
         const uint32_t quadrant = warp & 3u;    // the tensor-memory lanes this warp may read
         const uint32_t band = bands + (warp - 2) * kBandBytes;
         const uint32_t t_row = tmem_address(tmem, 32 * quadrant, half * kBlockN);
-        uint32_t count = 0;
+        uint32_t count = 0, taken = 0, number = 0, upcoming = 0;
         bool live = true;
-        for (uint32_t number = cluster_id_x(); live && number < unit_count<kSplitK>(plan);
-             number += cluster_count_x()) {
+        // The unit after the current one is read as soon as the current one's accumulator is full:
+        // whether there is one decides how the stores of the current one are staged.
+        bool have = take(taken, 0, number, live, true), more = false;
+        for (bool first = true;; first = false) {
+            if (!first) number = upcoming, have = more;
+            if (!live || !have) break;
             const Unit unit = unit_at<kSplitK>(plan, number);
             const Item& item = unit.item;
-            const uint32_t index = kSplitK ? number : unit.index;  // the last-unit test below walks units
-            if (item.halves == 0) continue;
+            if (item.halves == 0) {
+                more = take(taken, number, upcoming, live, true);
+                continue;
+            }
             if (!mbar_wait(acc_full, count & 1u, site, kStallEpilogue, count)) {
                 live = false;
                 break;
             }
             ++count;
             tc_fence_after_sync();
+            more = take(taken, number, upcoming, live, true);
+            if (!live) break;
             const bool mine = half < item.halves;
             if constexpr (kSplitK) {
                 // This unit's share of the sums: the warp's [32, 256] fp32 band goes into the workspace
@@ -516,7 +621,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 else
                     tma_store_2d(map, tile, column, c_row);
             };
-            if (index + cluster_count_x() >= plan.items) {
+            if (!more) {
                 // This CTA's last item: no load is outstanding or to come and every MMA that read
                 // the operand ring has retired (acc_full), so the ring is free shared memory. Each
                 // warp stages all its passes there at once, kPasses tiles of its own, and the
@@ -833,6 +938,7 @@ static Schedule schedule(uint32_t m, uint32_t n, uint32_t k, uint32_t group, uin
     plan.idesc = instruction_descriptor(2 * kBlockM, tile_n, false, false,
                                         (flags & FK_GEMM_F16_OPERANDS) ? 0u : 1u);
     plan.tile_n = tile_n;
+    plan.dynamic = 0;
     plan.accumulate = (flags & FK_GEMM_ACCUMULATE) ? 1u : 0u;
     plan.relu = (flags & FK_GEMM_RELU) ? 1u : 0u;
     plan.bias = nullptr;
@@ -996,7 +1102,10 @@ static int launch_fused(const void* a_map, const void* b_map, const void* c_map,
         return launch_narrow(gemm::narrow::gemm_bf16_narrow_kernel<gemm::narrow::kStagesShared, false>,
                              gemm::narrow::shared_bytes<gemm::narrow::kStagesShared>(), 1);
     }
-    const uint32_t grid = 2 * (plan.items < clusters ? plan.items : clusters);
+    // More items than resident clusters: one cluster per item in the grid, handed out as clusters
+    // fall free (the resident ones never exit before the grid is used up).
+    plan.dynamic = plan.items > clusters ? 1u : 0u;
+    const uint32_t grid = 2 * (plan.dynamic ? plan.items : plan.items < clusters ? plan.items : clusters);
     gemm::gemm_bf16_pair_kernel<false><<<grid, gemm::kThreads, gemm::kSharedBytes,
                                          static_cast<cudaStream_t>(stream)>>>(
         *static_cast<const CUtensorMap*>(a_map), *static_cast<const CUtensorMap*>(b_map),

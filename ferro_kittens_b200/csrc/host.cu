@@ -429,6 +429,8 @@ static const char* stall_role(uint32_t code) {
         case 0x102: return "gemm MMA waiting for a loaded stage";
         case 0x103: return "gemm MMA waiting for a drained accumulator";
         case 0x104: return "gemm epilogue waiting for a finished accumulator";
+        case 0x105: return "gemm role waiting for the item feed";
+        case 0x106: return "gemm item feed waiting for the answer to a cluster-launch-control request";
         case 0x201: return "flash loader waiting for a free K/V slot";
         case 0x202: return "flash MMA waiting for Q";
         case 0x203: return "flash MMA waiting for a loaded K/V slot";

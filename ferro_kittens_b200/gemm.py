@@ -14,8 +14,9 @@ from .global_layout import GlobalLayout
 BLOCK_M = 128
 BLOCK_N = 256
 BLOCK_K = 64
-#: The traversal width the reference ships (examples/src/gemm.rs:138).
-GROUP = 8
+#: The traversal width: the reference ships 8 for its kernel (examples/src/gemm.rs:138); this one measures
+#: best at 6 on 148 SMs (its 74 items in flight then cover 6 x 12.3 tiles: the fewest operand bytes per wave).
+GROUP = 6
 #: fp16 A and B (C stays bf16): the operand types of examples/src/gemm_sol.rs.
 F16_OPERANDS = 1
 #: C += A . B^T through the copy engine's reduce-add (src/shared.rs:974-1009).

@@ -113,8 +113,11 @@ uint32_t fk_gemm_threads(void);
 uint32_t fk_flash_shared_bytes(void);
 uint32_t fk_flash_threads(void);
 
-/* `gemm::grid` (examples/src/gemm.rs:472-475): CTAs the launch asks for, a whole
- * number of two-CTA clusters, capped at one cluster per SM pair. */
+/* `gemm::grid` (examples/src/gemm.rs:472-475): CTAs of a launch resident at a time, a whole
+ * number of two-CTA clusters, capped at one cluster per SM pair. (A launch of more items than
+ * that puts one cluster per item in its grid; the resident clusters never exit and take the
+ * others' items over one by one through cluster launch control, so the items in flight are always
+ * the next ones of the traversal.) */
 uint32_t fk_gemm_grid(uint32_t m, uint32_t n, uint32_t sm_count);
 
 /* `launch::admit_shared_plan` (src/launch.rs:110-132): opt `kernel` (a host
@@ -182,6 +185,10 @@ int fk_gemm_bf16(const void* a, const void* b, void* c, uint32_t m, uint32_t n, 
  * src/global.rs:410-416, as examples/src/layernorm.rs:200-203 uses them for beta). Bias first,
  * then the map, then (with FK_GEMM_ACCUMULATE) the add into C.
  * fk_gemm_bf16_launch / fk_gemm_bf16 are these with flags = 0 and no bias. */
+/* The traversal width (`group`, the reference's x8, examples/src/gemm.rs:138) this kernel measures
+ * best with on a 148-SM part: its 74 items in flight then cover 6 x 12.3 tiles, the fewest operand
+ * panel bytes per wave for [512, 256] items. */
+#define FK_GEMM_GROUP 6u
 #define FK_GEMM_F16_OPERANDS 1u
 #define FK_GEMM_ACCUMULATE 2u
 #define FK_GEMM_RELU 4u

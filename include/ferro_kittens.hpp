@@ -176,7 +176,7 @@ inline void wait_event(void* event, uint32_t budget_ms = DEFAULT_BUDGET_MS) { ch
 namespace gemm {
 
 constexpr std::size_t BLOCK_M = 128, BLOCK_N = 256, HALF_N = 128, BLOCK_K = 64;
-constexpr uint32_t GROUP = 8;  // examples/src/gemm.rs:138
+constexpr uint32_t GROUP = FK_GEMM_GROUP;  // the reference ships 8 for its kernel (examples/src/gemm.rs:138)
 using ATile = shared::SharedTile<shared::Bf16, BLOCK_M, BLOCK_K>;
 using BTile = shared::SharedTile<shared::Bf16, HALF_N, BLOCK_K>;
 using CStage = shared::SharedTile<shared::Bf16, 32, 64>;

@@ -313,3 +313,39 @@ def test_widths_the_kernel_does_not_have_are_refused(device):
     maps.columns, maps.c_tail = 224, None
     with pytest.raises(FerroKittensError, match="a map of their own"):
         gemm.launch_tiled(maps, 1024, 1792, 64, flags=gemm.TILE_WIDE)
+
+
+# ---- launches of more items than resident clusters: one cluster per item in the grid, handed out through
+# ---- cluster launch control by the leader CTA's feed warp
+
+@pytest.mark.parametrize("shape", [(8192, 8192, 64), (4352, 4096, 128), (2048, 14336, 192), (16384, 4096, 64)])
+@pytest.mark.parametrize("group", [6, 1])
+def test_items_handed_out_by_the_feed_are_exact(device, shape, group):
+    """A k-block or two per item, so that a cluster runs through items as fast as the feed can claim
+    them (512 to 1024 items on 74 clusters), a ragged last tile row, and a width the launch chooses:
+    every tile must be computed exactly once, whichever cluster took it."""
+    m, n, k = shape
+    a = _device_words(oracle.gemm_stage("a", m, k), device, torch.bfloat16)
+    b = _device_words(oracle.gemm_stage("b", n, k), device, torch.bfloat16)
+    c = torch.full((m, n), -3.0, dtype=torch.bfloat16, device=device)
+    status = gemm.new_status(device)
+    for _ in range(3):
+        c.fill_(-3.0)
+        gemm.run(a, b, c, group=group, status=status, tile="wide")
+        torch.cuda.synchronize(device)
+        gemm.check_status(status)
+        wrong, _, first = oracle.gemm_check_c(_words(c), m, n, k)
+        assert wrong == 0, f"{wrong} of {m * n} wrong, first at {first}"
+
+
+def test_accumulate_under_the_feed_adds_every_tile_once(device):
+    """C += A.B^T with more items than clusters: a tile taken twice, or dropped, shows in the sum."""
+    m, n, k = 4096, 8192, 64
+    a = _device_words(oracle.gemm_stage("a", m, k), device, torch.bfloat16)
+    b = _device_words(oracle.gemm_stage("b", n, k), device, torch.bfloat16)
+    c = torch.zeros((m, n), dtype=torch.bfloat16, device=device)
+    _run(a, b, c, accumulate=True)
+    once = _words(c).copy()
+    assert oracle.gemm_check_c(once, m, n, k)[0] == 0
+    _run(a, b, c, accumulate=True)
+    assert np.array_equal(_words(c), oracle.bf16_add_words(once, once))

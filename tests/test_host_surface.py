@@ -186,15 +186,19 @@ def test_this_librarys_own_plans_fit_one_cta_per_sm():
     lib = library()
     for total in (lib.fk_gemm_shared_bytes(), lib.fk_flash_shared_bytes()):
         assert 116_736 < total <= 232_448  # admits exactly one CTA per SM
+    # gemm: producer, MMA, eight epilogue warps and the item feed.
     # flash: three warpgroups (two softmax teams; loader + MMA), so that registers can move between them.
-    assert lib.fk_gemm_threads() == 320 and lib.fk_flash_threads() == 384
-    # gemm: 4 stages of two A tiles and one B tile, 8 staging bands, 10 barriers, slot, stop word.
+    assert lib.fk_gemm_threads() == 352 and lib.fk_flash_threads() == 384
+    # gemm: 4 stages of two A tiles and one B tile, 8 staging bands, 10 barriers of the operand and
+    # accumulator hand-overs, 6 of the item feed, its 16-byte claim answer and two-entry ring, slot, stop word.
     plan = SharedPlan.sizing()
     plan.tile_ring(128, 64, 8)
     plan.tile_ring(128, 64, 4)
     plan.tile_ring(32, 64, 8)
-    for count in (4, 4, 1, 1):
+    for count in (4, 4, 1, 1, 2, 2, 1, 1):
         plan.semaphores(count)
+    plan.reserve(16, 16)
+    plan.reserve(8, 4)
     plan.tmem_slot()
     plan.reserve(4, 4)
     assert plan.bytes() == lib.fk_gemm_shared_bytes()
