@@ -582,8 +582,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak,
                          # dram__bytes_read + write of one launch of this kernel on the full 16384^3 shape,
-                         # one ncu capture at traversal width 8, scaled by the rank's share of N
-                         "traffic": (7.35e9 + 0.591e9) * n_local / N, "traffic_unit": "bytes/launch",
+                         # the mean of six launches in one ncu capture at traversal width 6, scaled by the rank's share of N
+                         "traffic": (8.11e9 + 0.669e9) * n_local / N, "traffic_unit": "bytes/launch",
                          "algorithmic_flops_per_launch": 2.0 * M * n_local * K,
                          "peak_source": f"{peaks['source']} ({'sustained' if sustained else 'burst'} cuBLAS bf16)",
                          "frac_of_measured_burst": achieved / peaks["burst"],
