@@ -656,7 +656,7 @@ def run_only(args, local_rank: int) -> None:
         b = (torch.randn((n, k), generator=generator, device=device) / math.sqrt(k)).to(torch.bfloat16)
         c = torch.empty((m, n), dtype=torch.bfloat16, device=device)
         maps = gemm.TiledMaps(a, b, c, columns=args.item_columns or None)
-        flags = gemm.TILE_WIDE if args.item_columns else 0
+        flags = (gemm.TILE_WIDE if args.item_columns else 0) | {"": 0, "feed": gemm.ORDER_FEED, "static": gemm.ORDER_STATIC}[args.order]
         fn = lambda: gemm.launch_tiled(maps, m, n, k, args.group, status, flags=flags)  # noqa: E731
         flops = 2.0 * m * n * k
         name = f"gemm_bf16_{m}x{n}x{k}"
@@ -726,6 +726,8 @@ def main() -> None:
                         help="with --only gemm: also launch torch.matmul (cuBLAS) on the same operands")
     parser.add_argument("--item-columns", type=int, default=0, choices=[0, 256, 224, 192],
                         help="with --only gemm: force the wide kernel with items this many columns wide (0: the launch chooses)")
+    parser.add_argument("--order", default="", choices=["", "feed", "static"],
+                        help="with --only gemm: how the wide kernel's clusters get their items (default: the launch chooses)")
     parser.add_argument("--m", type=int, default=8192)
     parser.add_argument("--n", type=int, default=8192)
     parser.add_argument("--k", type=int, default=8192)

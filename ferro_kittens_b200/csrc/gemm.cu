@@ -237,7 +237,10 @@ __device__ __forceinline__ Unit unit_at(const Schedule& plan, uint32_t number) {
     return unit;
 }
 
-template <bool kSplitK>
+// kAnyWidth: items may be 224 or 192 columns wide (Schedule::tile_n); without it the width is the
+// constant 256 and the epilogue's passes are fixed at compile time, which is what launches of a
+// few shallow items, whose epilogue is not hidden under a next item, are timed by.
+template <bool kSplitK, bool kAnyWidth>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap a_map,
                           const __grid_constant__ CUtensorMap b_map,
@@ -341,9 +344,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 if (item.halves == 0) continue;
                 const int a_row = static_cast<int>(item.row + kBlockM * rank);
                 // Each CTA stages its half of the item's columns: tile_n / 2 rows of B (the B map's box).
-                const int b_row = static_cast<int>(item.column + (plan.tile_n / 2) * rank);
+                const uint32_t tile_n = kAnyWidth ? plan.tile_n : kBlockN;
+                const int b_row = static_cast<int>(item.column + (tile_n / 2) * rank);
                 // Both CTAs' boxes land on the leader's barrier.
-                const uint32_t pair_bytes = 2 * (item.halves * kATileBytes + (plan.tile_n / 2) * kBlockK * 2);
+                const uint32_t pair_bytes = 2 * (item.halves * kATileBytes + (tile_n / 2) * kBlockK * 2);
                 for (uint32_t k = unit.k0; k < unit.k1; ++k, ++fill) {
                     const uint32_t s = fill % kStages;
                     const uint32_t parity = (fill / kStages) & 1u;
@@ -573,7 +577,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             // Read this warp's band of the item out as bf16 pairs, then release the accumulator: the
             // stores below overlap the next item's main loop. An item is 256, 224 or 192 columns wide:
             // three passes of 64 columns, then a fourth of 64, of 32 (`kLastNarrow`) or none.
-            const uint32_t last_pass = plan.tile_n == kBlockN ? kLastWhole : plan.tile_n == kBlockN - 32 ? kLastNarrow : kLastNone;
+            const uint32_t last_pass = !kAnyWidth || plan.tile_n == kBlockN ? kLastWhole
+                                       : plan.tile_n == kBlockN - 32        ? kLastNarrow
+                                                                            : kLastNone;
             uint32_t held[kPasses][32];
             if (mine) {
 #pragma unroll
@@ -772,6 +778,7 @@ __global__ void __launch_bounds__(kThreads, kStages == kStagesShared ? 2 : 1)
     const uint32_t run = (plan.k_blocks + slices - 1) / slices;
     const uint32_t k0 = slice * run;
     const uint32_t k1 = k0 + run < plan.k_blocks ? k0 + run : plan.k_blocks;
+    uint32_t preloaded = 0;  // k-blocks whose loads the producer thread issued before the rendezvous
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
@@ -783,8 +790,17 @@ __global__ void __launch_bounds__(kThreads, kStages == kStagesShared ? 2 : 1)
         mbar_init(partial_full, (slices > 1 ? slices - 1 : 1) * kEpilogueWarps);
         *stop_flag = 0;
         fence_mbarrier_init();
-        prefetch_tensormap(&a_map);
-        prefetch_tensormap(&b_map);
+        fence_proxy_async_shared();
+        // This thread is the producer, and the ring's first stages are free by construction: their
+        // loads go out now, under the tensor-memory allocation and the rendezvous below (a launch of
+        // a few k-blocks is mostly its own start-up).
+        preloaded = k1 - k0 < kStages ? k1 - k0 : kStages;
+        for (uint32_t i = 0; i < preloaded; ++i) {
+            mbar_arrive_expect_tx(full + 8 * i, 2 * kTileBytes);
+            const int column = static_cast<int>(kBlockK * (k0 + i));
+            tma_load_2d(a_ring + i * kTileBytes, &a_map, column, static_cast<int>(row0), full + 8 * i);
+            tma_load_2d(b_ring + i * kTileBytes, &b_map, column, static_cast<int>(column0), full + 8 * i);
+        }
         prefetch_tensormap(&c_map);
     }
     if (warp == 1) {
@@ -804,7 +820,7 @@ __global__ void __launch_bounds__(kThreads, kStages == kStagesShared ? 2 : 1)
     if (warp == 0) {
         // ------------------------------------------------ producer
         if (lane == 0) {
-            for (uint32_t k = k0; k < k1; ++k) {
+            for (uint32_t k = k0 + preloaded; k < k1; ++k) {
                 const uint32_t s = (k - k0) % kStages;
                 if (!mbar_wait(empty + 8 * s, (((k - k0) / kStages) & 1u) ^ 1u, prompt, kStallProducer, k)) break;
                 mbar_arrive_expect_tx(full + 8 * s, 2 * kTileBytes);
@@ -1032,10 +1048,13 @@ static bool takes_narrow(uint32_t m, uint32_t n, uint32_t k, uint32_t flags, uin
 static int launch_fused(const void* a_map, const void* b_map, const void* c_map, const void* c_narrow_map,
                         uint32_t tile_n, const void* bias, uint32_t m, uint32_t n, uint32_t k, uint32_t group,
                         uint32_t flags, void* stream, uint32_t* device_status) {
-    if (flags & ~(FK_GEMM_F16_OPERANDS | FK_GEMM_ACCUMULATE | FK_GEMM_RELU | FK_GEMM_TILE_NARROW | FK_GEMM_TILE_WIDE))
+    if (flags & ~(FK_GEMM_F16_OPERANDS | FK_GEMM_ACCUMULATE | FK_GEMM_RELU | FK_GEMM_TILE_NARROW | FK_GEMM_TILE_WIDE |
+                  FK_GEMM_ORDER_FEED | FK_GEMM_ORDER_STATIC))
         return fk_fail(FK_ERR_INVALID, "unknown GEMM flags 0x%x", flags);
     if ((flags & FK_GEMM_TILE_NARROW) && (flags & FK_GEMM_TILE_WIDE))
         return fk_fail(FK_ERR_INVALID, "the narrow and the wide tile were both asked for");
+    if ((flags & FK_GEMM_ORDER_FEED) && (flags & FK_GEMM_ORDER_STATIC))
+        return fk_fail(FK_ERR_INVALID, "the fed and the static item order were both asked for");
     if (reinterpret_cast<uintptr_t>(bias) & 15u)
         return fk_fail(FK_ERR_ALIGNMENT, "the bias vector wants 16-byte alignment");
     if (!a_map || !b_map || !c_map) return fk_fail(FK_ERR_INVALID, "a tensor map pointer is null");
@@ -1052,7 +1071,7 @@ static int launch_fused(const void* a_map, const void* b_map, const void* c_map,
     const int sm_count = facts.sm_count;
     uint32_t limit = 0;
     const int admitted = fk_admit_shared_plan(
-        reinterpret_cast<const void*>(gemm::gemm_bf16_pair_kernel<false>), gemm::kSharedBytes, &limit);
+        reinterpret_cast<const void*>(gemm::gemm_bf16_pair_kernel<false, false>), gemm::kSharedBytes, &limit);
     if (admitted != FK_OK) return admitted;
 
     const uint32_t clusters = static_cast<uint32_t>(sm_count) / 2;
@@ -1102,14 +1121,30 @@ static int launch_fused(const void* a_map, const void* b_map, const void* c_map,
         return launch_narrow(gemm::narrow::gemm_bf16_narrow_kernel<gemm::narrow::kStagesShared, false>,
                              gemm::narrow::shared_bytes<gemm::narrow::kStagesShared>(), 1);
     }
-    // More items than resident clusters: one cluster per item in the grid, handed out as clusters
-    // fall free (the resident ones never exit before the grid is used up).
-    plan.dynamic = plan.items > clusters ? 1u : 0u;
+    // Long launches: one cluster per item in the grid, handed out as clusters fall free (the resident
+    // ones never exit before the grid is used up). What that order buys is that clusters cannot drift
+    // waves apart, which takes several waves to matter; and the feed learns the next item a claim's
+    // round trip (~2 us) after the current one begins, which the producer of a short item would wait
+    // out at every item boundary (4096 x 4096 x 512, 128 items of 8 k-blocks: 23.9 us against 19.4
+    // with the static walk). So: from four waves on, items of at least 32 k-blocks.
+    plan.dynamic = (plan.items >= 4 * clusters && plan.k_blocks >= 32) ? 1u : 0u;
+    if (flags & FK_GEMM_ORDER_STATIC) plan.dynamic = 0;
+    if (flags & FK_GEMM_ORDER_FEED) plan.dynamic = plan.items > clusters ? 1u : 0u;
     const uint32_t grid = 2 * (plan.dynamic ? plan.items : plan.items < clusters ? plan.items : clusters);
-    gemm::gemm_bf16_pair_kernel<false><<<grid, gemm::kThreads, gemm::kSharedBytes,
-                                         static_cast<cudaStream_t>(stream)>>>(
-        *static_cast<const CUtensorMap*>(a_map), *static_cast<const CUtensorMap*>(b_map),
-        *static_cast<const CUtensorMap*>(c_map), *static_cast<const CUtensorMap*>(c_narrow_map), plan, device_status);
+    if (plan.tile_n == gemm::kBlockN) {
+        gemm::gemm_bf16_pair_kernel<false, false><<<grid, gemm::kThreads, gemm::kSharedBytes,
+                                                    static_cast<cudaStream_t>(stream)>>>(
+            *static_cast<const CUtensorMap*>(a_map), *static_cast<const CUtensorMap*>(b_map),
+            *static_cast<const CUtensorMap*>(c_map), *static_cast<const CUtensorMap*>(c_narrow_map), plan, device_status);
+    } else {
+        const int wide_admitted = fk_admit_shared_plan(
+            reinterpret_cast<const void*>(gemm::gemm_bf16_pair_kernel<false, true>), gemm::kSharedBytes, &limit);
+        if (wide_admitted != FK_OK) return wide_admitted;
+        gemm::gemm_bf16_pair_kernel<false, true><<<grid, gemm::kThreads, gemm::kSharedBytes,
+                                                   static_cast<cudaStream_t>(stream)>>>(
+            *static_cast<const CUtensorMap*>(a_map), *static_cast<const CUtensorMap*>(b_map),
+            *static_cast<const CUtensorMap*>(c_map), *static_cast<const CUtensorMap*>(c_narrow_map), plan, device_status);
+    }
     FK_CUDA(cudaGetLastError());
     return FK_OK;
 }
@@ -1262,7 +1297,7 @@ extern "C" int fk_gemm_fused_workspace(const void* a, const void* b, void* c, co
         return fk_fail(FK_ERR_ALIGNMENT, "the workspace wants 16-byte alignment");
     if (!a || !b || !c) return fk_fail(FK_ERR_INVALID, "an operand pointer is null");
     if (ldc < n) return fk_fail(FK_ERR_SHAPE, "ldc %u is narrower than the %u columns of C", ldc, n);
-    if (flags & ~(FK_GEMM_F16_OPERANDS | FK_GEMM_ACCUMULATE | FK_GEMM_RELU | FK_GEMM_TILE_WIDE))
+    if (flags & ~(FK_GEMM_F16_OPERANDS | FK_GEMM_ACCUMULATE | FK_GEMM_RELU | FK_GEMM_TILE_WIDE | FK_GEMM_ORDER_STATIC))
         return fk_fail(FK_ERR_INVALID, "unknown GEMM flags 0x%x for a launch that splits K", flags);
     if (reinterpret_cast<uintptr_t>(bias) & 15u)
         return fk_fail(FK_ERR_ALIGNMENT, "the bias vector wants 16-byte alignment");
@@ -1278,7 +1313,7 @@ extern "C" int fk_gemm_fused_workspace(const void* a, const void* b, void* c, co
     if (status != FK_OK) return status;
 
     uint32_t limit = 0;
-    const int admitted = fk_admit_shared_plan(reinterpret_cast<const void*>(gemm::gemm_bf16_pair_kernel<true>),
+    const int admitted = fk_admit_shared_plan(reinterpret_cast<const void*>(gemm::gemm_bf16_pair_kernel<true, false>),
                                               gemm::kSharedBytes, &limit);
     if (admitted != FK_OK) return admitted;
     const uint32_t clusters = static_cast<uint32_t>(facts.sm_count) / 2;
@@ -1291,7 +1326,7 @@ extern "C" int fk_gemm_fused_workspace(const void* a, const void* b, void* c, co
     plan.arrivals = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(workspace) + uint64_t(m) * n * 4);
     const uint32_t units = plan.items * plan.splits;
     const uint32_t grid = 2 * (units < clusters ? units : clusters);
-    gemm::gemm_bf16_pair_kernel<true><<<grid, gemm::kThreads, gemm::kSharedBytes, static_cast<cudaStream_t>(stream)>>>(
+    gemm::gemm_bf16_pair_kernel<true, false><<<grid, gemm::kThreads, gemm::kSharedBytes, static_cast<cudaStream_t>(stream)>>>(
         maps[0], maps[1], maps[2], maps[3], plan, device_status);
     FK_CUDA(cudaGetLastError());
     return FK_OK;

@@ -28,6 +28,10 @@ RELU = 4
 #: persistent two-CTA clusters.
 TILE_NARROW = 8
 TILE_WIDE = 16
+#: Pick how the wide kernel's clusters get their items: handed out through cluster launch control as
+#: clusters fall free, or a static round-robin.
+ORDER_FEED = 32
+ORDER_STATIC = 64
 
 
 def tile_grid(m: int, n: int) -> tuple[int, int]:
@@ -114,7 +118,8 @@ def workspace(m: int, n: int, k: int, device, sm_count: int | None = None) -> to
 
 def run(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor | None = None, group: int = GROUP,
         status: torch.Tensor | None = None, accumulate: bool = False, bias: torch.Tensor | None = None,
-        relu: bool = False, workspace: torch.Tensor | None = None, tile: str | None = None) -> torch.Tensor:
+        relu: bool = False, workspace: torch.Tensor | None = None, tile: str | None = None,
+        order: str | None = None) -> torch.Tensor:
     """``C[m, n] (+)= map(sum_k A[m, k] * B[n, k] + bias[n])``; A is [m, k], B is [n, k], both bf16 or both fp16 on
     one GPU, C bf16. With ``accumulate`` the rounded product is added into ``c`` (in bf16, by the
     copy engine), which must then be given and hold values. With a ``workspace`` (see :func:`workspace`) a
@@ -143,8 +148,11 @@ def run(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor | None = None, group: 
         raise ValueError("bias must be a contiguous bfloat16 [n] tensor on the device")
     if tile not in (None, "narrow", "wide"):
         raise ValueError("tile is None (the launch chooses), 'narrow' or 'wide'")
+    if order not in (None, "feed", "static"):
+        raise ValueError("order is None (the launch chooses), 'feed' or 'static'")
     flags = ((F16_OPERANDS if a.dtype == torch.float16 else 0) | (ACCUMULATE if accumulate else 0)
-             | (RELU if relu else 0) | {None: 0, "narrow": TILE_NARROW, "wide": TILE_WIDE}[tile])
+             | (RELU if relu else 0) | {None: 0, "narrow": TILE_NARROW, "wide": TILE_WIDE}[tile]
+             | {None: 0, "feed": ORDER_FEED, "static": ORDER_STATIC}[order])
     if workspace is not None and (not workspace.is_cuda or not workspace.is_contiguous()):
         raise ValueError("the workspace must be a contiguous tensor on the device")
     with torch.cuda.device(a.device):

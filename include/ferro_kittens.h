@@ -180,6 +180,13 @@ int fk_gemm_bf16(const void* a, const void* b, void* c, uint32_t m, uint32_t n, 
  *                         a tile's k-blocks are cut across a cluster of two or four CTAs that
  *                         hand their fp32 tiles to the first through distributed shared memory.
  *                         Same operand maps, same C map, same results up to fp32 summation order.
+ *   FK_GEMM_ORDER_FEED / FK_GEMM_ORDER_STATIC  pick how the wide kernel's clusters get their items
+ *                         instead of letting the launch choose: one cluster per item in the grid,
+ *                         the resident clusters taking the others' items over through cluster
+ *                         launch control (the items in flight are then always the next ones of the
+ *                         traversal), or cluster c walking items c, c + clusters, ... . Unasked, a
+ *                         launch of at least four waves of items of at least 32 k-blocks is fed.
+ *                         Same results either way.
  * The `_fused` entries also take `bias`: null, or n bf16 values (16-byte aligned) added per column
  * in fp32 before the rounding -- a column vector every row shares (`load_vec` / `add_col`,
  * src/global.rs:410-416, as examples/src/layernorm.rs:200-203 uses them for beta). Bias first,
@@ -194,6 +201,8 @@ int fk_gemm_bf16(const void* a, const void* b, void* c, uint32_t m, uint32_t n, 
 #define FK_GEMM_RELU 4u
 #define FK_GEMM_TILE_NARROW 8u
 #define FK_GEMM_TILE_WIDE 16u
+#define FK_GEMM_ORDER_FEED 32u
+#define FK_GEMM_ORDER_STATIC 64u
 int fk_gemm_launch_fused(const void* a_map, const void* b_map, const void* c_map, const void* bias, uint32_t m,
                          uint32_t n, uint32_t k, uint32_t group, uint32_t flags, void* stream,
                          uint32_t* device_status);

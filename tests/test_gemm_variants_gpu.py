@@ -100,7 +100,7 @@ def test_unknown_flags_and_missing_c_are_refused(device):
         gemm.run(a, a, accumulate=True)
     c = torch.zeros((256, 256), dtype=torch.bfloat16, device=device)
     with pytest.raises(FerroKittensError, match="unknown GEMM flags"):
-        check(library().fk_gemm(a.data_ptr(), a.data_ptr(), c.data_ptr(), 256, 256, 64, 256, 8, 32,
+        check(library().fk_gemm(a.data_ptr(), a.data_ptr(), c.data_ptr(), 256, 256, 64, 256, 8, 128,
                                 torch.cuda.current_stream().cuda_stream, None))
 
 
@@ -318,12 +318,14 @@ def test_widths_the_kernel_does_not_have_are_refused(device):
 # ---- launches of more items than resident clusters: one cluster per item in the grid, handed out through
 # ---- cluster launch control by the leader CTA's feed warp
 
-@pytest.mark.parametrize("shape", [(8192, 8192, 64), (4352, 4096, 128), (2048, 14336, 192), (16384, 4096, 64)])
+@pytest.mark.parametrize("shape", [(8192, 8192, 64), (4352, 4096, 128), (2048, 14336, 192), (16384, 4096, 64),
+                                   (8192, 8192, 2048)])
 @pytest.mark.parametrize("group", [6, 1])
 def test_items_handed_out_by_the_feed_are_exact(device, shape, group):
-    """A k-block or two per item, so that a cluster runs through items as fast as the feed can claim
-    them (512 to 1024 items on 74 clusters), a ragged last tile row, and a width the launch chooses:
-    every tile must be computed exactly once, whichever cluster took it."""
+    """A k-block or two per item (the feed forced on launches it would not choose), so that a cluster
+    runs through items as fast as the feed can claim them (512 to 1024 items on 74 clusters), a
+    ragged last tile row, a width the launch chooses, and a launch that is fed unasked: every tile
+    must be computed exactly once, whichever cluster took it."""
     m, n, k = shape
     a = _device_words(oracle.gemm_stage("a", m, k), device, torch.bfloat16)
     b = _device_words(oracle.gemm_stage("b", n, k), device, torch.bfloat16)
@@ -331,11 +333,24 @@ def test_items_handed_out_by_the_feed_are_exact(device, shape, group):
     status = gemm.new_status(device)
     for _ in range(3):
         c.fill_(-3.0)
-        gemm.run(a, b, c, group=group, status=status, tile="wide")
+        gemm.run(a, b, c, group=group, status=status, tile="wide", order="feed" if k < 2048 else None)
         torch.cuda.synchronize(device)
         gemm.check_status(status)
         wrong, _, first = oracle.gemm_check_c(_words(c), m, n, k)
         assert wrong == 0, f"{wrong} of {m * n} wrong, first at {first}"
+
+
+def test_the_static_order_gives_the_same_words(device):
+    m, n, k = 8192, 4096, 2048
+    generator = torch.Generator(device=device).manual_seed(9)
+    a = (torch.randn((m, k), generator=generator, device=device) * 0.05).to(torch.bfloat16)
+    b = (torch.randn((n, k), generator=generator, device=device) * 0.05).to(torch.bfloat16)
+    fed = gemm.run(a, b, order="feed")
+    static = gemm.run(a, b, order="static")
+    assert torch.equal(fed, static)
+    with pytest.raises(FerroKittensError, match="both asked for"):
+        check(library().fk_gemm(a.data_ptr(), b.data_ptr(), fed.data_ptr(), m, n, k, n, 6, 96,
+                                torch.cuda.current_stream().cuda_stream, None))
 
 
 def test_accumulate_under_the_feed_adds_every_tile_once(device):
@@ -344,8 +359,13 @@ def test_accumulate_under_the_feed_adds_every_tile_once(device):
     a = _device_words(oracle.gemm_stage("a", m, k), device, torch.bfloat16)
     b = _device_words(oracle.gemm_stage("b", n, k), device, torch.bfloat16)
     c = torch.zeros((m, n), dtype=torch.bfloat16, device=device)
-    _run(a, b, c, accumulate=True)
+    status = gemm.new_status(device)
+    gemm.run(a, b, c, status=status, accumulate=True, order="feed")
+    torch.cuda.synchronize(device)
+    gemm.check_status(status)
     once = _words(c).copy()
     assert oracle.gemm_check_c(once, m, n, k)[0] == 0
-    _run(a, b, c, accumulate=True)
+    gemm.run(a, b, c, status=status, accumulate=True, order="feed")
+    torch.cuda.synchronize(device)
+    gemm.check_status(status)
     assert np.array_equal(_words(c), oracle.bf16_add_words(once, once))
