@@ -146,7 +146,8 @@ struct Problem {
     uint32_t planes;
     uint32_t pairs;   // query blocks of kTiles * kTileRows rows per plane: ceil(seq / 256)
     uint32_t causal;
-    uint32_t items;   // work items of the launch
+    uint32_t whole;   // leading work items that are whole query blocks (two tiles)
+    uint32_t items;   // entries the launch walks: `whole`, then the remaining blocks as two single tiles each
 };
 
 // One visit of a CTA: a query block of one plane, or nothing (`most` == 0).
@@ -168,7 +169,7 @@ __host__ __device__ __forceinline__ uint32_t item_count(uint32_t pairs, uint32_t
 // The `visit`-th stop of CTA `cta` of `ctas`; false past the end of its list.
 __device__ __forceinline__ bool work_at(const Problem& problem, uint32_t cta, uint32_t ctas, uint32_t visit,
                                         Work& work) {
-    uint32_t q_block;
+    uint32_t q_block, single = 0, tiles = kTiles;
     bool present = true;
     if (problem.causal) {
         const uint32_t per_plane = (problem.pairs + 1) / 2;
@@ -179,16 +180,26 @@ __device__ __forceinline__ bool work_at(const Problem& problem, uint32_t cta, ui
         q_block = (visit & 1u) ? h : problem.pairs - 1 - h;
         present = !((visit & 1u) && h == problem.pairs - 1 - h);  // the middle block of an odd count, once
     } else {
-        const uint32_t item = cta + visit * ctas;
-        if (item >= problem.items) return false;
+        // The last, partly filled round of a launch is re-cut into single tiles when those still
+        // fit one round: a tile alone takes about five sixths of a pair's time, and twice as many
+        // CTAs share the round.
+        const uint32_t entry = cta + visit * ctas;
+        if (entry >= problem.items) return false;
+        uint32_t item = entry;
+        if (entry >= problem.whole) {
+            const uint32_t rest = entry - problem.whole;
+            item = problem.whole + (rest >> 1);
+            single = rest & 1u;
+            tiles = 1;
+        }
         work.plane = item / problem.pairs;
         q_block = item % problem.pairs;
     }
-    work.q_row0 = q_block * kTiles * kTileRows;
+    work.q_row0 = q_block * kTiles * kTileRows + kTileRows * single;
     work.most = 0;
     for (uint32_t t = 0; t < kTiles; ++t) {
         const uint32_t first = work.q_row0 + kTileRows * t;
-        work.blocks[t] = (!present || first >= problem.seq) ? 0u
+        work.blocks[t] = (!present || t >= tiles || first >= problem.seq) ? 0u
                          : problem.causal                   ? first / kBlockKeys + 1u
                                                             : problem.seq / kBlockKeys;
         work.most = work.blocks[t] > work.most ? work.blocks[t] : work.most;
@@ -683,11 +694,21 @@ extern "C" int fk_flash_fwd_launch(const void* q_map, const void* k_map, const v
     problem.causal = causal ? 1u : 0u;
     if (static_cast<uint64_t>(causal ? (problem.pairs + 1) / 2 : problem.pairs) * planes > 0x7fffffffull)
         return fk_fail(FK_ERR_SHAPE, "%u planes x %u queries is more work items than a launch walks", planes, seq);
-    problem.items = flash::item_count(problem.pairs, planes, causal != 0);
+    problem.items = problem.whole = flash::item_count(problem.pairs, planes, causal != 0);
 
     DeviceFacts facts;
     const int known = device_facts(&facts);
     if (known != FK_OK) return known;
+    if (!causal) {
+        // Items of one weight: what is left after the whole rounds goes out as single tiles when
+        // two tiles per leftover block still fit one round of CTAs.
+        const uint32_t round = static_cast<uint32_t>(facts.sm_count);
+        const uint32_t tail = problem.items % round;
+        if (tail != 0 && 2 * tail <= round) {
+            problem.whole = problem.items - tail;
+            problem.items = problem.whole + 2 * tail;
+        }
+    }
     uint32_t limit = 0;
     const int admitted = fk_admit_shared_plan(
         reinterpret_cast<const void*>(flash::flash_forward_kernel), flash::kSharedBytes, &limit);

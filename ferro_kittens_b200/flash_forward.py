@@ -24,8 +24,13 @@ def items(sequence: int, planes: int, causal: bool = False) -> int:
 
 
 def grid(sequence: int, planes: int, sm_count: int = 148, causal: bool = False) -> int:
-    """CTAs of a launch: one persistent CTA per SM, fewer when there are fewer work items."""
-    return min(items(sequence, planes, causal), sm_count)
+    """CTAs of a launch: one persistent CTA per SM, fewer when there are fewer work entries. Without a
+    mask the items left after the whole rounds are walked as two single tiles each when those fit one round."""
+    count = items(sequence, planes, causal)
+    tail = count % sm_count
+    if not causal and tail and 2 * tail <= sm_count:
+        count += tail
+    return min(count, sm_count)
 
 
 def _require(name: str, tensor: torch.Tensor) -> None:
