@@ -61,6 +61,17 @@ __device__ __forceinline__ void st_shared_cluster_v4(uint32_t cluster_addr, uint
 }
 /// Makes what peer CTAs wrote into this CTA's shared memory before their release-arrive visible
 /// to the loads that follow a wait on the barrier they arrived on.
+/// Bulk copy from this CTA's shared memory into a peer CTA's (both addresses and the size multiples
+/// of 16 bytes), completing `bytes` on an mbarrier of the cluster (the peer's, as a rule). The
+/// source may be reused once that barrier's phase has completed.
+__device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster_addr, uint32_t src_cta_addr, uint32_t bytes,
+                                                  uint32_t cluster_bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+            dst_cluster_addr),
+        "r"(src_cta_addr), "r"(bytes), "r"(cluster_bar)
+        : "memory");
+}
 __device__ __forceinline__ void fence_acq_rel_cluster() {
     asm volatile("fence.acq_rel.cluster;" ::: "memory");
 }

@@ -787,7 +787,7 @@ __global__ void __launch_bounds__(kThreads, kStages == kStagesShared ? 2 : 1)
         }
         mbar_init(acc_full, 1);
         mbar_init(go, 1);
-        mbar_init(partial_full, (slices > 1 ? slices - 1 : 1) * kEpilogueWarps);
+        mbar_init(partial_full, 1);
         *stop_flag = 0;
         fence_mbarrier_init();
         fence_proxy_async_shared();
@@ -862,31 +862,38 @@ __global__ void __launch_bounds__(kThreads, kStages == kStagesShared ? 2 : 1)
         if (live) tc_fence_after_sync();
         const uint32_t row = 32 * quadrant + lane;  // of the tile
         if (kSliced && live && slice != 0) {
-            // A contributor: once the first CTA's ring is idle (`go`), this warp's 32 rows of the fp32
-            // tile go into its slot there, then the warp counts itself in.
-            live = mbar_wait(go, 0, site, kStallEpilogue, 1);
-            if (live) {
-                const uint32_t slot_base = a_ring + (slice - 1) * kPartialBytes;
+            // A contributor: this warp's 32 rows of the fp32 tile are staged in the CTA's own ring
+            // (idle: its MMAs have retired) and, once the first CTA's ring is idle too (`go`), go
+            // into this CTA's slot there as one 16 KiB bulk copy that completes on the first CTA's
+            // `partial_full`. (Written there by 4096 remote 16-byte stores instead, the hand-over
+            // took several microseconds.)
 #pragma unroll 1
-                for (uint32_t part = 0; part < kTile / 32; ++part) {
-                    uint32_t v[32];
-                    tmem_ld_32x32(t_row + 32 * part, v);
-                    tmem_wait_ld();
+            for (uint32_t part = 0; part < kTile / 32; ++part) {
+                uint32_t v[32];
+                tmem_ld_32x32(t_row + 32 * part, v);
+                tmem_wait_ld();
 #pragma unroll
-                    for (uint32_t chunk = 0; chunk < 8; ++chunk)
-                        st_shared_cluster_v4(mapa(slot_base + partial_offset(row, 8 * part + chunk), 0), v[4 * chunk],
-                                             v[4 * chunk + 1], v[4 * chunk + 2], v[4 * chunk + 3]);
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(mapa(partial_full, 0));
+                for (uint32_t chunk = 0; chunk < 8; ++chunk)
+                    st_shared_v4(a_ring + partial_offset(row, 8 * part + chunk), v[4 * chunk], v[4 * chunk + 1],
+                                 v[4 * chunk + 2], v[4 * chunk + 3]);
+            }
+            fence_proxy_async_shared();
+            __syncwarp();
+            live = mbar_wait(go, 0, site, kStallEpilogue, 1);
+            if (live && lane == 0) {
+                constexpr uint32_t kBandOfPartial = 32 * kTile * 4;
+                const uint32_t band_at = quadrant * kBandOfPartial;
+                bulk_copy_to_peer(mapa(a_ring + (slice - 1) * kPartialBytes + band_at, 0), a_ring + band_at, kBandOfPartial,
+                                  mapa(partial_full, 0));
             }
         } else if (live) {
             if (kSliced) {
                 // The first CTA: its MMAs have retired, so its ring is free for the others' tiles.
-                if (warp == 2 && lane == 0)
+                if (warp == 2 && lane == 0) {
+                    mbar_arrive_expect_tx(partial_full, (slices - 1) * kPartialBytes);
                     for (uint32_t peer = 1; peer < slices; ++peer) mbar_arrive_cluster(mapa(go, peer));
+                }
                 live = mbar_wait(partial_full, 0, site, kStallEpilogue, 2);
-                fence_acq_rel_cluster();
             }
             const int c_row = static_cast<int>(row0 + 32 * quadrant);
 #pragma unroll 1
@@ -1041,6 +1048,37 @@ static bool takes_narrow(uint32_t m, uint32_t n, uint32_t k, uint32_t flags, uin
     return (flags & FK_GEMM_TILE_NARROW) || (!(flags & FK_GEMM_TILE_WIDE) && narrow_by_default(m, n, k, sm_count));
 }
 
+// Clusters of `slices` CTAs of the sliced narrow kernel this device holds at once (0 if the runtime
+// cannot say), asked once per device and size.
+static uint32_t resident_narrow_clusters(uint32_t slices) {
+    static std::mutex guard;
+    static int known[64][gemm::narrow::kMaxSlices + 1];  // 0 = not asked yet, -1 = no answer
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64 || slices > gemm::narrow::kMaxSlices) return 0;
+    std::lock_guard<std::mutex> lock(guard);
+    if (known[device][slices] == 0) {
+        const auto kernel = gemm::narrow::gemm_bf16_narrow_kernel<gemm::narrow::kStagesAlone, true>;
+        const uint32_t bytes = gemm::narrow::shared_bytes<gemm::narrow::kStagesAlone>();
+        uint32_t limit = 0;
+        int clusters = 0;
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(1, 1, slices);
+        config.blockDim = dim3(gemm::narrow::kThreads, 1, 1);
+        config.dynamicSmemBytes = bytes;
+        cudaLaunchAttribute cluster;
+        cluster.id = cudaLaunchAttributeClusterDimension;
+        cluster.val.clusterDim.x = 1, cluster.val.clusterDim.y = 1, cluster.val.clusterDim.z = slices;
+        config.attrs = &cluster;
+        config.numAttrs = 1;
+        if (fk_admit_shared_plan(reinterpret_cast<const void*>(kernel), bytes, &limit) == FK_OK &&
+            cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) == cudaSuccess && clusters > 0)
+            known[device][slices] = clusters;
+        else
+            known[device][slices] = -1, (void)cudaGetLastError();
+    }
+    return known[device][slices] > 0 ? static_cast<uint32_t>(known[device][slices]) : 0u;
+}
+
 // The launch behind every GEMM entry. `tile_n` is the width of the wide kernel's items: 256 with the
 // caller's maps (B's box is then 128 rows); the entries that build the maps themselves may pass 224
 // or 192 with a B box of tile_n / 2 rows and, when tile_n is an odd multiple of 32, `c_narrow_map`,
@@ -1104,13 +1142,16 @@ static int launch_fused(const void* a_map, const void* b_map, const void* c_map,
         };
         const uint64_t count = uint64_t(tiles.x) * tiles.y;
         // Few tiles and a deep K: a cluster per tile, each CTA a run of the k-blocks. The hand-over
-        // (two cluster rendezvous, 64 KiB per contributor through distributed shared memory, the
-        // first CTA summing them) costs 5-7 us, a k-block on a lone CTA ~0.25 us: worth it from 128
-        // k-blocks on, in runs of at least 32 (1024 x 1024 x 8192: 30.4 -> 24.5 us; 512 x 512 x 16384:
-        // 56 -> 26; but 512 x 768 x 2048 in four runs of 8: 10.4 -> 17.5).
+        // (two cluster rendezvous, 64 KiB per contributor staged and bulk-copied into the first CTA's
+        // shared memory, the first CTA summing them) costs 2-3 us, a k-block on a lone CTA ~0.21 us:
+        // worth it from 64 k-blocks on, in runs of at least 16 (1024 x 1024 x 4096: 16.4 -> 14.9 us;
+        // 256 x 256 x 4096: 16.2 -> 12.9; 512 x 512 x 16384: 56 -> 23; but 1024 x 1024 x 2048 in two runs
+        // of 16: 10.0 -> 11.5) -- and only while every cluster is resident at once: clusters of four
+        // pack a GPC's SMs worse than single CTAs (768 x 768 x 4096, 36 clusters of four: two rounds,
+        // 25.6 us against 16.4 uncut), so the count is the runtime's, not SMs / slices.
         uint32_t slices = 1;
-        while (plan.k_blocks >= 128 && slices < gemm::narrow::kMaxSlices &&
-               count * (2 * slices) <= static_cast<uint64_t>(sm_count) && plan.k_blocks / (2 * slices) >= 32)
+        while (plan.k_blocks >= 64 && slices < gemm::narrow::kMaxSlices && plan.k_blocks / (2 * slices) >= 16 &&
+               count <= resident_narrow_clusters(2 * slices))
             slices *= 2;
         if (slices > 1)
             return launch_narrow(gemm::narrow::gemm_bf16_narrow_kernel<gemm::narrow::kStagesAlone, true>,

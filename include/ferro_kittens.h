@@ -176,7 +176,7 @@ int fk_gemm_bf16(const void* a, const void* b, void* c, uint32_t m, uint32_t n, 
  *                         reference ships as its own entry for launches at or below half a wave
  *                         (`gemm_sol_m256_n128`, examples/src/gemm_sol.rs:1063, dispatch :1335-1337).
  *                         Unasked, a launch of at most 128 narrow tiles, or of at most two per SM
- *                         with K <= 2048, takes the narrow tile; with K >= 8192 and SMs to spare
+ *                         with K <= 2048, takes the narrow tile; with K >= 4096 and SMs to spare
  *                         a tile's k-blocks are cut across a cluster of two or four CTAs that
  *                         hand their fp32 tiles to the first through distributed shared memory.
  *                         Same operand maps, same C map, same results up to fp32 summation order.
