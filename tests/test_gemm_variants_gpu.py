@@ -340,6 +340,21 @@ def test_items_handed_out_by_the_feed_are_exact(device, shape, group):
         assert wrong == 0, f"{wrong} of {m * n} wrong, first at {first}"
 
 
+@pytest.mark.parametrize("columns", [224, 192])
+def test_narrower_items_under_the_feed(device, columns):
+    """Both choices at once: items of 224 / 192 columns handed out through cluster launch control,
+    a ragged last tile row, twice in a row."""
+    m, n, k = 7936, 5376, 128
+    a = _device_words(oracle.gemm_stage("a", m, k), device, torch.bfloat16)
+    b = _device_words(oracle.gemm_stage("b", n, k), device, torch.bfloat16)
+    c = torch.full((m, n), -3.0, dtype=torch.bfloat16, device=device)
+    for _ in range(2):
+        c.fill_(-3.0)
+        _run_tiled(a, b, c, columns, flags=gemm.ORDER_FEED)
+        wrong, _, first = oracle.gemm_check_c(_words(c), m, n, k)
+        assert wrong == 0, f"{wrong} of {m * n} wrong, first at {first}"
+
+
 def test_the_static_order_gives_the_same_words(device):
     m, n, k = 8192, 4096, 2048
     generator = torch.Generator(device=device).manual_seed(9)
