@@ -83,12 +83,14 @@ def test_seeded_random_within_tolerance(device, causal, shape):
 
 
 @pytest.mark.parametrize("planes, sequence, causal", [(80, 512, False), (100, 768, True), (170, 256, False),
-                                                      (160, 256, True)])
+                                                      (160, 256, True), (100, 384, False), (20, 512, False)])
 def test_more_work_items_than_sms(device, planes, sequence, causal):
     """The grid is one persistent CTA per SM: with more (query block, plane) items than SMs a CTA
     walks several, carrying its barrier phases, its K/V ring position and the hand-over of the
     output accumulator from one item to the next. Causal items are pairs of query blocks (three
-    blocks per plane: a pair and a lone middle block); 256 queries leave a single block per plane."""
+    blocks per plane: a pair and a lone middle block); 256 queries leave a single block per plane.
+    Without a mask the items left after the whole rounds are walked as single tiles (80 x 512: 12 items
+    -> 24 tiles; 100 x 384: 52 items, every second one a lone tile already; 20 x 512: all 40 items)."""
     generator = torch.Generator(device="cpu").manual_seed(11 + planes)
     q, k, v = (torch.randn((planes, sequence, 128), generator=generator).to(torch.bfloat16) for _ in range(3))
     out, lse = _run_checked(q.to(device), k.to(device), v.to(device), causal=causal)
