@@ -295,6 +295,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     from ferro_kittens_b200._lib import check, library
     from ferro_kittens_b200.build import build_cublaslt
 
+    asked_group = args.group
     args.group = args.group or gemm.GROUP
 
     if not torch.cuda.is_available():
@@ -335,11 +336,12 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         status = gemm.new_status(device)
         # maps built once, as the reference's `run` does, to the item width this shard's waves want
         maps = gemm.TiledMaps(a, b, c)
+        group = asked_group or gemm.group_for(m, n_local, device)
         if cublaslt.fkb_prepare(m, n_local, k) != 0:
             raise RuntimeError(cublaslt.fkb_last_error().decode())
 
         def step():
-            gemm.launch_tiled(maps, m, n_local, k, args.group, status)
+            gemm.launch_tiled(maps, m, n_local, k, group, status)
 
         def library_step():
             if cublaslt.fkb_gemm(a.data_ptr(), b.data_ptr(), c_ref.data_ptr(), stream) != 0:
@@ -380,7 +382,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         achieved = flops_rank / (ours["seconds"] / args.steps) / 1e12
         result = {
             "config": {"m": m, "n": n, "k": k, "seed": config["seed"], "entries": config["entries"],
-                       "columns_per_rank": n_local, "item_columns": maps.columns},
+                       "columns_per_rank": n_local, "item_columns": maps.columns, "group": group},
             "ours": ours_out, "cublaslt_alone": theirs_out,
             "interleaved": {"pairs": max(10, args.steps), "ours": side["ours"], "cublaslt": side["cublaslt"],
                             "ratio_ours_over_cublaslt_at_median": side["cublaslt"]["median_ms"] / side["ours"]["median_ms"],
@@ -568,7 +570,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": per_launch_s * 1e3, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "m": M, "n": N, "k": K, "group": args.group,
+            "config": {"workload": WORKLOAD, "m": M, "n": N, "k": K, "group": c2["config"]["group"],
                        "sharding": f"B split by N-column blocks over {world} rank(s), {n_local} columns each; "
                                    "A replicated; no collective",
                        "l2": "inputs (A 512 MiB + B shard) larger than the 126 MB L2; no flush between steps",
@@ -644,6 +646,7 @@ def run_only(args, local_rank: int) -> None:
     from ferro_kittens_b200 import gemm
     from ferro_kittens_b200._lib import check, library
 
+    asked_group = args.group
     args.group = args.group or gemm.GROUP
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
@@ -657,7 +660,8 @@ def run_only(args, local_rank: int) -> None:
         c = torch.empty((m, n), dtype=torch.bfloat16, device=device)
         maps = gemm.TiledMaps(a, b, c, columns=args.item_columns or None)
         flags = (gemm.TILE_WIDE if args.item_columns else 0) | {"": 0, "feed": gemm.ORDER_FEED, "static": gemm.ORDER_STATIC}[args.order]
-        fn = lambda: gemm.launch_tiled(maps, m, n, k, args.group, status, flags=flags)  # noqa: E731
+        group = asked_group or gemm.group_for(m, n, device)
+        fn = lambda: gemm.launch_tiled(maps, m, n, k, group, status, flags=flags)  # noqa: E731
         flops = 2.0 * m * n * k
         name = f"gemm_bf16_{m}x{n}x{k}"
     elif args.only in ("softmax", "layernorm", "groupnorm"):

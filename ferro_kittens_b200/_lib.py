@@ -72,6 +72,7 @@ SIGNATURES = {
     "fk_flash_shared_bytes": (c_uint32, []),
     "fk_flash_threads": (c_uint32, []),
     "fk_gemm_grid": (c_uint32, [c_uint32, c_uint32, c_uint32]),
+    "fk_gemm_group": (c_uint32, [c_uint32, c_uint32, c_uint32]),
     "fk_gemm_item_columns": (c_uint32, [c_uint32, c_uint32, c_uint32, c_uint32, c_uint32]),
     "fk_gemm_launch_tiled": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_uint32, c_void_p, c_uint32, c_uint32,
                                      c_uint32, c_uint32, c_uint32, c_void_p, c_void_p]),

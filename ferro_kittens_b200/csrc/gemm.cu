@@ -1196,6 +1196,21 @@ extern "C" int fk_gemm_launch_fused(const void* a_map, const void* b_map, const 
     return launch_fused(a_map, b_map, c_map, c_map, gemm::kBlockN, bias, m, n, k, group, flags, stream, device_status);
 }
 
+extern "C" uint32_t fk_gemm_group(uint32_t m, uint32_t n, uint32_t sm_count) {
+    // Items in flight: one per cluster, g tile rows by clusters / g tile columns of the traversal. A tile
+    // row's panel of A is twice a tile column's panel of B, so the fewest panel bytes per wave are at
+    // g = sqrt(clusters / 2): 6 on 148 SMs (measured: 5-7 level, 8 is 1.5 % behind, 16 is 6 %). A
+    // matrix narrower than that window (16384 x 2048: 8 tile columns) is covered whole by any g, and
+    // short bands did better there (g = 2-4: 1334-1344 TFLOP/s, 6-8: 1313-1322).
+    (void)m;
+    const uint32_t clusters = sm_count / 2;
+    uint32_t best = 1;
+    while (2 * (best + 1) * (best + 1) <= clusters) ++best;
+    const uint32_t window_columns = best ? clusters / best : clusters;
+    if (n / gemm::kBlockN < window_columns) best = best > 2 ? (2 * best) / 3 : best;
+    return best ? best : 1u;
+}
+
 extern "C" uint32_t fk_gemm_item_columns(uint32_t m, uint32_t n, uint32_t k, uint32_t flags, uint32_t sm_count) {
     if (m == 0 || n == 0 || k == 0 || m % (2 * gemm::kBlockM) || n % gemm::kBlockN || k % gemm::kBlockK || sm_count < 2)
         return gemm::kBlockN;

@@ -72,6 +72,13 @@ def launch(a_map, b_map, c_map, m: int, n: int, k: int, group: int = GROUP, stat
                                         group, handle, status.data_ptr() if status is not None else None))
 
 
+def group_for(m: int, n: int, device) -> int:
+    """The traversal width this library would pick for an [m, n] product on ``device`` (:data:`GROUP` for
+    matrices at least as wide as the items in flight span, shorter bands for narrower ones)."""
+    sm_count = torch.cuda.get_device_properties(device).multi_processor_count
+    return library().fk_gemm_group(m, n, sm_count)
+
+
 def item_columns(m: int, n: int, k: int, device, flags: int = 0) -> int:
     """Columns of C per item the wide kernel would take for this shape on ``device``: 256, or 224 / 192
     where a launch's tiles sit just past a whole number of waves and narrower items fill them better."""

@@ -196,6 +196,9 @@ int fk_gemm_bf16(const void* a, const void* b, void* c, uint32_t m, uint32_t n, 
  * best with on a 148-SM part: its 74 items in flight then cover 6 x 12.3 tiles, the fewest operand
  * panel bytes per wave for [512, 256] items. */
 #define FK_GEMM_GROUP 6u
+/* The same for a given shape and device: FK_GEMM_GROUP's rule, sqrt(clusters / 2), and two thirds of it
+ * for a matrix with fewer tile columns than the items in flight span (an eighth of 16384 columns). */
+uint32_t fk_gemm_group(uint32_t m, uint32_t n, uint32_t sm_count);
 #define FK_GEMM_F16_OPERANDS 1u
 #define FK_GEMM_ACCUMULATE 2u
 #define FK_GEMM_RELU 4u

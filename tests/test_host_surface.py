@@ -213,6 +213,21 @@ def test_grid_is_whole_clusters_capped_at_one_per_sm_pair():
     assert lib.fk_gemm_grid(16384, 2048, 148) == 148
 
 
+def test_traversal_width_follows_the_window_of_items_in_flight():
+    lib = library()
+    # sqrt(clusters / 2): the fewest operand-panel bytes per wave when a tile row's A panel is twice a tile column's B panel
+    from ferro_kittens_b200 import gemm
+
+    assert lib.fk_gemm_group(16384, 16384, 148) == 6 == gemm.GROUP
+    assert lib.fk_gemm_group(8192, 28672, 148) == 6
+    assert lib.fk_gemm_group(8192, 3584, 148) == 6       # 14 tile columns: wider than the 12.3 the window spans
+    assert lib.fk_gemm_group(16384, 2048, 148) == 4      # 8 tile columns: shorter bands
+    assert lib.fk_gemm_group(4096, 4096, 132) == 5
+    for sm_count in (2, 3, 16, 64, 132, 148, 160):
+        for n in (256, 2048, 16384):
+            assert 1 <= lib.fk_gemm_group(4096, n, sm_count) <= max(1, sm_count // 2)
+
+
 def _wave_time(m, n, columns, clusters):
     """Wave-times of [512, 256] items a launch takes with items `columns` wide: whole waves, and a last
     one that costs half when it holds at most half a wave of tiles (it is re-cut into halves)."""
