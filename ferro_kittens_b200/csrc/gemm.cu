@@ -29,7 +29,11 @@
 //               one item ahead, and publishes its index to every role of both CTAs. The items in
 //               flight are therefore always the next ones of the traversal, however far the
 //               clusters' speeds drift apart over a launch: a static round-robin lets slow clusters
-//               fall waves behind, and the operand panels live in L2 multiply.
+//               fall waves behind, and the operand panels live in L2 multiply. (The reference's
+//               stealing item loop, `run_stealing` over a `ClcQueue`, src/pipeline.rs:276-660, which
+//               its `gemm_sol` runs on, examples/src/gemm_sol.rs:289-321; it asks after an item,
+//               with the answer multicast to the cluster; here the request goes out an item ahead
+//               and the leader forwards the answer, so no role ever waits for it.)
 //
 // Barriers are initialised once per launch and their phases carried across
 // items; roles meet only through them. Every wait is bounded.

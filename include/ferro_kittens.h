@@ -181,7 +181,8 @@ int fk_gemm_bf16(const void* a, const void* b, void* c, uint32_t m, uint32_t n, 
  *                         hand their fp32 tiles to the first through distributed shared memory.
  *                         Same operand maps, same C map, same results up to fp32 summation order.
  *   FK_GEMM_ORDER_FEED / FK_GEMM_ORDER_STATIC  pick how the wide kernel's clusters get their items
- *                         instead of letting the launch choose: one cluster per item in the grid,
+ *                         instead of letting the launch choose (the reference's two item loops,
+ *                         `run_stealing` and `run`, src/pipeline.rs:613-660, 226-273): one cluster per item in the grid,
  *                         the resident clusters taking the others' items over through cluster
  *                         launch control (the items in flight are then always the next ones of the
  *                         traversal), or cluster c walking items c, c + clusters, ... . Unasked, a
