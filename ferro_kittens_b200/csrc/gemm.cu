@@ -638,17 +638,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 // stores go out back to back instead of waiting for one staging tile in turn.
                 const uint32_t spare = a_ring + (warp - 2) * kPasses * kBandBytes;
 #pragma unroll
-                for (uint32_t pass = 0; pass + 1 < kPasses; ++pass) stage(spare + pass * kBandBytes, held[pass]);
-                if (last_pass == kLastWhole) stage(spare + (kPasses - 1) * kBandBytes, held[kPasses - 1]);
-                if (last_pass == kLastNarrow) stage_narrow(spare + (kPasses - 1) * kBandBytes, held[kPasses - 1]);
-                fence_proxy_async_shared();
-                __syncwarp();
-                if (lane == 0) {
-#pragma unroll
-                    for (uint32_t pass = 0; pass + 1 < kPasses; ++pass) store(&c_map, spare + pass * kBandBytes, pass);
-                    if (last_pass == kLastWhole) store(&c_map, spare + (kPasses - 1) * kBandBytes, kPasses - 1);
-                    if (last_pass == kLastNarrow) store(&extra_map, spare + (kPasses - 1) * kBandBytes, kPasses - 1);
-                    tma_store_commit();
+                for (uint32_t pass = 0; pass < kPasses; ++pass) {
+                    const bool narrow = pass + 1 == kPasses && last_pass == kLastNarrow;
+                    if (pass + 1 == kPasses && last_pass == kLastNone) break;
+                    // Staged and sent pass by pass: the copy engine reads one tile while the next is staged.
+                    if (narrow)
+                        stage_narrow(spare + pass * kBandBytes, held[pass]);
+                    else
+                        stage(spare + pass * kBandBytes, held[pass]);
+                    fence_proxy_async_shared();
+                    __syncwarp();
+                    if (lane == 0) {
+                        store(narrow ? &extra_map : &c_map, spare + pass * kBandBytes, pass);
+                        tma_store_commit();
+                    }
                 }
                 continue;
             }
@@ -723,7 +726,9 @@ struct Plan {
     constexpr Plan()
         : a_ring(SharedPlan{}.tile_ring(kTile, kBlockK, 2, kStages)),
           b_ring(a_ring.tile_ring(kTile, kBlockK, 2, kStages)),
-          bands(b_ring.tile_ring(32, kStageColumns, 2, kEpilogueWarps)),
+          // one staging tile per epilogue warp and pass where the shared memory allows (a CTA alone on its
+          // SM): the second pass is then staged while the copy engine still reads the first
+          bands(b_ring.tile_ring(32, kStageColumns, 2, kEpilogueWarps * (kStages == kStagesAlone ? kTile / kStageColumns : 1))),
           full(bands.semaphores(kStages)),
           empty(full.semaphores(kStages)),
           acc_full(empty.semaphore()),
@@ -923,20 +928,25 @@ __global__ void __launch_bounds__(kThreads, kStages == kStagesShared ? 2 : 1)
                     }
                 }
                 finish_pass(lo, hi, plan, column0 + pass * kStageColumns, packed);
-                if (lane == 0) tma_store_wait_read<0>();
-                __syncwarp();
+                // A tile of its own per pass, or the one tile once the store that read it last is done reading.
+                constexpr bool kTilePerPass = kStages == kStagesAlone;
+                const uint32_t tile = kTilePerPass ? band + pass * kEpilogueWarps * kBandBytes : band;
+                if (!kTilePerPass) {
+                    if (lane == 0) tma_store_wait_read<0>();
+                    __syncwarp();
+                }
 #pragma unroll
                 for (uint32_t chunk = 0; chunk < 8; ++chunk)
-                    st_shared_v4(band + swizzled_chunk_offset(lane, chunk, 0), packed[4 * chunk], packed[4 * chunk + 1],
+                    st_shared_v4(tile + swizzled_chunk_offset(lane, chunk, 0), packed[4 * chunk], packed[4 * chunk + 1],
                                  packed[4 * chunk + 2], packed[4 * chunk + 3]);
                 fence_proxy_async_shared();
                 __syncwarp();
                 if (lane == 0) {
                     const int column = static_cast<int>(column0 + pass * kStageColumns);
                     if (plan.accumulate)
-                        tma_reduce_add_2d(&c_map, band, column, c_row);
+                        tma_reduce_add_2d(&c_map, tile, column, c_row);
                     else
-                        tma_store_2d(&c_map, band, column, c_row);
+                        tma_store_2d(&c_map, tile, column, c_row);
                     tma_store_commit();
                 }
             }
