@@ -368,6 +368,25 @@ def test_the_static_order_gives_the_same_words(device):
                                 torch.cuda.current_stream().cuda_stream, None))
 
 
+def test_fed_launches_back_to_back_stay_clean(device):
+    """A few hundred fed launches in a row over three shapes (items of one k-block to 64): no wait runs
+    out, and every C equals the static order's bit for bit."""
+    cases = []
+    for m, n, k in [(8192, 8192, 64), (4096, 8192, 1024), (8192, 4096, 4096)]:
+        generator = torch.Generator(device=device).manual_seed(m + k)
+        a = (torch.randn((m, k), generator=generator, device=device) / k ** 0.5).to(torch.bfloat16)
+        b = (torch.randn((n, k), generator=generator, device=device) / k ** 0.5).to(torch.bfloat16)
+        cases.append((a, b, gemm.run(a, b, tile="wide", order="static")))
+    status = gemm.new_status(device)
+    for _ in range(12):
+        for a, b, expected in cases:
+            c = torch.empty_like(expected)
+            for _ in range(8):
+                gemm.run(a, b, c, status=status, tile="wide", order="feed")
+            gemm.check_status(status)
+            assert torch.equal(c, expected)
+
+
 def test_accumulate_under_the_feed_adds_every_tile_once(device):
     """C += A.B^T with more items than clusters: a tile taken twice, or dropped, shows in the sum."""
     m, n, k = 4096, 8192, 64
